@@ -1,0 +1,154 @@
+/*
+ * C ABI of the B200 (sm_100a) W4A16 matmul path.
+ *
+ * This is the drop-in boundary for the AWQ int4 / group-128 / bf16-activation
+ * linear layers of the reference server: the functions below are what its C++
+ * launchers in src/kernels/gemv_w4a16.{cuh,cu} and src/kernels/gemm_w4a16.{cuh,cu}
+ * bind to (the inline C++ shims with the reference's exact signatures live in
+ * dropin/kernels/ of the package). Every pointer that names tensor data is a
+ * DEVICE pointer; `stream` is a cudaStream_t passed as void*. Every function
+ * returns 0 on success or a negative W4A16_E* code, never aborts, and leaves a
+ * message for w4a16_last_error(). Nothing here synchronises the device or
+ * allocates inside a launch, so all launchers can be captured into a CUDA graph
+ * after one eager warm-up call.
+ *
+ * "file:line" below cites the reference interface each entry replaces, by the
+ * file's path inside the reference project.
+ */
+#ifndef W4A16_B200_H_
+#define W4A16_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+#define W4A16_OK 0
+#define W4A16_EINVAL (-1)   /* bad argument: null/misaligned pointer, unsupported shape */
+#define W4A16_ECUDA (-2)    /* a CUDA runtime call failed */
+#define W4A16_ESCRATCH (-3) /* scratch / workspace too small for this call */
+#define W4A16_ETIMEOUT (-4) /* a bounded device-side wait expired */
+#define W4A16_ECOMM (-5)    /* shard descriptor inconsistent */
+
+/* Kernel-private weight container; field-for-field the reference's
+ * qwen::W4A16Weights (src/kernels/gemv_w4a16.cuh:50-60). The three buffers are
+ * independent allocations, so callers may cudaFree them one by one as the
+ * reference's callers do. Private layout (group_size 128):
+ *   qweight [out_f/16][in_f/64][32] uint4  one 16-row x 64-k block per 512 B; lane l
+ *           holds rows l/4 and l/4+8, k = 16*(l%4)+[0,16), 8 nibbles per word with
+ *           k-offset c at nibble (c>>1)+4*(c&1), words ordered {row lo k0-7, row lo
+ *           k8-15, row hi k0-7, row hi k8-15}
+ *   scale   [out_f/16][G][16] bf16
+ *   zp      [out_f/16][G][16] u8    raw stored nibble (value+8) */
+typedef struct w4a16_weights {
+  uint32_t* qweight;
+  uint16_t* scale; /* bf16 bits */
+  uint8_t* zp;
+  int out_f, in_f, group_size, num_groups;
+} w4a16_weights_t;
+
+/* Caller-owned scratch; field-for-field qwen::GemvScratch
+ * (src/kernels/gemv_w4a16.cuh:94-110). Here: `partial` holds split-K partial
+ * tiles, `xgsum` the per-tile arrival counters (kept zero between calls),
+ * `xf` the per-CTA (max, index) pairs of the fused argmax. One call in flight
+ * per scratch, as in the reference. */
+typedef struct w4a16_scratch {
+  float* xf;
+  float* xgsum;
+  float* partial;
+  int max_in, max_groups, max_out, max_splits, max_m;
+  size_t partial_elems;
+} w4a16_scratch_t;
+
+/* Prefill workspace; mirrors qwen::GemmWorkspace (src/kernels/gemm_w4a16.cuh:30-38).
+ * The fused prefill GEMM needs no dequantised tile, so `wbuf` only holds the
+ * tensor-map descriptors and is small; `cublas` stays NULL (no cuBLAS). */
+typedef struct w4a16_workspace {
+  uint16_t* wbuf;
+  size_t bytes;
+  int max_rows;
+  void* cublas;
+} w4a16_workspace_t;
+
+const char* w4a16_last_error(void);
+/* Sticky device-side status of the last kernels on the current device (0 = ok,
+ * W4A16_ETIMEOUT if a bounded wait expired). Synchronises the device. */
+int w4a16_device_status(void);
+
+/* awq_alloc_fused (gemv_w4a16.cuh:85, gemv_w4a16.cu:308-315): allocate the three buffers. */
+int w4a16_weights_alloc(w4a16_weights_t* w, int out_f, int in_f, int group_size, void* stream);
+/* awq_repack_into (gemv_w4a16.cuh:87-89, gemv_w4a16.cu:317-323): on-disk tensors
+ * packed [out_f][in_f/8] u32, scale [out_f][G] bf16, zp [out_f/8][G] u32 -> private
+ * layout, rows written at dst_row_offset (a multiple of 16). */
+int w4a16_repack_into(const w4a16_weights_t* w, int dst_row_offset, const uint32_t* packed,
+                      const uint16_t* scale, const uint32_t* zp, int out_f, void* stream);
+/* awq_free (gemv_w4a16.cuh:90). */
+int w4a16_weights_free(w4a16_weights_t* w);
+
+/* gemv_scratch_alloc / gemv_scratch_free (gemv_w4a16.cuh:106-107, gemv_w4a16.cu:344-371). */
+int w4a16_scratch_alloc(w4a16_scratch_t* s, int max_in, int max_out, int min_group, int max_m);
+int w4a16_scratch_free(w4a16_scratch_t* s);
+/* gemv_partial_check (gemv_w4a16.cuh:109): W4A16_ESCRATCH instead of abort. */
+int w4a16_scratch_check(const w4a16_scratch_t* s, int out_f, int M);
+/* gemv_choose_splits (gemv_w4a16.cuh:135): the number of CTAs that share one
+ * output tile's K range under the persistent schedule (>= 1). */
+int w4a16_choose_splits(int out_f, int num_groups);
+
+/* gemv_w4a16 / gemv_w4a16_f32 (gemv_w4a16.cuh:129-132): y[out_f] = W x, x bf16 [in_f];
+ * y is bf16 when y_is_f32 == 0, fp32 otherwise. */
+int w4a16_gemv(void* y, int y_is_f32, const w4a16_weights_t* w, const uint16_t* x,
+               w4a16_scratch_t* s, void* stream);
+/* gemm_small_w4a16 and gemm_mma_w4a16 (gemv_w4a16.cuh:124-125,187-188):
+ * Y[M][out_f] = X[M][in_f] W^T, 1 <= M <= 16, row-major bf16, weights read once. */
+int w4a16_gemm_skinny(uint16_t* y, const w4a16_weights_t* w, const uint16_t* x, int M,
+                      w4a16_scratch_t* s, void* stream);
+/* lm_head with the argmax fused. Replaces gemv_w4a16 / gemm_mma_w4a16 on lm_head
+ * followed by argmax / argmax_rows (src/model/model.cu:796-815,1009-1051;
+ * src/kernels/elementwise.cu:96-194): ids[m] = index of the largest bf16-rounded
+ * logit of row m, lowest index on ties. `logits` (bf16 [M][out_f]) may be NULL.
+ * `pairs` may be NULL; otherwise it receives M x {float best, int32 index} with
+ * index = row + row_offset, for the cross-rank reduction of a vocab-sharded head. */
+int w4a16_lm_head_argmax(int32_t* ids, uint16_t* logits, void* pairs, int row_offset,
+                         const w4a16_weights_t* w, const uint16_t* x, int M,
+                         w4a16_scratch_t* s, void* stream);
+/* Reduce nranks x M gathered {float,int32} pairs (rank-major) to ids[M]:
+ * larger value wins, then lower index. The cross-rank step of the sharded lm_head. */
+int w4a16_argmax_pairs_reduce(int32_t* ids, const void* pairs, int nranks, int M, void* stream);
+
+/* w4a16_dequant_rows (gemm_w4a16.cuh:45-48, gemm_w4a16.cu:15-38,56-61): rows
+ * [row0,row0+nrows) -> row-major bf16 [nrows][in_f], bf16(float(q-zp)*float(s)). */
+int w4a16_dequant_rows(uint16_t* dst, const w4a16_weights_t* w, int row0, int nrows, void* stream);
+
+/* gemm_workspace_alloc / free (gemm_w4a16.cuh:37-38). */
+int w4a16_workspace_alloc(w4a16_workspace_t* ws, size_t bytes);
+int w4a16_workspace_free(w4a16_workspace_t* ws);
+/* gemm_w4a16 (gemm_w4a16.cuh:42-43, gemm_w4a16.cu:63-88): C[M][out_f] = A[M][in_f] W^T,
+ * any M >= 1, bf16 in/out, fp32 accumulate, dequantisation fused into the tensor-core tiles. */
+int w4a16_gemm_prefill(uint16_t* C, const w4a16_weights_t* w, const uint16_t* A, int M,
+                       w4a16_workspace_t* ws, void* stream);
+
+/* Column (output-row) sharding over the GPUs of one node. No reference
+ * counterpart (the reference is single-GPU; README.md:123). Rank r of nranks owns
+ * rows [row_begin,row_end) of an out_f-row layer; both are multiples of 16. */
+int w4a16_shard_rows(int out_f, int nranks, int rank, int* row_begin, int* row_end);
+/* Skinny GEMM on this rank's shard whose epilogue stores the [M][shard rows] slice
+ * straight into every rank's full Y[M][out_f_total] at column row_begin: the
+ * all-gather fused into the kernel over NVLink peer stores. y_peers[nranks] are
+ * device pointers to each rank's Y (peer-mapped); y_peers[rank] is the local one.
+ * Completion on the peers is ordered by the caller's next cross-rank barrier. */
+int w4a16_gemm_skinny_sharded(uint16_t* const* y_peers, int nranks, int rank, int out_f_total,
+                              int row_begin, const w4a16_weights_t* w_shard, const uint16_t* x,
+                              int M, w4a16_scratch_t* s, void* stream);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* W4A16_B200_H_ */

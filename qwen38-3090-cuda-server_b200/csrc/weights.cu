@@ -1,0 +1,272 @@
+// Weight container management for the W4A16 path: allocation, the load-time
+// repack from the checkpoint's on-disk layout into the private block layout, and
+// the row dequantiser that anchors bit-exactness on the GPU.
+//
+// Replaces awq_alloc_fused / awq_repack_into / awq_free
+// (src/kernels/gemv_w4a16.cu:308-334 of the reference project) and
+// w4a16_dequant_rows (src/kernels/gemm_w4a16.cu:15-38,56-61).
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace w4a16 {
+
+// ------------------------------------------------------------------ errors
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof g_err, fmt, ap);
+  va_end(ap);
+}
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof g_err, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+// ------------------------------------------------------------------ device info
+constexpr int kMaxDevices = 64;
+static DeviceInfo g_dev[kMaxDevices];
+static std::mutex g_dev_mu;
+
+__device__ int g_status_word = 0;
+
+const DeviceInfo* device_info() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    set_error("no current CUDA device");
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lk(g_dev_mu);
+  DeviceInfo& d = g_dev[dev];
+  if (d.device != dev) {
+    int sms = 0, smem = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) {
+      set_error("cudaDeviceGetAttribute failed");
+      return nullptr;
+    }
+    int* st = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&st), g_status_word) != cudaSuccess) {
+      set_error("cudaGetSymbolAddress(status word) failed");
+      return nullptr;
+    }
+    d.sms = sms;
+    d.smem_optin = smem;
+    d.status = st;
+    d.device = dev;
+  }
+  return &d;
+}
+
+// ------------------------------------------------------------------ kernels
+namespace {
+
+// One thread per destination uint4 (16 rows x 64 k block, lane slot).
+__global__ void k_repack_q(uint4* __restrict__ dq, const uint32_t* __restrict__ sq, int out_f,
+                           int words_per_row, int KB, int row_offset) {
+  const long long n = static_cast<long long>(out_f / kRowBlock) * KB * 32;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int lane = static_cast<int>(i & 31);
+    const long long blk = i >> 5;
+    const int kb = static_cast<int>(blk % KB);
+    const int srb = static_cast<int>(blk / KB);  // source row block
+    const int g = lane >> 2, t = lane & 3;
+    uint32_t out[4];
+#pragma unroll
+    for (int hi = 0; hi < 2; ++hi) {
+      const int srow = srb * kRowBlock + g + 8 * hi;
+      const uint32_t* src = sq + static_cast<size_t>(srow) * words_per_row + (kb * kStepK + 16 * t) / 8;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t w = src[h];
+        uint32_t o = 0;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) o |= ((w >> (4 * c)) & 0xFu) << (4 * nib_pos(c));
+        out[hi * 2 + h] = o;
+      }
+    }
+    const int drb = srb + row_offset / kRowBlock;
+    dq[(static_cast<size_t>(drb) * KB + kb) * 32 + lane] = make_uint4(out[0], out[1], out[2], out[3]);
+  }
+}
+
+__global__ void k_repack_sz(uint16_t* __restrict__ ds, uint8_t* __restrict__ dz,
+                            const uint16_t* __restrict__ ss, const uint32_t* __restrict__ sz,
+                            int out_f, int G, int row_offset) {
+  const long long n = static_cast<long long>(out_f) * G;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int g = static_cast<int>(i % G);
+    const int so = static_cast<int>(i / G);
+    const int o = so + row_offset;
+    const size_t d = (static_cast<size_t>(o / kRowBlock) * G + g) * kRowBlock + (o % kRowBlock);
+    ds[d] = ss[static_cast<size_t>(so) * G + g];
+    const uint32_t zw = sz[static_cast<size_t>(so >> 3) * G + g];
+    dz[d] = static_cast<uint8_t>((zw >> ((so & 7) * 4)) & 0xFu);
+  }
+}
+
+// One thread per (row, 16-k slot): 16 bf16 values out, 32 contiguous bytes.
+__global__ void k_dequant_rows(uint16_t* __restrict__ dst, const uint4* __restrict__ qw,
+                               const uint16_t* __restrict__ sc, const uint8_t* __restrict__ zp,
+                               int row0, int nrows, int K, int G) {
+  const int KB = K / kStepK;
+  const long long n = static_cast<long long>(nrows) * KB * 4;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(i & 3);
+    const int kb = static_cast<int>((i >> 2) % KB);
+    const int r = static_cast<int>((i >> 2) / KB);
+    const int o = row0 + r;
+    const int rb = o / kRowBlock, ro = o % kRowBlock;
+    const int lane = (ro & 7) * 4 + t;
+    const uint4 q = qw[(static_cast<size_t>(rb) * KB + kb) * 32 + lane];
+    const uint32_t w0 = (ro >> 3) ? q.z : q.x;
+    const uint32_t w1 = (ro >> 3) ? q.w : q.y;
+    const int k0 = kb * kStepK + 16 * t;
+    const int g = k0 / kGroup;
+    const size_t si = (static_cast<size_t>(rb) * G + g) * kRowBlock + ro;
+    const float s = bf16_bits_to_float(sc[si]);
+    const float z = static_cast<float>(zp[si]);
+    uint16_t v[16];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      v[c] = float_to_bf16_bits((static_cast<float>((w0 >> (4 * nib_pos(c))) & 0xFu) - z) * s);
+      v[8 + c] = float_to_bf16_bits((static_cast<float>((w1 >> (4 * nib_pos(c))) & 0xFu) - z) * s);
+    }
+    uint4* d = reinterpret_cast<uint4*>(dst + static_cast<size_t>(r) * K + k0);
+    d[0] = make_uint4(v[0] | (uint32_t(v[1]) << 16), v[2] | (uint32_t(v[3]) << 16),
+                      v[4] | (uint32_t(v[5]) << 16), v[6] | (uint32_t(v[7]) << 16));
+    d[1] = make_uint4(v[8] | (uint32_t(v[9]) << 16), v[10] | (uint32_t(v[11]) << 16),
+                      v[12] | (uint32_t(v[13]) << 16), v[14] | (uint32_t(v[15]) << 16));
+  }
+}
+
+int grid_for(long long n, int block) {
+  long long g = (n + block - 1) / block;
+  return static_cast<int>(g < 1 ? 1 : (g > 65535 * 16 ? 65535 * 16 : g));
+}
+
+}  // namespace
+
+int check_weights(const w4a16_weights_t* w) {
+  W4_REQUIRE(w != nullptr, "weights: null struct");
+  W4_REQUIRE(w->qweight && w->scale && w->zp, "weights: null buffer");
+  W4_REQUIRE(w->group_size == kGroup, "weights: group_size %d unsupported (only 128)", w->group_size);
+  W4_REQUIRE(w->out_f > 0 && w->out_f % kRowBlock == 0, "weights: out_f %d not a positive multiple of 16",
+             w->out_f);
+  W4_REQUIRE(w->in_f > 0 && w->in_f % kGroup == 0, "weights: in_f %d not a positive multiple of 128",
+             w->in_f);
+  W4_REQUIRE(w->num_groups == w->in_f / kGroup, "weights: num_groups %d != in_f/128", w->num_groups);
+  W4_REQUIRE((reinterpret_cast<uintptr_t>(w->qweight) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(w->scale) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(w->zp) & 15) == 0,
+             "weights: buffers must be 16-byte aligned");
+  return W4A16_OK;
+}
+
+}  // namespace w4a16
+
+using namespace w4a16;
+
+extern "C" {
+
+const char* w4a16_last_error(void) { return g_err; }
+
+int w4a16_device_status(void) {
+  int v = 0;
+  W4_CUDA(cudaDeviceSynchronize());
+  W4_CUDA(cudaMemcpyFromSymbol(&v, g_status_word, sizeof(int)));
+  if (v != 0) set_error("device status %d: a bounded device-side wait expired", v);
+  return v;
+}
+
+int w4a16_weights_alloc(w4a16_weights_t* w, int out_f, int in_f, int group_size, void* stream) {
+  W4_REQUIRE(w != nullptr, "weights_alloc: null struct");
+  W4_REQUIRE(group_size == kGroup, "weights_alloc: group_size %d unsupported (only 128)", group_size);
+  W4_REQUIRE(out_f > 0 && out_f % kRowBlock == 0, "weights_alloc: out_f %d not a positive multiple of 16",
+             out_f);
+  W4_REQUIRE(in_f > 0 && in_f % kGroup == 0, "weights_alloc: in_f %d not a positive multiple of 128", in_f);
+  (void)stream;
+  memset(w, 0, sizeof *w);
+  const int G = in_f / group_size;
+  const size_t qb = static_cast<size_t>(out_f) * in_f / 2;
+  const size_t sb = static_cast<size_t>(out_f) * G * 2;
+  const size_t zb = static_cast<size_t>(out_f) * G;
+  // Three independent bases: the reference's callers cudaFree them one by one
+  // (src/model/model.cu:111,204).
+  void *q = nullptr, *s = nullptr, *z = nullptr;
+  cudaError_t e = cudaMalloc(&q, qb);
+  if (e == cudaSuccess) e = cudaMalloc(&s, sb);
+  if (e == cudaSuccess) e = cudaMalloc(&z, zb);
+  if (e != cudaSuccess) {
+    cudaFree(q);
+    cudaFree(s);
+    cudaFree(z);
+    return fail(W4A16_ECUDA, "weights_alloc(%d x %d): %s", out_f, in_f, cudaGetErrorString(e));
+  }
+  w->qweight = static_cast<uint32_t*>(q);
+  w->scale = static_cast<uint16_t*>(s);
+  w->zp = static_cast<uint8_t*>(z);
+  w->out_f = out_f;
+  w->in_f = in_f;
+  w->group_size = group_size;
+  w->num_groups = G;
+  return W4A16_OK;
+}
+
+int w4a16_repack_into(const w4a16_weights_t* w, int dst_row_offset, const uint32_t* packed,
+                      const uint16_t* scale, const uint32_t* zp, int out_f, void* stream) {
+  if (int rc = check_weights(w)) return rc;
+  W4_REQUIRE(packed && scale && zp, "repack_into: null source tensor");
+  W4_REQUIRE(out_f > 0 && out_f % kRowBlock == 0, "repack_into: out_f %d not a positive multiple of 16",
+             out_f);
+  W4_REQUIRE(dst_row_offset >= 0 && dst_row_offset % kRowBlock == 0,
+             "repack_into: row offset %d not a multiple of 16", dst_row_offset);
+  W4_REQUIRE(dst_row_offset + out_f <= w->out_f, "repack_into: rows [%d,%d) exceed out_f %d",
+             dst_row_offset, dst_row_offset + out_f, w->out_f);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int KB = w->in_f / kStepK;
+  const long long nq = static_cast<long long>(out_f / kRowBlock) * KB * 32;
+  k_repack_q<<<grid_for(nq, 256), 256, 0, st>>>(reinterpret_cast<uint4*>(w->qweight), packed, out_f,
+                                                w->in_f / 8, KB, dst_row_offset);
+  const long long ns = static_cast<long long>(out_f) * w->num_groups;
+  k_repack_sz<<<grid_for(ns, 256), 256, 0, st>>>(w->scale, w->zp, scale, zp, out_f, w->num_groups,
+                                                 dst_row_offset);
+  W4_CUDA(cudaGetLastError());
+  return W4A16_OK;
+}
+
+int w4a16_weights_free(w4a16_weights_t* w) {
+  W4_REQUIRE(w != nullptr, "weights_free: null struct");
+  cudaFree(w->qweight);
+  cudaFree(w->scale);
+  cudaFree(w->zp);
+  memset(w, 0, sizeof *w);
+  return W4A16_OK;
+}
+
+int w4a16_dequant_rows(uint16_t* dst, const w4a16_weights_t* w, int row0, int nrows, void* stream) {
+  if (int rc = check_weights(w)) return rc;
+  W4_REQUIRE(dst != nullptr && (reinterpret_cast<uintptr_t>(dst) & 15) == 0,
+             "dequant_rows: dst null or not 16-byte aligned");
+  W4_REQUIRE(row0 >= 0 && nrows >= 0 && row0 + nrows <= w->out_f, "dequant_rows: rows [%d,%d) outside [0,%d)",
+             row0, row0 + nrows, w->out_f);
+  if (nrows == 0) return W4A16_OK;
+  const long long n = static_cast<long long>(nrows) * (w->in_f / kStepK) * 4;
+  k_dequant_rows<<<grid_for(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      dst, reinterpret_cast<const uint4*>(w->qweight), w->scale, w->zp, row0, nrows, w->in_f,
+      w->num_groups);
+  W4_CUDA(cudaGetLastError());
+  return W4A16_OK;
+}
+
+}  // extern "C"
