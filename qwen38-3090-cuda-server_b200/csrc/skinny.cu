@@ -6,22 +6,23 @@
 // and k_gemm_mma of the reference (src/kernels/gemv_w4a16.cu:74-279,673-865) and,
 // for lm_head, the separate argmax kernels (src/kernels/elementwise.cu:96-194).
 //
-// Shape of the computation (HBM-bound: every packed weight byte is read once):
-//   * grid = one CTA per SM; the (row tile, k group) units of the whole matrix are
-//     dealt out as equal contiguous ranges, so every SM streams the same number of
-//     bytes whatever N and K are. A row tile whose K range is shared by several
-//     CTAs is finished by the last CTA to arrive, which adds the partial tiles in a
-//     fixed order (bitwise reproducible, no float atomics).
-//   * each warp owns 16 output rows and streams their packed int4 blocks, scales
-//     and zero points through a private ring of shared-memory stages filled by 1-D
-//     bulk async copies (cp.async.bulk + mbarrier); the ring is primed before the
-//     kernel waits on its predecessor (programmatic dependent launch), so the
-//     weight stream of one layer starts while the previous layer drains.
-//   * activations are staged per 1024-k chunk with cp.async directly in MMA
-//     fragment order; nibbles are turned into bf16 (128+q) pairs with one LOP3 per
-//     two weights and fed from registers to mma.sync m16n8k16 (bf16 x bf16 -> fp32).
-//     Per group:  y += s * (sum((128+q) x) - (128+zp) * sum(x)),  sum(x) coming from
-//     one more MMA against a tile of ones.
+// Shape of the computation (HBM-bound: every weight byte is read exactly once):
+//   * persistent grid (a multiple of the SM count). The (row tile, k group) units of
+//     the matrix are dealt out as equal contiguous ranges, so every CTA streams the
+//     same number of bytes whatever N and K are. A row tile whose K range is shared by
+//     several CTAs is finished by the last CTA to arrive, which adds the partial tiles
+//     in a fixed order (bitwise reproducible, no float atomics).
+//   * weights arrive as one contiguous stream per 16-row block (int4 blocks, scales
+//     and zero points interleaved). A producer warp keeps a private ring of
+//     shared-memory stages full for each consumer warp with 1-D bulk async copies
+//     (cp.async.bulk + mbarrier full/empty pairs). The producer does not wait for the
+//     previous kernel (programmatic dependent launch), so one layer's weight stream
+//     starts while the previous layer drains.
+//   * activations are staged per k chunk with cp.async in MMA-fragment order. Nibbles
+//     become bf16 (128+q) pairs with one LOP3 per two weights, the zero point is
+//     removed exactly with one packed bf16 subtract ((128+q) - (128+zp) = q - zp), and
+//     the pairs go from registers into mma.sync m16n8k16 (bf16 x bf16 -> fp32); the
+//     group scale multiplies the fp32 group sum:  y += s * sum((q - zp) x).
 #include <cfloat>
 #include <climits>
 #include <cstdlib>
@@ -32,29 +33,31 @@
 namespace w4a16 {
 namespace {
 
-constexpr int kChunkGroups = 8;                       // k groups per activation chunk (1024 k)
-constexpr int kChunkSteps = kChunkGroups * 2;         // 64-k steps per chunk
-constexpr int kItemGroups = 2;                        // k groups per ring stage
-constexpr int kItemQ = kItemGroups * 2 * kStepBytes;  // 2048 B of packed weights
-constexpr int kItemS = kItemGroups * 32;              // 16 bf16 scales per group
-constexpr int kItemZ = kItemGroups * 16;              // 16 u8 zero points per group
-constexpr int kItemStride = 2176;                     // 2048 + 64 + 32, padded to 128
-static_assert(kItemQ + kItemS + kItemZ <= kItemStride, "ring stage too small");
+constexpr int CW = kTileBlocks;                       // consumer warps per CTA: one per 16-row block
+constexpr int kWarps = CW + 2;                        // + weight producer warp + activation warp
+constexpr int kItemGroups = 2;                        // k groups per weight ring stage
+constexpr int kStageBytes = kItemGroups * kTileGroupBytes;  // 17152: [group][warp][unit]
+static_assert(kStageBytes % 128 == 0, "ring stages must stay 128-byte aligned");
+constexpr int kXBufs = 3;                             // activation chunk buffers
+constexpr int kFirstChunk = 2;                        // groups in a CTA's first activation chunk (short start-up)
+constexpr int kMaxChunkGroups = 32;                   // bound on groups per activation chunk
 constexpr uint32_t kSpinLimit = 1u << 20;             // polls before a wait gives up
 constexpr uint32_t kMagic = 0x43004300u;              // bf16 pair (128.0, 128.0)
 constexpr uint32_t kNibMask = 0x000F000Fu;
 constexpr uint32_t kOnes = 0x3F803F80u;               // bf16 pair (1.0, 1.0)
+constexpr int kConsumerBar = 1;                       // named barrier of the consumer warps
 
 struct SkinnyParams {
-  const uint4* qw;
-  const uint16_t* sc;
-  const uint8_t* zp;
-  const uint16_t* x;  // [M][K] bf16
-  void* y;            // bf16 or fp32 [M][ldy], may be null in argmax mode
+  const uint8_t* stream;  // weight stream, kTileGroupBytes per (row tile, group)
+  const uint16_t* x;      // [M][K] bf16
+  void* y;                // bf16 or fp32 [M][ldy], may be null in argmax mode
   int y_f32;
   long long ldy;  // elements between rows of y
   int y_col0;     // first column of this launch's rows inside y
   int M, N, K, G, NRB, tiles;
+  int chunk_groups;  // k groups per activation chunk (even)
+  int xrow_bytes;    // bytes between token rows inside an activation buffer
+  int xbuf_bytes;    // bytes of one activation buffer
   float* partial;
   unsigned* counters;  // [tiles + 1], zero between launches
   int argmax;
@@ -63,6 +66,8 @@ struct SkinnyParams {
   int row_offset;
   void* cta_pairs;  // [grid][16] x {float,int}
   int* status;
+  unsigned long long* dbg;  // TEMP: per-CTA timestamps
+  int debug_skip;  // TEMP: 1 = consumers skip the math, 2 = producer skips the copies
   int npeers;  // extra destinations for y (fused all-gather), 0 = none
   uint16_t* y_peers[8];
 };
@@ -76,104 +81,273 @@ __device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
   return v > bv || (v == bv && i < bi);
 }
 
-template <int NT>
-__host__ __device__ constexpr int xbuf_bytes() {
-  return kChunkSteps * NT * 1024;
+// ---- the order in which a CTA walks its unit range [u0,u1) -------------------------------
+// Row tiles that this CTA shares with a neighbour come first (the piece at the end of the
+// range, then the piece at its start), whole tiles after, so the cross-CTA reduction of the
+// shared tiles overlaps everybody's main loop instead of sitting at the end of the kernel.
+// Every role (weight producer, activation warp, consumers) runs the same iterator.
+struct Chunk {
+  int tile, g, n;      // row tile, first group, number of groups (<= chunk_groups)
+  int seg_g0, seg_g1;  // the segment this chunk belongs to: groups [seg_g0, seg_g1) of `tile`
+  bool seg_last;       // last chunk of its segment
+};
+
+struct WorkIter {
+  int G, CG, t_first, t_last, head_g0, tail_g1;
+  bool single, head_partial, tail_partial, first;
+  int phase, t;
+  int s_tile, s_g0, s_g1, g;  // current segment and cursor
+  bool have;
+
+  __device__ void init(int u0, int u1, int G_, int CG_) {
+    G = G_;
+    CG = CG_;
+    t_first = u0 / G;
+    t_last = (u1 - 1) / G;
+    head_g0 = u0 - t_first * G;
+    tail_g1 = u1 - t_last * G;
+    single = (t_first == t_last);
+    head_partial = single ? !(head_g0 == 0 && tail_g1 == G) : (head_g0 != 0);
+    tail_partial = single ? false : (tail_g1 != G);
+    phase = 0;
+    t = t_first;
+    have = false;
+    first = true;
+    s_tile = s_g0 = s_g1 = g = 0;
+  }
+  __device__ bool next_segment() {
+    if (phase == 0) {
+      phase = 1;
+      if (tail_partial) {
+        s_tile = t_last; s_g0 = 0; s_g1 = tail_g1;
+        return true;
+      }
+    }
+    if (phase == 1) {
+      phase = 2;
+      if (head_partial) {
+        s_tile = t_first; s_g0 = head_g0; s_g1 = single ? tail_g1 : G;
+        return true;
+      }
+    }
+    while (t <= t_last) {
+      const int tt = t++;
+      if (tt == t_first && head_partial) continue;
+      if (tt == t_last && tail_partial) continue;
+      s_tile = tt; s_g0 = 0; s_g1 = G;
+      return true;
+    }
+    return false;
+  }
+  __device__ bool next(Chunk& c) {
+    if (!have || g >= s_g1) {
+      if (!next_segment()) return false;
+      have = true;
+      g = s_g0;
+    }
+    int n = first ? kFirstChunk : CG;
+    first = false;
+    if (s_g1 - g < n) n = s_g1 - g;
+    c.tile = s_tile; c.g = g; c.n = n; c.seg_g0 = s_g0; c.seg_g1 = s_g1;
+    g += n;
+    c.seg_last = (g == s_g1);
+    return true;
+  }
+};
+
+// x >> s on the FMA pipe (integer multiply-high), to keep the half-rate ALU pipe for the LOP3s
+template <int S>
+__device__ __forceinline__ uint32_t shr_fma(uint32_t x) {
+#ifdef W4A16_SHIFT_ALU
+  return x >> S;
+#else
+  uint32_t d;
+  asm("mul.hi.u32 %0, %1, %2;" : "=r"(d) : "r"(x), "r"(1u << (32 - S)));
+  return d;
+#endif
 }
 
-template <int NT, int WARPS, int D>
-constexpr int skinny_smem_bytes() {
-  return WARPS * D * kItemStride + 2 * xbuf_bytes<NT>() + 2 * kChunkGroups * 8 * NT * 4 + WARPS * D * 8 + 16;
+// dynamic shared memory:
+//   [weight ring D stages][x buffers kXBufs][x sums kXBufs x 32 groups x 16][32 B zeros][mbarriers][flag]
+constexpr int kXsumFloats = kMaxChunkGroups * 16;
+template <int D>
+__host__ __device__ constexpr int skinny_fixed_smem() {
+  return D * kStageBytes + kXBufs * kXsumFloats * 4 + 32 + (2 * D + 3 * kXBufs) * 8 + 16;
 }
 
-template <int NT, int WARPS, int D>
-__global__ void __launch_bounds__(WARPS * 32, 1) k_skinny(const SkinnyParams p) {
-  static_assert(WARPS >= kChunkGroups, "one warp per group computes the activation sums");
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define DBG_T(i) do { if (p.dbg && tid == 0) p.dbg[blockIdx.x * 8 + (i)] = gtime(); } while (0)
+
+template <int NT, int D>
+__global__ void __launch_bounds__(kWarps * 32, 2) k_skinny(const SkinnyParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  constexpr int XBUF = xbuf_bytes<NT>();
-  constexpr int TILE_ROWS = WARPS * 16;
-  constexpr int SLOT = TILE_ROWS * 8 * NT;  // floats per partial tile
+  constexpr int SLOT = CW * 16 * 8 * NT;  // floats per partial tile
+  constexpr int NCT = CW * 32;            // consumer threads
 
   uint8_t* ring = smem;
-  uint8_t* xbuf = ring + WARPS * D * kItemStride;
-  float* xsum = reinterpret_cast<float*>(xbuf + 2 * XBUF);  // [2][8][8*NT]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(xsum + 2 * kChunkGroups * 8 * NT);
-  int* sflag = reinterpret_cast<int*>(bars + WARPS * D);
+  uint8_t* xbuf = ring + D * kStageBytes;
+  float* xsum = reinterpret_cast<float*>(xbuf + kXBufs * p.xbuf_bytes);
+  uint8_t* zeros = reinterpret_cast<uint8_t*>(xsum + kXBufs * kXsumFloats);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(zeros + 32);
+  int* sflag = reinterpret_cast<int*>(bars + 2 * D + 3 * kXBufs);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int grow = lane >> 2, t = lane & 3;
-  const int G = p.G, KB = p.K / kStepK;
-  const long long U = static_cast<long long>(p.tiles) * G;
-  const long long u0 = U * blockIdx.x / gridDim.x;
-  const long long u1 = U * (blockIdx.x + 1) / gridDim.x;
+  const int G = p.G, M = p.M;
+  const int U = p.tiles * G;
+  const int u0 = static_cast<int>(static_cast<long long>(U) * blockIdx.x / gridDim.x);
+  const int u1 = static_cast<int>(static_cast<long long>(U) * (blockIdx.x + 1) / gridDim.x);
 
-  const uint32_t ring_w = smem_u32(ring) + warp * D * kItemStride;
-  const uint32_t bars_w = smem_u32(bars) + warp * D * 8;
+  const uint32_t ring_a = smem_u32(ring);
   const uint32_t xbuf_a = smem_u32(xbuf);
+  const uint32_t wfull_a = smem_u32(bars);        // [D]  weights landed
+  const uint32_t wempty_a = wfull_a + D * 8;      // [D]  stage free again (8 consumer warps)
+  const uint32_t xfull_a = wempty_a + D * 8;      // [kXBufs] activation chunk landed
+  const uint32_t xsfull_a = xfull_a + kXBufs * 8; // [kXBufs] its per-group sums are ready
+  const uint32_t xempty_a = xsfull_a + kXBufs * 8;// [kXBufs] buffer free again (8 consumers + activation warp)
 
-  // ---- prologue: nothing here depends on the previous kernel's output ----
-  for (int i = tid; i < 2 * XBUF / 16; i += WARPS * 32) reinterpret_cast<uint4*>(xbuf)[i] = make_uint4(0, 0, 0, 0);
-  if (lane == 0) {
-    for (int s = 0; s < D; ++s) mbar_init(bars_w + s * 8, 1);
+  DBG_T(0);
+  if (tid < 8) reinterpret_cast<uint32_t*>(zeros)[tid] = 0u;
+  if (tid == 0) {
+    for (int i = 0; i < D; ++i) {
+      mbar_init(wfull_a + i * 8, 1);
+      mbar_init(wempty_a + i * 8, CW);
+    }
+    for (int i = 0; i < kXBufs; ++i) {
+      mbar_init(xfull_a + i * 8, 1);
+      mbar_init(xsfull_a + i * 8, 1);
+      mbar_init(xempty_a + i * 8, CW + 1);
+    }
     fence_mbar_init();
   }
   __syncthreads();
-
-  // Producer cursor (meaningful in lane 0 only): next unit to fetch, next stage to fill.
-  long long pu = u0;
-  int pstage = 0;
-  auto issue_next = [&]() {
-    while (pu < u1) {
-      const int tile = static_cast<int>(pu / G);
-      const int g = static_cast<int>(pu - static_cast<long long>(tile) * G);
-      int ng = kItemGroups;
-      if (G - g < ng) ng = G - g;
-      if (u1 - pu < ng) ng = static_cast<int>(u1 - pu);
-      pu += ng;
-      const int rb = tile * WARPS + warp;
-      if (rb >= p.NRB) continue;  // rows past the end of the matrix: this warp has no item
-      const uint32_t bar = bars_w + pstage * 8;
-      const uint32_t dst = ring_w + pstage * kItemStride;
-      mbar_expect_tx(bar, ng * (2 * kStepBytes + 32 + 16));
-      bulk_g2s(dst, p.qw + (static_cast<size_t>(rb) * KB + g * 2) * 32, ng * 2 * kStepBytes, bar);
-      bulk_g2s(dst + kItemQ, p.sc + (static_cast<size_t>(rb) * G + g) * 16, ng * 32, bar);
-      bulk_g2s(dst + kItemQ + kItemS, p.zp + (static_cast<size_t>(rb) * G + g) * 16, ng * 16, bar);
-      pstage = (pstage + 1 == D) ? 0 : pstage + 1;
-      return;
-    }
-  };
-  if (lane == 0)
-    for (int s = 0; s < D; ++s) issue_next();
-
   pdl_launch_dependents();
-  pdl_wait();  // activations (and the scratch this kernel shares) are now safe to touch
 
-  // Stage the activation chunk that starts at unit `u` into buffer `buf`, in
-  // fragment order: slot (step, nt, h, lane) holds x[8nt + lane/4][k0 + 64 step + 16 (lane%4) + 8h .. +8).
-  auto stage_x = [&](long long u, int buf) {
-    const int tile = static_cast<int>(u / G);
-    const int g0 = static_cast<int>(u - static_cast<long long>(tile) * G);
-    int ngc = kChunkGroups;
-    if (G - g0 < ngc) ngc = G - g0;
-    if (u1 - u < ngc) ngc = static_cast<int>(u1 - u);
-    const int nslots = ngc * 2 * NT * 64;
-    for (int i = tid; i < nslots; i += WARPS * 32) {
-      const int l = i & 31, h = (i >> 5) & 1, nt = (i >> 6) % NT, step = i / (64 * NT);
-      const int n = nt * 8 + (l >> 2);
-      if (n < p.M)
-        cp_async16(xbuf_a + buf * XBUF + ((step * NT + nt) * 2 + h) * 512 + l * 16,
-                   p.x + static_cast<size_t>(n) * p.K + g0 * kGroup + step * kStepK + 16 * (l & 3) + 8 * h);
+  // B-fragment addressing of a lane: token row 8 nt + lane/4, k offset 16 (lane%4) within a
+  // 64-k step. Lanes whose token row does not exist read a block of zeros (all strides 0).
+  const int grow = lane >> 2, t = lane & 3;
+  uint32_t xlane[NT], xstep[NT], xbufoff[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const int mm = nt * 8 + grow;
+    const bool valid = mm < M;
+    xlane[nt] = valid ? xbuf_a + mm * p.xrow_bytes + t * 32 : smem_u32(zeros);
+    xstep[nt] = valid ? 128 : 0;
+    xbufoff[nt] = valid ? p.xbuf_bytes : 0;
+  }
+
+  // ================================================================ weight producer
+  // One thread streams this CTA's share of the weight stream, one stage (two k groups of all
+  // eight 16-row blocks, 17 KB, contiguous in memory) per bulk copy. It does not wait for the
+  // previous kernel: weights never depend on it.
+  if (warp == CW) {
+    if (lane == 0) {
+      WorkIter it;
+      it.init(u0, u1, G, p.chunk_groups);
+      Chunk c;
+      int st = 0;
+      uint32_t ph = 1;  // a fresh "empty" barrier reads as already released
+      bool ok = true;
+      while (ok && it.next(c)) {
+        for (int gi = 0; gi < c.n; gi += kItemGroups) {
+          const int ng = (c.n - gi < kItemGroups) ? c.n - gi : kItemGroups;
+          if (!mbar_wait_bounded(wempty_a + st * 8, ph, kSpinLimit)) {
+            atomicExch(p.status, W4A16_ETIMEOUT);
+            ok = false;
+            break;
+          }
+          if (p.debug_skip == 2) {
+            mbar_arrive(wfull_a + st * 8);
+          } else {
+            mbar_expect_tx(wfull_a + st * 8, ng * kTileGroupBytes);
+            bulk_g2s(ring_a + st * kStageBytes,
+                     p.stream + (static_cast<size_t>(c.tile) * G + c.g + gi) * kTileGroupBytes,
+                     ng * kTileGroupBytes, wfull_a + st * 8);
+          }
+          if (++st == D) {
+            st = 0;
+            ph ^= 1;
+          }
+        }
+      }
     }
-    cp_async_commit();
-  };
+    return;
+  }
+
+  // ================================================================ activation warp
+  // Waits for the previous kernel (it produced x), then per chunk: bulk-copies the token rows,
+  // and turns them into per-(group, token) sums with the tensor core (ones(16x16) * X).
+  if (warp == CW + 1) {
+    pdl_wait();
+    WorkIter it;
+    it.init(u0, u1, G, p.chunk_groups);
+    Chunk c;
+    int xb = 0;
+    uint32_t fph = 0, eph = 1;
+    while (it.next(c)) {
+      if (!mbar_wait_bounded(xempty_a + xb * 8, eph, kSpinLimit)) {
+        atomicExch(p.status, W4A16_ETIMEOUT);
+        break;
+      }
+      if (lane == 0) {
+        mbar_expect_tx(xfull_a + xb * 8, M * c.n * 256);
+        for (int m = 0; m < M; ++m)
+          bulk_g2s(xbuf_a + xb * p.xbuf_bytes + m * p.xrow_bytes,
+                   p.x + static_cast<size_t>(m) * p.K + c.g * kGroup, c.n * 256, xfull_a + xb * 8);
+      }
+      if (!mbar_wait_bounded(xfull_a + xb * 8, fph, kSpinLimit)) {
+        atomicExch(p.status, W4A16_ETIMEOUT);
+        break;
+      }
+      for (int gl = 0; gl < c.n; ++gl) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          float ax[4][4];
+          const uint8_t* xa = smem + (xlane[nt] - ring_a) + xb * xbufoff[nt] + gl * 2 * xstep[nt];
+          const uint4 b0 = *reinterpret_cast<const uint4*>(xa);
+          const uint4 b1 = *reinterpret_cast<const uint4*>(xa + 16);
+          const uint4 b2 = *reinterpret_cast<const uint4*>(xa + xstep[nt]);
+          const uint4 b3 = *reinterpret_cast<const uint4*>(xa + xstep[nt] + 16);
+          mma_bf16_16816_zero(ax[0], kOnes, kOnes, kOnes, kOnes, b0.x, b0.y);
+          mma_bf16_16816_zero(ax[1], kOnes, kOnes, kOnes, kOnes, b1.x, b1.y);
+          mma_bf16_16816_zero(ax[2], kOnes, kOnes, kOnes, kOnes, b2.x, b2.y);
+          mma_bf16_16816_zero(ax[3], kOnes, kOnes, kOnes, kOnes, b3.x, b3.y);
+          mma_bf16_16816(ax[0], kOnes, kOnes, kOnes, kOnes, b0.z, b0.w);
+          mma_bf16_16816(ax[1], kOnes, kOnes, kOnes, kOnes, b1.z, b1.w);
+          mma_bf16_16816(ax[2], kOnes, kOnes, kOnes, kOnes, b2.z, b2.w);
+          mma_bf16_16816(ax[3], kOnes, kOnes, kOnes, kOnes, b3.z, b3.w);
+          if (grow == 0) {
+            float* xs = xsum + xb * kXsumFloats + gl * 16 + nt * 8 + 2 * t;
+            xs[0] = (ax[0][0] + ax[1][0]) + (ax[2][0] + ax[3][0]);
+            xs[1] = (ax[0][1] + ax[1][1]) + (ax[2][1] + ax[3][1]);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(xsfull_a + xb * 8);  // sums published
+        mbar_arrive(xempty_a + xb * 8);  // this warp no longer reads the chunk
+      }
+      if (++xb == kXBufs) {
+        xb = 0;
+        fph ^= 1;
+        eph ^= 1;
+      }
+    }
+    return;
+  }
+
+  // ================================================================ consumer warps
+  pdl_wait();  // outputs and the shared scratch are safe to touch from here on
+  DBG_T(1);
 
   float fin[NT][4];
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) fin[nt][j] = 0.f;
+  for (int nt = 0; nt < NT; ++nt) fin[nt][0] = fin[nt][1] = fin[nt][2] = fin[nt][3] = 0.f;
 
-  // running argmax candidates of this thread: [nt][column parity]
   float best_v[NT][2];
   int best_i[NT][2];
 #pragma unroll
@@ -186,7 +360,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_skinny(const SkinnyParams p) 
 
   // Final values of one row tile are in registers: write them out / fold into the argmax.
   auto finalize = [&](int tile, const float (&v)[NT][4]) {
-    const int rb = tile * WARPS + warp;
+    const int rb = tile * CW + warp;
     if (rb >= p.NRB) return;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
@@ -194,7 +368,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_skinny(const SkinnyParams p) 
       for (int j = 0; j < 4; ++j) {
         const int m = nt * 8 + 2 * t + (j & 1);
         const int r = rb * 16 + grow + 8 * (j >> 1);
-        if (m >= p.M) continue;
+        if (m >= M) continue;
         const uint16_t hb = float_to_bf16_bits(v[nt][j]);
         if (p.y) {
           const size_t o = static_cast<size_t>(m) * p.ldy + p.y_col0 + r;
@@ -212,163 +386,181 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_skinny(const SkinnyParams p) 
       }
   };
 
-  int cb = 0, cstage = 0;
-  uint32_t cphase = 0;
+  // The 8 MMAs per token tile of one 128-k group of this warp's 16 rows, on bf16 (128+q) pairs.
+  auto group_mma = [&](const uint8_t* up, const uint8_t* const (&xp)[NT], float (&acc)[NT][2][4]) {
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const uint4 wq = *reinterpret_cast<const uint4*>(up + s * kStepBytes + lane * 16);
+      uint32_t a[4][4];  // [mma][register]: rows (lo, hi, lo, hi) x k pairs
+#ifdef EXP_NOUNPACK
+      a[0][0] = wq.x; a[0][1] = wq.y; a[0][2] = wq.z; a[0][3] = wq.w;
+      a[1][0] = wq.y; a[1][1] = wq.x; a[1][2] = wq.w; a[1][3] = wq.z;
+      a[2][0] = wq.z; a[2][1] = wq.w; a[2][2] = wq.x; a[2][3] = wq.y;
+      a[3][0] = wq.w; a[3][1] = wq.z; a[3][2] = wq.y; a[3][3] = wq.x;
+#else
+      a[0][0] = (wq.x & kNibMask) | kMagic;
+      a[0][1] = (wq.z & kNibMask) | kMagic;
+      a[0][2] = (shr_fma<4>(wq.x) & kNibMask) | kMagic;
+      a[0][3] = (shr_fma<4>(wq.z) & kNibMask) | kMagic;
+      a[1][0] = (shr_fma<8>(wq.x) & kNibMask) | kMagic;
+      a[1][1] = (shr_fma<8>(wq.z) & kNibMask) | kMagic;
+      a[1][2] = (shr_fma<12>(wq.x) & kNibMask) | kMagic;
+      a[1][3] = (shr_fma<12>(wq.z) & kNibMask) | kMagic;
+      a[2][0] = (wq.y & kNibMask) | kMagic;
+      a[2][1] = (wq.w & kNibMask) | kMagic;
+      a[2][2] = (shr_fma<4>(wq.y) & kNibMask) | kMagic;
+      a[2][3] = (shr_fma<4>(wq.w) & kNibMask) | kMagic;
+      a[3][0] = (shr_fma<8>(wq.y) & kNibMask) | kMagic;
+      a[3][1] = (shr_fma<8>(wq.w) & kNibMask) | kMagic;
+      a[3][2] = (shr_fma<12>(wq.y) & kNibMask) | kMagic;
+      a[3][3] = (shr_fma<12>(wq.w) & kNibMask) | kMagic;
+#endif
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const uint4 bl = *reinterpret_cast<const uint4*>(xp[nt] + s * xstep[nt]);
+        const uint4 bh = *reinterpret_cast<const uint4*>(xp[nt] + s * xstep[nt] + 16);
+#ifdef EXP_NOMMA
+        {  // keep every operand alive without issuing the MMAs
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            asm volatile("" ::"r"(a[j][0]), "r"(a[j][1]), "r"(a[j][2]), "r"(a[j][3]));
+          asm volatile("" ::"r"(bl.x), "r"(bl.y), "r"(bl.z), "r"(bl.w), "r"(bh.x), "r"(bh.y), "r"(bh.z), "r"(bh.w));
+          if (s == 0) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) acc[nt][0][q] = acc[nt][1][q] = 0.f;
+          }
+          continue;
+        }
+#endif
+        if (s == 0) {
+          mma_bf16_16816_zero(acc[nt][0], a[0][0], a[0][1], a[0][2], a[0][3], bl.x, bl.y);
+          mma_bf16_16816_zero(acc[nt][1], a[1][0], a[1][1], a[1][2], a[1][3], bl.z, bl.w);
+        } else {
+          mma_bf16_16816(acc[nt][0], a[0][0], a[0][1], a[0][2], a[0][3], bl.x, bl.y);
+          mma_bf16_16816(acc[nt][1], a[1][0], a[1][1], a[1][2], a[1][3], bl.z, bl.w);
+        }
+        mma_bf16_16816(acc[nt][0], a[2][0], a[2][1], a[2][2], a[2][3], bh.x, bh.y);
+        mma_bf16_16816(acc[nt][1], a[3][0], a[3][1], a[3][2], a[3][3], bh.z, bh.w);
+      }
+    }
+  };
+  // y += s * (acc - (128 + zp) * sum(x)) for the lane's two rows
+  auto group_fix = [&](const uint8_t* up, const float* xs, const float (&acc)[NT][2][4]) {
+    const uint32_t sp = *reinterpret_cast<const uint32_t*>(up + kUnitScaleOff + grow * 4);
+    const uint32_t zz = *reinterpret_cast<const uint16_t*>(up + kUnitZpOff + grow * 2);
+    const float s_lo = __uint_as_float(sp << 16), s_hi = __uint_as_float(sp & 0xFFFF0000u);
+    const float z_lo = __uint_as_float(__byte_perm(zz, 0x43000000u, 0x7044));  // 128 + zp, low row
+    const float z_hi = __uint_as_float(__byte_perm(zz, 0x43000000u, 0x7144));  // high row
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const float2 x2 = *reinterpret_cast<const float2*>(xs + nt * 8 + 2 * t);
+      fin[nt][0] = fmaf(s_lo, fmaf(-z_lo, x2.x, acc[nt][0][0] + acc[nt][1][0]), fin[nt][0]);
+      fin[nt][1] = fmaf(s_lo, fmaf(-z_lo, x2.y, acc[nt][0][1] + acc[nt][1][1]), fin[nt][1]);
+      fin[nt][2] = fmaf(s_hi, fmaf(-z_hi, x2.x, acc[nt][0][2] + acc[nt][1][2]), fin[nt][2]);
+      fin[nt][3] = fmaf(s_hi, fmaf(-z_hi, x2.y, acc[nt][0][3] + acc[nt][1][3]), fin[nt][3]);
+    }
+  };
+
+  WorkIter it;
+  it.init(u0, u1, G, p.chunk_groups);
+  Chunk c;
+  int wst = 0, xb = 0;
+  uint32_t wph = 0, xph = 0;
   bool dead = false;
-  long long u = u0;
-  int seg_begin = static_cast<int>(u0 % G);
-  if (u < u1) stage_x(u, 0);
+  bool first_chunk = true;
 
-  while (u < u1) {
-    const int tile = static_cast<int>(u / G);
-    const int g0 = static_cast<int>(u - static_cast<long long>(tile) * G);
-    int ngc = kChunkGroups;
-    if (G - g0 < ngc) ngc = G - g0;
-    if (u1 - u < ngc) ngc = static_cast<int>(u1 - u);
+  while (it.next(c)) {
+    // ---- one activation chunk: groups [c.g, c.g + c.n) of row tile c.tile ----
+    if (!dead && !mbar_wait_bounded(xfull_a + xb * 8, xph, kSpinLimit)) {
+      dead = true;
+      atomicExch(p.status, W4A16_ETIMEOUT);
+    }
+    if (first_chunk) DBG_T(2);
+    first_chunk = false;
+    const uint8_t* xchunk[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) xchunk[nt] = smem + (xlane[nt] - ring_a) + xb * xbufoff[nt];
+    const float* xs = xsum + xb * kXsumFloats;
+    bool sums_ready = false;
 
-    cp_async_wait_all();
-    __syncthreads();  // chunk `cb` is complete; everyone is done with the other buffer
-    const long long un = u + ngc;
-    if (un < u1) stage_x(un, cb ^ 1);
-
-    // Activation sums per (group, token) through the tensor core: ones(16x16) * X.
-    if (warp < ngc) {
-      float ax[NT][4];
+    for (int gi = 0; gi < c.n; gi += kItemGroups) {
+      if (!dead && !mbar_wait_bounded(wfull_a + wst * 8, wph, kSpinLimit)) {
+        dead = true;
+        atomicExch(p.status, W4A16_ETIMEOUT);
+      }
+      const uint8_t* up = ring + wst * kStageBytes + warp * kUnitBytes;
+      if (p.debug_skip != 1) {
+        float acc0[NT][2][4], acc1[NT][2][4];
+        const uint8_t* xp[NT];
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) ax[nt][0] = ax[nt][1] = ax[nt][2] = ax[nt][3] = 0.f;
+        for (int nt = 0; nt < NT; ++nt) xp[nt] = xchunk[nt] + gi * 2 * xstep[nt];
+        const bool two = gi + 1 < c.n;
+        group_mma(up, xp, acc0);
+        if (two) {
 #pragma unroll
-      for (int s = 0; s < 2; ++s)
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          const uint32_t xa = xbuf_a + cb * XBUF + (((warp * 2 + s) * NT + nt) * 2) * 512 + lane * 16;
-          const uint4 bl = lds128(xa), bh = lds128(xa + 512);
-          mma_bf16_16816(ax[nt], kOnes, kOnes, kOnes, kOnes, bl.x, bl.y);
-          mma_bf16_16816(ax[nt], kOnes, kOnes, kOnes, kOnes, bl.z, bl.w);
-          mma_bf16_16816(ax[nt], kOnes, kOnes, kOnes, kOnes, bh.x, bh.y);
-          mma_bf16_16816(ax[nt], kOnes, kOnes, kOnes, kOnes, bh.z, bh.w);
+          for (int nt = 0; nt < NT; ++nt) xp[nt] += 2 * xstep[nt];
+          group_mma(up + kTileGroupBytes, xp, acc1);
         }
-      if (grow == 0) {
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          float* xs = xsum + (cb * kChunkGroups + warp) * 8 * NT + nt * 8 + 2 * t;
-          xs[0] = ax[nt][0];
-          xs[1] = ax[nt][1];
+        if (!sums_ready) {
+          if (!dead && !mbar_wait_bounded(xsfull_a + xb * 8, xph, kSpinLimit)) {
+            dead = true;
+            atomicExch(p.status, W4A16_ETIMEOUT);
+          }
+          sums_ready = true;
         }
+        group_fix(up, xs + gi * 16, acc0);
+        if (two) group_fix(up + kTileGroupBytes, xs + (gi + 1) * 16, acc1);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(wempty_a + wst * 8);  // this warp is done with the stage
+      if (++wst == D) {
+        wst = 0;
+        wph ^= 1;
       }
     }
-    __syncthreads();
-
-    const int rb = tile * WARPS + warp;
-    if (rb < p.NRB) {
-      for (int gi = 0; gi < ngc; gi += kItemGroups) {
-        const int ng = (ngc - gi < kItemGroups) ? ngc - gi : kItemGroups;
-        if (!dead && !mbar_wait_bounded(bars_w + cstage * 8, cphase, kSpinLimit)) {
-          dead = true;
-          atomicExch(p.status, W4A16_ETIMEOUT);
-        }
-        const uint32_t base = ring_w + cstage * kItemStride;
-        for (int gg = 0; gg < ng; ++gg) {
-          const int gl = gi + gg;
-          float acc[NT][2][4];
-#pragma unroll
-          for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-            for (int c = 0; c < 2; ++c) acc[nt][c][0] = acc[nt][c][1] = acc[nt][c][2] = acc[nt][c][3] = 0.f;
-#pragma unroll
-          for (int s = 0; s < 2; ++s) {
-            const uint4 wq = lds128(base + (gg * 2 + s) * kStepBytes + lane * 16);
-            uint32_t a[4][4];  // [mma j][register]
-            a[0][0] = (wq.x & kNibMask) | kMagic;
-            a[0][1] = (wq.z & kNibMask) | kMagic;
-            a[0][2] = ((wq.x >> 4) & kNibMask) | kMagic;
-            a[0][3] = ((wq.z >> 4) & kNibMask) | kMagic;
-            a[1][0] = ((wq.x >> 8) & kNibMask) | kMagic;
-            a[1][1] = ((wq.z >> 8) & kNibMask) | kMagic;
-            a[1][2] = ((wq.x >> 12) & kNibMask) | kMagic;
-            a[1][3] = ((wq.z >> 12) & kNibMask) | kMagic;
-            a[2][0] = (wq.y & kNibMask) | kMagic;
-            a[2][1] = (wq.w & kNibMask) | kMagic;
-            a[2][2] = ((wq.y >> 4) & kNibMask) | kMagic;
-            a[2][3] = ((wq.w >> 4) & kNibMask) | kMagic;
-            a[3][0] = ((wq.y >> 8) & kNibMask) | kMagic;
-            a[3][1] = ((wq.w >> 8) & kNibMask) | kMagic;
-            a[3][2] = ((wq.y >> 12) & kNibMask) | kMagic;
-            a[3][3] = ((wq.w >> 12) & kNibMask) | kMagic;
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-              const uint32_t xa = xbuf_a + cb * XBUF + (((gl * 2 + s) * NT + nt) * 2) * 512 + lane * 16;
-              const uint4 bl = lds128(xa), bh = lds128(xa + 512);
-              mma_bf16_16816(acc[nt][0], a[0][0], a[0][1], a[0][2], a[0][3], bl.x, bl.y);
-              mma_bf16_16816(acc[nt][1], a[1][0], a[1][1], a[1][2], a[1][3], bl.z, bl.w);
-              mma_bf16_16816(acc[nt][0], a[2][0], a[2][1], a[2][2], a[2][3], bh.x, bh.y);
-              mma_bf16_16816(acc[nt][1], a[3][0], a[3][1], a[3][2], a[3][3], bh.z, bh.w);
-            }
-          }
-          // group fix-up: y += s * (acc - (128 + zp) * sum(x))
-          const uint8_t* itm = ring + (warp * D + cstage) * kItemStride;
-          const uint16_t* isc = reinterpret_cast<const uint16_t*>(itm + kItemQ) + gg * 16;
-          const uint8_t* izp = itm + kItemQ + kItemS + gg * 16;
-          const float s_lo = bf16_bits_to_float(isc[grow]), s_hi = bf16_bits_to_float(isc[grow + 8]);
-          const float z_lo = 128.f + static_cast<float>(izp[grow]);
-          const float z_hi = 128.f + static_cast<float>(izp[grow + 8]);
-#pragma unroll
-          for (int nt = 0; nt < NT; ++nt) {
-            const float2 xs =
-                *reinterpret_cast<const float2*>(xsum + (cb * kChunkGroups + gl) * 8 * NT + nt * 8 + 2 * t);
-            fin[nt][0] = fmaf(s_lo, fmaf(-z_lo, xs.x, acc[nt][0][0] + acc[nt][1][0]), fin[nt][0]);
-            fin[nt][1] = fmaf(s_lo, fmaf(-z_lo, xs.y, acc[nt][0][1] + acc[nt][1][1]), fin[nt][1]);
-            fin[nt][2] = fmaf(s_hi, fmaf(-z_hi, xs.x, acc[nt][0][2] + acc[nt][1][2]), fin[nt][2]);
-            fin[nt][3] = fmaf(s_hi, fmaf(-z_hi, xs.y, acc[nt][0][3] + acc[nt][1][3]), fin[nt][3]);
-          }
-        }
-        __syncwarp();
-        if (lane == 0) {
-          fence_proxy_async();  // our reads of this stage precede the async refill
-          issue_next();
-        }
-        if (++cstage == D) {
-          cstage = 0;
-          cphase ^= 1;
-        }
-      }
+    if (lane == 0) mbar_arrive(xempty_a + xb * 8);  // (the __syncwarp above ordered every lane's reads)
+    if (++xb == kXBufs) {
+      xb = 0;
+      xph ^= 1;
     }
 
-    u = un;
-    cb ^= 1;
-    const long long tile_end = static_cast<long long>(tile + 1) * G;
-    if (u == u1 || u == tile_end) {
-      // ---- end of this CTA's segment of row tile `tile`: groups [seg_begin, g_end) ----
-      const int g_end = static_cast<int>(u - static_cast<long long>(tile) * G);
-      if (seg_begin == 0 && g_end == G) {
+    if (c.seg_last) {
+      // ---- end of this CTA's segment of row tile c.tile: groups [seg_g0, seg_g1) ----
+      const int tile = c.tile;
+      if (c.seg_g0 == 0 && c.seg_g1 == G) {
         finalize(tile, fin);
       } else {
         const long long X0 = static_cast<long long>(tile) * G;
         const int c_first = static_cast<int>(((X0 + 1) * gridDim.x - 1) / U);
-        const int c_last = static_cast<int>((tile_end * gridDim.x - 1) / U);
-        const int which = (static_cast<int>(u0 / G) == tile) ? 0 : 1;
+        const int c_last = static_cast<int>(((X0 + G) * gridDim.x - 1) / U);
+        const int which = (u0 / G == tile) ? 0 : 1;
         float* slot = p.partial + (static_cast<size_t>(blockIdx.x) * 2 + which) * SLOT;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
           for (int j = 0; j < 4; ++j)
             slot[(warp * 16 + grow + 8 * (j >> 1)) * 8 * NT + nt * 8 + 2 * t + (j & 1)] = fin[nt][j];
-        __threadfence();
-        __syncthreads();
+        named_bar_sync(kConsumerBar, NCT);
         if (tid == 0) {
+          // release: the barrier ordered every thread's partial stores before this fence
+          __threadfence();
           const unsigned old = atomicAdd(p.counters + tile, 1u);
           const int last = (old == static_cast<unsigned>(c_last - c_first));
-          if (last) p.counters[tile] = 0;  // every contributor has arrived: leave it clean
+          if (last) {
+            p.counters[tile] = 0;  // every contributor has arrived: leave it clean
+            __threadfence();       // acquire side for the reads below
+          }
           *sflag = last;
         }
-        __syncthreads();
+        named_bar_sync(kConsumerBar, NCT);
         if (*sflag) {
-          __threadfence();
           float v[NT][4];
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) v[nt][0] = v[nt][1] = v[nt][2] = v[nt][3] = 0.f;
-          for (int c = c_first; c <= c_last; ++c) {  // fixed order: bitwise reproducible
-            const int wc = (static_cast<int>((U * c / gridDim.x) / G) == tile) ? 0 : 1;
-            const float* sl = p.partial + (static_cast<size_t>(c) * 2 + wc) * SLOT;
+          for (int cc = c_first; cc <= c_last; ++cc) {  // fixed order: bitwise reproducible
+            const int cu0 = static_cast<int>(static_cast<long long>(U) * cc / gridDim.x);
+            const int wc = (cu0 / G == tile) ? 0 : 1;
+            const float* sl = p.partial + (static_cast<size_t>(cc) * 2 + wc) * SLOT;
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
@@ -377,16 +569,16 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_skinny(const SkinnyParams p) 
           }
           finalize(tile, v);
         }
-        __syncthreads();  // sflag may be rewritten by the next segment
+        named_bar_sync(kConsumerBar, NCT);  // sflag may be rewritten by the next segment
       }
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) fin[nt][0] = fin[nt][1] = fin[nt][2] = fin[nt][3] = 0.f;
-      seg_begin = 0;
     }
   }
+  DBG_T(3);
 
-  if (dead) {  // drain whatever this warp still has in flight before the CTA exits
-    for (int s = 0; s < D; ++s) mbar_wait_bounded(bars_w + s * 8, 0, 1u << 16);
+  if (dead) {  // let whatever is still in flight land before the CTA exits
+    for (int s = 0; s < D; ++s) mbar_wait_bounded(wfull_a + s * 8, 0, 1u << 16);
   }
 
   if (p.argmax) {
@@ -394,58 +586,62 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_skinny(const SkinnyParams p) 
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-      for (int c = 0; c < 2; ++c)
+      for (int cc = 0; cc < 2; ++cc)
 #pragma unroll
         for (int off = 4; off < 32; off <<= 1) {
-          const float ov = __shfl_xor_sync(0xffffffffu, best_v[nt][c], off);
-          const int oi = __shfl_xor_sync(0xffffffffu, best_i[nt][c], off);
-          if (better(ov, oi, best_v[nt][c], best_i[nt][c])) {
-            best_v[nt][c] = ov;
-            best_i[nt][c] = oi;
+          const float ov = __shfl_xor_sync(0xffffffffu, best_v[nt][cc], off);
+          const int oi = __shfl_xor_sync(0xffffffffu, best_i[nt][cc], off);
+          if (better(ov, oi, best_v[nt][cc], best_i[nt][cc])) {
+            best_v[nt][cc] = ov;
+            best_i[nt][cc] = oi;
           }
         }
-    __syncthreads();  // xbuf is free now: reuse it for the per-warp candidates
-    Pair* cand = reinterpret_cast<Pair*>(xbuf);  // [WARPS][16]
+    named_bar_sync(kConsumerBar, NCT);
+    // per-warp candidates go through the (now idle) weight ring: every stage was consumed
+    Pair* cand = reinterpret_cast<Pair*>(ring);  // [CW][16]
     if (grow == 0) {
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int c = 0; c < 2; ++c) cand[warp * 16 + nt * 8 + 2 * t + c] = Pair{best_v[nt][c], best_i[nt][c]};
+        for (int cc = 0; cc < 2; ++cc) cand[warp * 16 + nt * 8 + 2 * t + cc] = Pair{best_v[nt][cc], best_i[nt][cc]};
     }
-    __syncthreads();
+    named_bar_sync(kConsumerBar, NCT);
     Pair* cta_pairs = static_cast<Pair*>(p.cta_pairs);
-    if (tid < p.M) {
+    if (tid < M) {
       Pair b{-FLT_MAX, INT_MAX};
-      if (tid < 8 * NT)
-        for (int w = 0; w < WARPS; ++w) {
-          const Pair c = cand[w * 16 + tid];
-          if (better(c.v, c.i, b.v, b.i)) b = c;
-        }
+      for (int w = 0; w < CW; ++w) {
+        const Pair q = cand[w * 16 + tid];
+        if (better(q.v, q.i, b.v, b.i)) b = q;
+      }
       cta_pairs[blockIdx.x * 16 + tid] = b;
     }
-    __threadfence();
-    __syncthreads();
+    named_bar_sync(kConsumerBar, NCT);
     if (tid == 0) {
+      __threadfence();
       const unsigned old = atomicAdd(p.counters + p.tiles, 1u);
       const int last = (old == gridDim.x - 1);
-      if (last) p.counters[p.tiles] = 0;
+      if (last) {
+        p.counters[p.tiles] = 0;
+        __threadfence();
+      }
       *sflag = last;
     }
-    __syncthreads();
-    if (*sflag && tid < p.M) {
-      __threadfence();
+    named_bar_sync(kConsumerBar, NCT);
+    if (*sflag && tid < M) {
       Pair b{-FLT_MAX, INT_MAX};
-      for (unsigned c = 0; c < gridDim.x; ++c) {
+      for (unsigned cc = 0; cc < gridDim.x; ++cc) {
         Pair q;
-        q.v = __ldcg(&cta_pairs[c * 16 + tid].v);
-        q.i = __ldcg(&cta_pairs[c * 16 + tid].i);
+        q.v = __ldcg(&cta_pairs[cc * 16 + tid].v);
+        q.i = __ldcg(&cta_pairs[cc * 16 + tid].i);
         if (better(q.v, q.i, b.v, b.i)) b = q;
       }
       const int idx = (b.i == INT_MAX) ? 0 : b.i;  // nothing finite: index 0, as a plain scan gives
       if (p.ids) p.ids[tid] = idx + p.row_offset;
-      if (p.pairs_out) static_cast<Pair*>(p.pairs_out)[tid] = Pair{b.v, (b.i == INT_MAX) ? INT_MAX : b.i + p.row_offset};
+      if (p.pairs_out)
+        static_cast<Pair*>(p.pairs_out)[tid] = Pair{b.v, (b.i == INT_MAX) ? INT_MAX : b.i + p.row_offset};
     }
   }
+  DBG_T(4);
 }
 
 __global__ void k_pairs_reduce(int32_t* ids, const Pair* pairs, int nranks, int M) {
@@ -460,37 +656,47 @@ __global__ void k_pairs_reduce(int32_t* ids, const Pair* pairs, int nranks, int 
 }
 
 // ------------------------------------------------------------------ host side
+}  // namespace
+unsigned long long* g_dbg = nullptr;
+namespace {
 struct Config {
-  int warps;
+  int depth;  // ring stages
+  int ctas;   // CTAs per SM
+  int xbuf;   // bytes of one activation buffer
   int pdl;
-  int ctas_per_sm_cap;  // grid = min(sms, units)
 };
 
 const Config& config() {
   static Config c = [] {
-    Config k{8, 1, 1};
-    if (const char* e = getenv("W4A16_WARPS")) k.warps = atoi(e) == 16 ? 16 : 8;
+    Config k{4, 2, 8192, 1};
+    if (const char* e = getenv("W4A16_DEPTH")) k.depth = atoi(e);
+    if (const char* e = getenv("W4A16_CTAS")) k.ctas = atoi(e) >= 2 ? 2 : 1;
+    if (const char* e = getenv("W4A16_XBUF")) k.xbuf = atoi(e);
     if (const char* e = getenv("W4A16_PDL")) k.pdl = atoi(e) != 0;
+    if (k.depth != 3 && k.depth != 4 && k.depth != 6) k.depth = 4;
+    if (k.xbuf < 4096) k.xbuf = 4096;
+    if (k.xbuf > 16384) k.xbuf = 16384;
+    k.xbuf &= ~1023;
     return k;
   }();
   return c;
 }
 
-constexpr int kMaxTileRows = 256;  // scratch is sized for the widest tile any configuration uses
+constexpr int kMaxCtasPerSm = 2;
 
-template <int NT, int WARPS, int D>
-int launch_cfg(const SkinnyParams& p, int grid, cudaStream_t st) {
-  constexpr int smem = skinny_smem_bytes<NT, WARPS, D>();
-  static bool attr_set[64] = {};
+template <int NT, int D>
+int launch_cfg(SkinnyParams& p, int grid, cudaStream_t st) {
+  const int smem = skinny_fixed_smem<D>() + kXBufs * p.xbuf_bytes;
+  static int attr_set[64] = {};
   int dev = 0;
   W4_CUDA(cudaGetDevice(&dev));
-  if (!attr_set[dev & 63]) {
-    W4_CUDA(cudaFuncSetAttribute(k_skinny<NT, WARPS, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    attr_set[dev & 63] = true;
+  if (attr_set[dev & 63] < smem) {
+    W4_CUDA(cudaFuncSetAttribute(k_skinny<NT, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    attr_set[dev & 63] = smem;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(WARPS * 32);
+  cfg.blockDim = dim3(kWarps * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute at[1];
@@ -498,16 +704,26 @@ int launch_cfg(const SkinnyParams& p, int grid, cudaStream_t st) {
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
   cfg.numAttrs = config().pdl ? 1 : 0;
-  W4_CUDA(cudaLaunchKernelEx(&cfg, k_skinny<NT, WARPS, D>, p));
+  W4_CUDA(cudaLaunchKernelEx(&cfg, k_skinny<NT, D>, p));
   return W4A16_OK;
 }
 
-int tile_rows() { return config().warps * 16; }
+template <int NT>
+int launch_depth(SkinnyParams& p, int grid, cudaStream_t st) {
+  switch (config().depth) {
+    case 3: return launch_cfg<NT, 3>(p, grid, st);
+    case 6: return launch_cfg<NT, 6>(p, grid, st);
+    default: return launch_cfg<NT, 4>(p, grid, st);
+  }
+}
+
+int tile_rows() { return kTileRows; }
 
 int grid_for_shape(int out_f, int G, int sms) {
   const int tiles = (out_f + tile_rows() - 1) / tile_rows();
   const long long U = static_cast<long long>(tiles) * G;
-  return static_cast<int>(U < sms ? U : sms);
+  const long long want = static_cast<long long>(sms) * config().ctas;
+  return static_cast<int>(U < want ? U : want);
 }
 
 int launch_skinny(SkinnyParams& p, const w4a16_weights_t* w, const uint16_t* x, int M, w4a16_scratch_t* s,
@@ -519,9 +735,7 @@ int launch_skinny(SkinnyParams& p, const w4a16_weights_t* w, const uint16_t* x, 
   const DeviceInfo* di = device_info();
   if (!di) return W4A16_ECUDA;
   const int TR = tile_rows();
-  p.qw = reinterpret_cast<const uint4*>(w->qweight);
-  p.sc = w->scale;
-  p.zp = w->zp;
+  p.stream = reinterpret_cast<const uint8_t*>(w->qweight);
   p.x = x;
   p.M = M;
   p.N = w->out_f;
@@ -533,11 +747,27 @@ int launch_skinny(SkinnyParams& p, const w4a16_weights_t* w, const uint16_t* x, 
   p.counters = reinterpret_cast<unsigned*>(s->xgsum);
   p.cta_pairs = s->xf;
   p.status = di->status;
+  if (const char* e = getenv("W4A16_DEBUG_SKIP")) p.debug_skip = atoi(e);
+  if (getenv("W4A16_DEBUG_TIME")) {
+    static unsigned long long* dbg = nullptr;
+    if (!dbg) cudaMalloc(&dbg, 4096 * 8 * 8);
+    p.dbg = dbg;
+    g_dbg = dbg;
+  }
+  const int nt = M <= 8 ? 1 : 2;
+  // groups per activation chunk: what one buffer holds (256 B per token per group), even.
+  // Token rows sit 16 bytes past a multiple of 128 apart, which keeps the B-fragment loads of
+  // neighbouring token rows on different banks.
+  int cg = config().xbuf / (256 * M);
+  if (cg > kMaxChunkGroups) cg = kMaxChunkGroups;
+  cg &= ~1;
+  if (cg < 2) cg = 2;
+  p.chunk_groups = cg;
+  p.xrow_bytes = cg * 256 + 16;
+  p.xbuf_bytes = (M * p.xrow_bytes + 127) & ~127;
   const int grid = grid_for_shape(w->out_f, w->num_groups, di->sms);
   if (int rc = w4a16_scratch_check(s, w->out_f, M)) return rc;
-  const int nt = M <= 8 ? 1 : 2;
-  if (config().warps == 16) return nt == 1 ? launch_cfg<1, 16, 4>(p, grid, st) : launch_cfg<2, 16, 4>(p, grid, st);
-  return nt == 1 ? launch_cfg<1, 8, 6>(p, grid, st) : launch_cfg<2, 8, 6>(p, grid, st);
+  return nt == 1 ? launch_depth<1>(p, grid, st) : launch_depth<2>(p, grid, st);
 }
 
 }  // namespace
@@ -557,11 +787,11 @@ int w4a16_scratch_alloc(w4a16_scratch_t* s, int max_in, int max_out, int min_gro
   s->max_out = max_out;
   s->max_m = max_m;
   s->max_groups = max_in / min_group;
-  s->max_splits = di->sms;  // CTAs of the persistent grid
+  s->max_splits = di->sms * kMaxCtasPerSm;  // CTAs of the persistent grid
   // two partial tiles per CTA (head and tail of its unit range), widest tile, 16 tokens
-  s->partial_elems = static_cast<size_t>(di->sms) * 2 * kMaxTileRows * 16;
+  s->partial_elems = static_cast<size_t>(s->max_splits) * 2 * kTileRows * 16;
   const size_t counters = (static_cast<size_t>(max_out) / 128 + 2) * sizeof(unsigned);
-  const size_t pairs = static_cast<size_t>(di->sms) * 16 * sizeof(Pair);
+  const size_t pairs = static_cast<size_t>(s->max_splits) * 16 * sizeof(Pair);
   void *xf = nullptr, *cn = nullptr, *pa = nullptr;
   cudaError_t e = cudaMalloc(&xf, pairs);
   if (e == cudaSuccess) e = cudaMalloc(&cn, counters);
@@ -594,13 +824,14 @@ int w4a16_scratch_check(const w4a16_scratch_t* s, int out_f, int M) {
   (void)M;
   const DeviceInfo* di = device_info();
   if (!di) return W4A16_ECUDA;
-  const size_t need = static_cast<size_t>(di->sms) * 2 * kMaxTileRows * 16;
+  const int ctas = di->sms * kMaxCtasPerSm;
+  const size_t need = static_cast<size_t>(ctas) * 2 * kTileRows * 16;
   if (need > s->partial_elems)
     return fail(W4A16_ESCRATCH, "scratch: partial buffer holds %zu floats, %zu needed", s->partial_elems, need);
   if (out_f > s->max_out)
     return fail(W4A16_ESCRATCH, "scratch: sized for out_f <= %d, got %d", s->max_out, out_f);
-  if (di->sms > s->max_splits)
-    return fail(W4A16_ESCRATCH, "scratch: sized for %d CTAs, device has %d SMs", s->max_splits, di->sms);
+  if (ctas > s->max_splits)
+    return fail(W4A16_ESCRATCH, "scratch: sized for %d CTAs, this device runs %d", s->max_splits, ctas);
   return W4A16_OK;
 }
 
@@ -690,3 +921,9 @@ int w4a16_gemm_skinny_sharded(uint16_t* const* y_peers, int nranks, int rank, in
 }
 
 }  // extern "C"
+
+extern "C" __attribute__((visibility("default"))) int w4a16_debug_read(unsigned long long* host, int n) {
+  if (!w4a16::g_dbg) return -1;
+  cudaDeviceSynchronize();
+  return cudaMemcpy(host, w4a16::g_dbg, size_t(n) * 8, cudaMemcpyDeviceToHost);
+}

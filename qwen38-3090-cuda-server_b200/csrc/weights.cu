@@ -69,8 +69,9 @@ const DeviceInfo* device_info() {
 namespace {
 
 // One thread per destination uint4 (16 rows x 64 k block, lane slot).
-__global__ void k_repack_q(uint4* __restrict__ dq, const uint32_t* __restrict__ sq, int out_f,
-                           int words_per_row, int KB, int row_offset) {
+__global__ void k_repack_q(uint8_t* __restrict__ dst, const uint32_t* __restrict__ sq, int out_f,
+                           int words_per_row, int G, int row_offset) {
+  const int KB = G * 2;
   const long long n = static_cast<long long>(out_f / kRowBlock) * KB * 32;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -93,31 +94,31 @@ __global__ void k_repack_q(uint4* __restrict__ dq, const uint32_t* __restrict__ 
         out[hi * 2 + h] = o;
       }
     }
-    const int drb = srb + row_offset / kRowBlock;
-    dq[(static_cast<size_t>(drb) * KB + kb) * 32 + lane] = make_uint4(out[0], out[1], out[2], out[3]);
+    const size_t unit = unit_offset(srb * kRowBlock + row_offset, kb >> 1, G);
+    *reinterpret_cast<uint4*>(dst + unit + (kb & 1) * kStepBytes + lane * 16) =
+        make_uint4(out[0], out[1], out[2], out[3]);
   }
 }
 
-__global__ void k_repack_sz(uint16_t* __restrict__ ds, uint8_t* __restrict__ dz,
-                            const uint16_t* __restrict__ ss, const uint32_t* __restrict__ sz,
-                            int out_f, int G, int row_offset) {
+__global__ void k_repack_sz(uint8_t* __restrict__ dst, const uint16_t* __restrict__ ss,
+                            const uint32_t* __restrict__ sz, int out_f, int G, int row_offset) {
   const long long n = static_cast<long long>(out_f) * G;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const int g = static_cast<int>(i % G);
     const int so = static_cast<int>(i / G);
     const int o = so + row_offset;
-    const size_t d = (static_cast<size_t>(o / kRowBlock) * G + g) * kRowBlock + (o % kRowBlock);
-    ds[d] = ss[static_cast<size_t>(so) * G + g];
+    uint8_t* unit = dst + unit_offset(o, g, G);
+    const int r = sz_pos(o % kRowBlock);
+    reinterpret_cast<uint16_t*>(unit + kUnitScaleOff)[r] = ss[static_cast<size_t>(so) * G + g];
     const uint32_t zw = sz[static_cast<size_t>(so >> 3) * G + g];
-    dz[d] = static_cast<uint8_t>((zw >> ((so & 7) * 4)) & 0xFu);
+    unit[kUnitZpOff + r] = static_cast<uint8_t>((zw >> ((so & 7) * 4)) & 0xFu);
   }
 }
 
 // One thread per (row, 16-k slot): 16 bf16 values out, 32 contiguous bytes.
-__global__ void k_dequant_rows(uint16_t* __restrict__ dst, const uint4* __restrict__ qw,
-                               const uint16_t* __restrict__ sc, const uint8_t* __restrict__ zp,
-                               int row0, int nrows, int K, int G) {
+__global__ void k_dequant_rows(uint16_t* __restrict__ dst, const uint8_t* __restrict__ stream, int row0,
+                               int nrows, int K, int G) {
   const int KB = K / kStepK;
   const long long n = static_cast<long long>(nrows) * KB * 4;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
@@ -126,16 +127,15 @@ __global__ void k_dequant_rows(uint16_t* __restrict__ dst, const uint4* __restri
     const int kb = static_cast<int>((i >> 2) % KB);
     const int r = static_cast<int>((i >> 2) / KB);
     const int o = row0 + r;
-    const int rb = o / kRowBlock, ro = o % kRowBlock;
+    const int ro = o % kRowBlock;
     const int lane = (ro & 7) * 4 + t;
-    const uint4 q = qw[(static_cast<size_t>(rb) * KB + kb) * 32 + lane];
+    const uint8_t* unit = stream + unit_offset(o, kb >> 1, G);
+    const uint4 q = *reinterpret_cast<const uint4*>(unit + (kb & 1) * kStepBytes + lane * 16);
     const uint32_t w0 = (ro >> 3) ? q.z : q.x;
     const uint32_t w1 = (ro >> 3) ? q.w : q.y;
     const int k0 = kb * kStepK + 16 * t;
-    const int g = k0 / kGroup;
-    const size_t si = (static_cast<size_t>(rb) * G + g) * kRowBlock + ro;
-    const float s = bf16_bits_to_float(sc[si]);
-    const float z = static_cast<float>(zp[si]);
+    const float s = bf16_bits_to_float(reinterpret_cast<const uint16_t*>(unit + kUnitScaleOff)[sz_pos(ro)]);
+    const float z = static_cast<float>(unit[kUnitZpOff + sz_pos(ro)]);
     uint16_t v[16];
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
@@ -195,14 +195,16 @@ int w4a16_weights_alloc(w4a16_weights_t* w, int out_f, int in_f, int group_size,
   W4_REQUIRE(out_f > 0 && out_f % kRowBlock == 0, "weights_alloc: out_f %d not a positive multiple of 16",
              out_f);
   W4_REQUIRE(in_f > 0 && in_f % kGroup == 0, "weights_alloc: in_f %d not a positive multiple of 128", in_f);
-  (void)stream;
   memset(w, 0, sizeof *w);
   const int G = in_f / group_size;
-  const size_t qb = static_cast<size_t>(out_f) * in_f / 2;
-  const size_t sb = static_cast<size_t>(out_f) * G * 2;
-  const size_t zb = static_cast<size_t>(out_f) * G;
-  // Three independent bases: the reference's callers cudaFree them one by one
-  // (src/model/model.cu:111,204).
+  // The whole weight stream (int4 blocks with their scales and zero points interleaved per
+  // 16-row x 128-k unit) lives behind `qweight`; for out_f a multiple of 128 its size is exactly
+  // the reference's total_bytes() = int4 + bf16 scales + one-byte zero points. `scale` and `zp` stay valid,
+  // independently freeable allocations because the reference's callers cudaFree all three
+  // pointers one by one (src/model/model.cu:111,204), but nothing is read through them.
+  const size_t qb = stream_bytes(out_f, G);  // out_f rounded up to whole 128-row tiles
+  const size_t sb = 256;
+  const size_t zb = 256;
   void *q = nullptr, *s = nullptr, *z = nullptr;
   cudaError_t e = cudaMalloc(&q, qb);
   if (e == cudaSuccess) e = cudaMalloc(&s, sb);
@@ -212,6 +214,16 @@ int w4a16_weights_alloc(w4a16_weights_t* w, int out_f, int in_f, int group_size,
     cudaFree(s);
     cudaFree(z);
     return fail(W4A16_ECUDA, "weights_alloc(%d x %d): %s", out_f, in_f, cudaGetErrorString(e));
+  }
+  if (out_f % kTileRows != 0) {
+    // rows of the last tile past out_f: zero scales, so they contribute nothing and are never stored
+    e = cudaMemset(q, 0, qb);
+    if (e != cudaSuccess) {
+      cudaFree(q);
+      cudaFree(s);
+      cudaFree(z);
+      return fail(W4A16_ECUDA, "weights_alloc: %s", cudaGetErrorString(e));
+    }
   }
   w->qweight = static_cast<uint32_t*>(q);
   w->scale = static_cast<uint16_t*>(s);
@@ -235,12 +247,12 @@ int w4a16_repack_into(const w4a16_weights_t* w, int dst_row_offset, const uint32
              dst_row_offset, dst_row_offset + out_f, w->out_f);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int KB = w->in_f / kStepK;
+  uint8_t* stream_base = reinterpret_cast<uint8_t*>(w->qweight);
   const long long nq = static_cast<long long>(out_f / kRowBlock) * KB * 32;
-  k_repack_q<<<grid_for(nq, 256), 256, 0, st>>>(reinterpret_cast<uint4*>(w->qweight), packed, out_f,
-                                                w->in_f / 8, KB, dst_row_offset);
+  k_repack_q<<<grid_for(nq, 256), 256, 0, st>>>(stream_base, packed, out_f, w->in_f / 8, w->num_groups,
+                                                dst_row_offset);
   const long long ns = static_cast<long long>(out_f) * w->num_groups;
-  k_repack_sz<<<grid_for(ns, 256), 256, 0, st>>>(w->scale, w->zp, scale, zp, out_f, w->num_groups,
-                                                 dst_row_offset);
+  k_repack_sz<<<grid_for(ns, 256), 256, 0, st>>>(stream_base, scale, zp, out_f, w->num_groups, dst_row_offset);
   W4_CUDA(cudaGetLastError());
   return W4A16_OK;
 }
@@ -263,8 +275,7 @@ int w4a16_dequant_rows(uint16_t* dst, const w4a16_weights_t* w, int row0, int nr
   if (nrows == 0) return W4A16_OK;
   const long long n = static_cast<long long>(nrows) * (w->in_f / kStepK) * 4;
   k_dequant_rows<<<grid_for(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      dst, reinterpret_cast<const uint4*>(w->qweight), w->scale, w->zp, row0, nrows, w->in_f,
-      w->num_groups);
+      dst, reinterpret_cast<const uint8_t*>(w->qweight), row0, nrows, w->in_f, w->num_groups);
   W4_CUDA(cudaGetLastError());
   return W4A16_OK;
 }
