@@ -42,35 +42,30 @@ const DeviceInfo* device_info();
 int check_weights(const w4a16_weights_t* w);
 
 // ------------------------------------------------------------------ layout
-constexpr int kRowBlock = 16;   // rows per weight block
-constexpr int kStepK = 64;      // k per weight block ("step")
-constexpr int kGroup = 128;     // quantisation group along k
-constexpr int kStepBytes = 512; // one 16x64 int4 block
-// One "unit" of the weight stream = 16 rows x one 128-k group, everything a warp
-// needs for it in one contiguous piece: two 512-byte int4 blocks, then the 16 bf16
-// scales, then the 16 one-byte zero points. Scales and zero points are ordered
-// r0,r8,r1,r9,...,r7,r15 so the lane that owns rows r and r+8 reads both with one load.
-constexpr int kUnitScaleOff = 2 * kStepBytes;        // 1024
-constexpr int kUnitZpOff = kUnitScaleOff + 32;       // 1056
-constexpr int kUnitBytes = kUnitZpOff + 16;          // 1072
-// The stream is ordered [row tile of 128 rows][group][16-row block within the tile], so the
-// eight warps of a CTA working on one (tile, group) read 8576 contiguous bytes, consecutive
-// groups follow each other, and a CTA's whole range of units is one sequential region.
-constexpr int kTileBlocks = 8;                             // 16-row blocks per row tile
-constexpr int kTileRows = kTileBlocks * kRowBlock;         // 128
-constexpr int kTileGroupBytes = kTileBlocks * kUnitBytes;  // 8576
+// Private weight layout ("stream"), group size 128. The matrix is cut into row tiles of 128
+// output rows; for every (row tile, k group) the stream holds one 8576-byte block:
+//     [4 k-chunks of 32][128 rows] uint4   8192 B   packed int4, one thread-load per (row, 32 k)
+//     [128 rows] bf16 scale                  256 B
+//     [128 rows] u8 zero point (raw nibble)  128 B
+// Blocks are ordered [row tile][group], so consecutive groups of a tile follow each other and
+// a CTA's whole share of the matrix is one sequential region of memory.
+// Inside a uint4, word i holds k = 32 c + 8 i .. +7 of its row; k-offset o sits at nibble
+// (o>>1) + 4*(o&1), so the masks 0x000F000F << {0,4,8,12} pull out pairs of adjacent k.
+constexpr int kGroup = 128;                               // quantisation group along k
+constexpr int kRowGranule = 16;                           // out_f and row offsets are multiples of this
+constexpr int kTileRows = 128;                            // output rows per row tile
+constexpr int kChunkBytes = kTileRows * 16;               // 2048: one 32-k chunk of a tile
+constexpr int kTgScaleOff = 4 * kChunkBytes;              // 8192
+constexpr int kTgZpOff = kTgScaleOff + kTileRows * 2;     // 8448
+constexpr int kTileGroupBytes = kTgZpOff + kTileRows;     // 8576
 
 __host__ __device__ inline size_t stream_bytes(int out_f, int G) {
   return static_cast<size_t>((out_f + kTileRows - 1) / kTileRows) * G * kTileGroupBytes;
 }
-// byte offset of the unit holding output row `o`, group `g`
-__host__ __device__ inline size_t unit_offset(int o, int g, int G) {
-  return (static_cast<size_t>(o / kTileRows) * G + g) * kTileGroupBytes +
-         static_cast<size_t>((o % kTileRows) / kRowBlock) * kUnitBytes;
+// byte offset of the block of (row tile of `o`, group g)
+__host__ __device__ inline size_t tile_group_offset(int o, int g, int G) {
+  return (static_cast<size_t>(o / kTileRows) * G + g) * kTileGroupBytes;
 }
-
-// slot of row r (0..15) inside a unit's scale / zero-point arrays
-__host__ __device__ inline int sz_pos(int r) { return (r & 7) * 2 + (r >> 3); }
 // nibble position inside a packed word for k-offset c (0..7)
 __host__ __device__ inline int nib_pos(int c) { return (c >> 1) + 4 * (c & 1); }
 
@@ -99,21 +94,33 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+// One potentially-blocking test of the barrier's phase: the hardware may park the thread for up
+// to `hint_ns` (it is woken when the phase completes), so a waiting warp does not burn issue slots.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t hint_ns = 2000) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after `limit` polls and returns false; never spins forever.
+// Bounded wait: gives up after `limit` tests (each may block for the hint time) and returns
+// false; never spins forever.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t limit) {
   for (uint32_t i = 0; i < limit; ++i)
     if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+// Same, for roles that are not latency critical: back off between polls so the spinning thread
+// leaves the issue slots of its scheduler to the warps doing the math.
+__device__ __forceinline__ bool mbar_wait_bounded_relaxed(uint32_t bar, uint32_t parity, uint32_t limit) {
+  for (uint32_t i = 0; i < limit; ++i) {
+    if (mbar_try_wait(bar, parity, 10000)) return true;
+    __nanosleep(200);
+  }
   return false;
 }
 // 1-D bulk async copy global -> this CTA's shared memory, completion on an mbarrier.
@@ -148,6 +155,95 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
       "{%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// ------------------------------------------------------------------ tcgen05 / tensor memory
+// Allocation is warp-collective; the base address lands in shared memory.
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// 16 consecutive 32-bit columns of this thread's TMEM lane (lane = 32*(warp%4) + laneid)
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+template <int N>
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, float (&d)[N]);
+template <>
+__device__ __forceinline__ void tmem_ld<1>(uint32_t taddr, float (&d)[1]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=f"(d[0]) : "r"(taddr) : "memory");
+}
+template <>
+__device__ __forceinline__ void tmem_ld<2>(uint32_t taddr, float (&d)[2]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0,%1}, [%2];" : "=f"(d[0]), "=f"(d[1]) : "r"(taddr) : "memory");
+}
+template <>
+__device__ __forceinline__ void tmem_ld<4>(uint32_t taddr, float (&d)[4]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+               : "r"(taddr)
+               : "memory");
+}
+template <>
+__device__ __forceinline__ void tmem_ld<8>(uint32_t taddr, float (&d)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3]), "=f"(d[4]), "=f"(d[5]), "=f"(d[6]), "=f"(d[7])
+               : "r"(taddr)
+               : "memory");
+}
+template <>
+__device__ __forceinline__ void tmem_ld<16>(uint32_t taddr, float (&d)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3]), "=f"(d[4]), "=f"(d[5]), "=f"(d[6]), "=f"(d[7]), "=f"(d[8]),
+        "=f"(d[9]), "=f"(d[10]), "=f"(d[11]), "=f"(d[12]), "=f"(d[13]), "=f"(d[14]), "=f"(d[15])
+      : "r"(taddr)
+      : "memory");
+}
+// Shared-memory operand descriptor, K-major, no swizzle: 8-row x 16-byte core matrices;
+// lbo = byte distance between core matrices along K, sbo = along the row (M/N) direction.
+__device__ __forceinline__ uint64_t umma_desc_kmajor(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+  return static_cast<uint64_t>((saddr >> 4) & 0x3FFFu) | (static_cast<uint64_t>(lbo >> 4) << 16) |
+         (static_cast<uint64_t>(sbo >> 4) << 32) | (1ull << 46);
+}
+// Instruction descriptor for kind::f16 with bf16 A/B (both K-major), fp32 accumulate.
+__host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(N >> 3) << 17) |
+         (static_cast<uint32_t>(M >> 4) << 24);
+}
+// D[tmem] (+)= A[tmem] * B[smem desc]; issued by ONE thread.
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc]
+__device__ __forceinline__ void umma_bf16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The mbarrier gets one arrival once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
 // Programmatic dependent launch: wait until the grids this one depends on have

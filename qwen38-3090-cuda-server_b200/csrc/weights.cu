@@ -68,35 +68,28 @@ const DeviceInfo* device_info() {
 // ------------------------------------------------------------------ kernels
 namespace {
 
-// One thread per destination uint4 (16 rows x 64 k block, lane slot).
+// One thread per destination uint4: (row, 32-k chunk).
 __global__ void k_repack_q(uint8_t* __restrict__ dst, const uint32_t* __restrict__ sq, int out_f,
                            int words_per_row, int G, int row_offset) {
-  const int KB = G * 2;
-  const long long n = static_cast<long long>(out_f / kRowBlock) * KB * 32;
+  const int C = G * 4;  // 32-k chunks per row
+  const long long n = static_cast<long long>(out_f) * C;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int lane = static_cast<int>(i & 31);
-    const long long blk = i >> 5;
-    const int kb = static_cast<int>(blk % KB);
-    const int srb = static_cast<int>(blk / KB);  // source row block
-    const int g = lane >> 2, t = lane & 3;
+    const int so = static_cast<int>(i % out_f);  // consecutive threads -> consecutive rows (coalesced stores)
+    const int c = static_cast<int>(i / out_f);
+    const uint4 src = *reinterpret_cast<const uint4*>(sq + static_cast<size_t>(so) * words_per_row + c * 4);
+    const uint32_t in[4] = {src.x, src.y, src.z, src.w};
     uint32_t out[4];
 #pragma unroll
-    for (int hi = 0; hi < 2; ++hi) {
-      const int srow = srb * kRowBlock + g + 8 * hi;
-      const uint32_t* src = sq + static_cast<size_t>(srow) * words_per_row + (kb * kStepK + 16 * t) / 8;
+    for (int w = 0; w < 4; ++w) {
+      uint32_t o = 0;
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const uint32_t w = src[h];
-        uint32_t o = 0;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) o |= ((w >> (4 * c)) & 0xFu) << (4 * nib_pos(c));
-        out[hi * 2 + h] = o;
-      }
+      for (int k = 0; k < 8; ++k) o |= ((in[w] >> (4 * k)) & 0xFu) << (4 * nib_pos(k));
+      out[w] = o;
     }
-    const size_t unit = unit_offset(srb * kRowBlock + row_offset, kb >> 1, G);
-    *reinterpret_cast<uint4*>(dst + unit + (kb & 1) * kStepBytes + lane * 16) =
-        make_uint4(out[0], out[1], out[2], out[3]);
+    const int o = so + row_offset;
+    *reinterpret_cast<uint4*>(dst + tile_group_offset(o, c >> 2, G) + (c & 3) * kChunkBytes +
+                              (o % kTileRows) * 16) = make_uint4(out[0], out[1], out[2], out[3]);
   }
 }
 
@@ -108,45 +101,40 @@ __global__ void k_repack_sz(uint8_t* __restrict__ dst, const uint16_t* __restric
     const int g = static_cast<int>(i % G);
     const int so = static_cast<int>(i / G);
     const int o = so + row_offset;
-    uint8_t* unit = dst + unit_offset(o, g, G);
-    const int r = sz_pos(o % kRowBlock);
-    reinterpret_cast<uint16_t*>(unit + kUnitScaleOff)[r] = ss[static_cast<size_t>(so) * G + g];
+    uint8_t* blk = dst + tile_group_offset(o, g, G);
+    const int r = o % kTileRows;
+    reinterpret_cast<uint16_t*>(blk + kTgScaleOff)[r] = ss[static_cast<size_t>(so) * G + g];
     const uint32_t zw = sz[static_cast<size_t>(so >> 3) * G + g];
-    unit[kUnitZpOff + r] = static_cast<uint8_t>((zw >> ((so & 7) * 4)) & 0xFu);
+    blk[kTgZpOff + r] = static_cast<uint8_t>((zw >> ((so & 7) * 4)) & 0xFu);
   }
 }
 
-// One thread per (row, 16-k slot): 16 bf16 values out, 32 contiguous bytes.
+// One thread per (row, 32-k chunk): 32 bf16 values out, 64 contiguous bytes.
 __global__ void k_dequant_rows(uint16_t* __restrict__ dst, const uint8_t* __restrict__ stream, int row0,
                                int nrows, int K, int G) {
-  const int KB = K / kStepK;
-  const long long n = static_cast<long long>(nrows) * KB * 4;
+  const int C = K / 32;
+  const long long n = static_cast<long long>(nrows) * C;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int t = static_cast<int>(i & 3);
-    const int kb = static_cast<int>((i >> 2) % KB);
-    const int r = static_cast<int>((i >> 2) / KB);
+    const int c = static_cast<int>(i % C);
+    const int r = static_cast<int>(i / C);
     const int o = row0 + r;
-    const int ro = o % kRowBlock;
-    const int lane = (ro & 7) * 4 + t;
-    const uint8_t* unit = stream + unit_offset(o, kb >> 1, G);
-    const uint4 q = *reinterpret_cast<const uint4*>(unit + (kb & 1) * kStepBytes + lane * 16);
-    const uint32_t w0 = (ro >> 3) ? q.z : q.x;
-    const uint32_t w1 = (ro >> 3) ? q.w : q.y;
-    const int k0 = kb * kStepK + 16 * t;
-    const float s = bf16_bits_to_float(reinterpret_cast<const uint16_t*>(unit + kUnitScaleOff)[sz_pos(ro)]);
-    const float z = static_cast<float>(unit[kUnitZpOff + sz_pos(ro)]);
-    uint16_t v[16];
+    const int ro = o % kTileRows;
+    const uint8_t* blk = stream + tile_group_offset(o, c >> 2, G);
+    const uint4 q = *reinterpret_cast<const uint4*>(blk + (c & 3) * kChunkBytes + ro * 16);
+    const float s = bf16_bits_to_float(reinterpret_cast<const uint16_t*>(blk + kTgScaleOff)[ro]);
+    const float z = static_cast<float>(blk[kTgZpOff + ro]);
+    const uint32_t in[4] = {q.x, q.y, q.z, q.w};
+    uint4* d = reinterpret_cast<uint4*>(dst + static_cast<size_t>(r) * K + c * 32);
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      v[c] = float_to_bf16_bits((static_cast<float>((w0 >> (4 * nib_pos(c))) & 0xFu) - z) * s);
-      v[8 + c] = float_to_bf16_bits((static_cast<float>((w1 >> (4 * nib_pos(c))) & 0xFu) - z) * s);
+    for (int w = 0; w < 4; ++w) {
+      uint16_t v[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        v[k] = float_to_bf16_bits((static_cast<float>((in[w] >> (4 * nib_pos(k))) & 0xFu) - z) * s);
+      d[w] = make_uint4(v[0] | (uint32_t(v[1]) << 16), v[2] | (uint32_t(v[3]) << 16),
+                        v[4] | (uint32_t(v[5]) << 16), v[6] | (uint32_t(v[7]) << 16));
     }
-    uint4* d = reinterpret_cast<uint4*>(dst + static_cast<size_t>(r) * K + k0);
-    d[0] = make_uint4(v[0] | (uint32_t(v[1]) << 16), v[2] | (uint32_t(v[3]) << 16),
-                      v[4] | (uint32_t(v[5]) << 16), v[6] | (uint32_t(v[7]) << 16));
-    d[1] = make_uint4(v[8] | (uint32_t(v[9]) << 16), v[10] | (uint32_t(v[11]) << 16),
-                      v[12] | (uint32_t(v[13]) << 16), v[14] | (uint32_t(v[15]) << 16));
   }
 }
 
@@ -161,7 +149,7 @@ int check_weights(const w4a16_weights_t* w) {
   W4_REQUIRE(w != nullptr, "weights: null struct");
   W4_REQUIRE(w->qweight && w->scale && w->zp, "weights: null buffer");
   W4_REQUIRE(w->group_size == kGroup, "weights: group_size %d unsupported (only 128)", w->group_size);
-  W4_REQUIRE(w->out_f > 0 && w->out_f % kRowBlock == 0, "weights: out_f %d not a positive multiple of 16",
+  W4_REQUIRE(w->out_f > 0 && w->out_f % kRowGranule == 0, "weights: out_f %d not a positive multiple of 16",
              w->out_f);
   W4_REQUIRE(w->in_f > 0 && w->in_f % kGroup == 0, "weights: in_f %d not a positive multiple of 128",
              w->in_f);
@@ -192,13 +180,13 @@ int w4a16_device_status(void) {
 int w4a16_weights_alloc(w4a16_weights_t* w, int out_f, int in_f, int group_size, void* stream) {
   W4_REQUIRE(w != nullptr, "weights_alloc: null struct");
   W4_REQUIRE(group_size == kGroup, "weights_alloc: group_size %d unsupported (only 128)", group_size);
-  W4_REQUIRE(out_f > 0 && out_f % kRowBlock == 0, "weights_alloc: out_f %d not a positive multiple of 16",
+  W4_REQUIRE(out_f > 0 && out_f % kRowGranule == 0, "weights_alloc: out_f %d not a positive multiple of 16",
              out_f);
   W4_REQUIRE(in_f > 0 && in_f % kGroup == 0, "weights_alloc: in_f %d not a positive multiple of 128", in_f);
   memset(w, 0, sizeof *w);
   const int G = in_f / group_size;
   // The whole weight stream (int4 blocks with their scales and zero points interleaved per
-  // 16-row x 128-k unit) lives behind `qweight`; for out_f a multiple of 128 its size is exactly
+  // 128-row x 128-k block) lives behind `qweight`; for out_f a multiple of 128 its size is exactly
   // the reference's total_bytes() = int4 + bf16 scales + one-byte zero points. `scale` and `zp` stay valid,
   // independently freeable allocations because the reference's callers cudaFree all three
   // pointers one by one (src/model/model.cu:111,204), but nothing is read through them.
@@ -239,16 +227,15 @@ int w4a16_repack_into(const w4a16_weights_t* w, int dst_row_offset, const uint32
                       const uint16_t* scale, const uint32_t* zp, int out_f, void* stream) {
   if (int rc = check_weights(w)) return rc;
   W4_REQUIRE(packed && scale && zp, "repack_into: null source tensor");
-  W4_REQUIRE(out_f > 0 && out_f % kRowBlock == 0, "repack_into: out_f %d not a positive multiple of 16",
+  W4_REQUIRE(out_f > 0 && out_f % kRowGranule == 0, "repack_into: out_f %d not a positive multiple of 16",
              out_f);
-  W4_REQUIRE(dst_row_offset >= 0 && dst_row_offset % kRowBlock == 0,
+  W4_REQUIRE(dst_row_offset >= 0 && dst_row_offset % kRowGranule == 0,
              "repack_into: row offset %d not a multiple of 16", dst_row_offset);
   W4_REQUIRE(dst_row_offset + out_f <= w->out_f, "repack_into: rows [%d,%d) exceed out_f %d",
              dst_row_offset, dst_row_offset + out_f, w->out_f);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int KB = w->in_f / kStepK;
   uint8_t* stream_base = reinterpret_cast<uint8_t*>(w->qweight);
-  const long long nq = static_cast<long long>(out_f / kRowBlock) * KB * 32;
+  const long long nq = static_cast<long long>(out_f) * (w->in_f / 32);
   k_repack_q<<<grid_for(nq, 256), 256, 0, st>>>(stream_base, packed, out_f, w->in_f / 8, w->num_groups,
                                                 dst_row_offset);
   const long long ns = static_cast<long long>(out_f) * w->num_groups;
@@ -273,7 +260,7 @@ int w4a16_dequant_rows(uint16_t* dst, const w4a16_weights_t* w, int row0, int nr
   W4_REQUIRE(row0 >= 0 && nrows >= 0 && row0 + nrows <= w->out_f, "dequant_rows: rows [%d,%d) outside [0,%d)",
              row0, row0 + nrows, w->out_f);
   if (nrows == 0) return W4A16_OK;
-  const long long n = static_cast<long long>(nrows) * (w->in_f / kStepK) * 4;
+  const long long n = static_cast<long long>(nrows) * (w->in_f / 32);
   k_dequant_rows<<<grid_for(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       dst, reinterpret_cast<const uint8_t*>(w->qweight), row0, nrows, w->in_f, w->num_groups);
   W4_CUDA(cudaGetLastError());
