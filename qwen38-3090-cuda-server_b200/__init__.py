@@ -15,7 +15,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.environ.get("W4A16_LIB_PATH") or os.path.join(_HERE, "libw4a16_b200.so")
+LIB_PATH = os.path.join(_HERE, "libw4a16_b200.so")
 HEADER_PATH = os.path.join(os.path.dirname(_HERE), "include", "w4a16_b200.h")
 
 

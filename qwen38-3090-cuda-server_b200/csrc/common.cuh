@@ -44,7 +44,7 @@ int check_weights(const w4a16_weights_t* w);
 // ------------------------------------------------------------------ layout
 // Private weight layout ("stream"), group size 128. The matrix is cut into row tiles of 128
 // output rows; for every (row tile, k group) the stream holds one 8576-byte block:
-//     [4 k-chunks of 32][128 rows] uint4   8192 B   packed int4, one thread-load per (row, 32 k)
+//     [4 k-chunks of 32][128 slots] uint4  8192 B   packed int4; row r of chunk c sits in slot weight_slot(r, c)
 //     [128 rows] bf16 scale                  256 B
 //     [128 rows] u8 zero point (raw nibble)  128 B
 // Blocks are ordered [row tile][group], so consecutive groups of a tile follow each other and
@@ -66,6 +66,11 @@ __host__ __device__ inline size_t stream_bytes(int out_f, int G) {
 __host__ __device__ inline size_t tile_group_offset(int o, int g, int G) {
   return (static_cast<size_t>(o / kTileRows) * G + g) * kTileGroupBytes;
 }
+// 16-byte slot of row r (0..127) inside 32-k chunk c of a block: rows of odd chunks are rotated by
+// four slots, so that a thread which reads 8 bytes of two neighbouring chunks (the mma.sync
+// fragment pattern) and a thread which reads its own row's 16 bytes (the tcgen05 pattern) are
+// both free of shared-memory bank conflicts.
+__host__ __device__ inline int weight_slot(int r, int c) { return (r + 4 * (c & 1)) & (kTileRows - 1); }
 // nibble position inside a packed word for k-offset c (0..7)
 __host__ __device__ inline int nib_pos(int c) { return (c >> 1) + 4 * (c & 1); }
 

@@ -6,28 +6,28 @@
 // and k_gemm_mma of the reference (src/kernels/gemv_w4a16.cu:74-279,673-865) and,
 // for lm_head, the separate argmax kernels (src/kernels/elementwise.cu:96-194).
 //
-// The path is HBM-bound (every weight byte is read exactly once); what limits a
-// straightforward port is instruction issue, and on this part the legacy
-// mma.sync pipe in particular (measured: ~3 TB/s ceiling). So the multiply runs
-// on the 5th-generation tensor core with the weights as the TMEM-resident A
-// operand:
+// Shape of the computation (HBM-bound: every weight byte is read exactly once):
 //   * persistent grid, two CTAs per SM. The (128-row tile, k group) units of the
 //     matrix are dealt out as equal contiguous ranges, so every CTA streams the same
 //     number of bytes whatever N and K are. A row tile whose K range is shared by
-//     several CTAs is finished by the last CTA to arrive, which adds the partial tiles
-//     in a fixed order (bitwise reproducible, no float atomics). Shared tiles are
-//     processed FIRST, so that reduction overlaps everybody's main loop.
+//     several CTAs is finished by the last warp to arrive for its rows, which adds the
+//     partial tiles in a fixed order (bitwise reproducible, no float atomics). Shared
+//     tiles are processed FIRST and each warp publishes its rows without any CTA-wide
+//     barrier, so that reduction overlaps everybody's main loop.
 //   * warp roles: a weight producer streams the CTA's contiguous share of the weight
 //     stream through a ring of shared-memory stages with 1-D bulk async copies
-//     (cp.async.bulk + mbarrier); it does not wait for the previous kernel
-//     (programmatic dependent launch), so one layer's weights start flowing while the
-//     previous layer drains. An activation warp stages x as the K-major B operand.
-//     Four consumer warps own one output row per thread: 16 bytes of packed int4 ->
-//     bf16 (128+q) pairs with one LOP3 per two weights, an exact packed bf16 subtract
-//     of (128+zp), then tcgen05.st into tensor memory. One thread issues
-//     tcgen05.mma (M=128 rows, N=16 tokens, K=16) per 16-k slab with A from TMEM and
-//     commits to an mbarrier; the consumers read the fp32 group sums back with
-//     tcgen05.ld and apply the group scale:  y += s * sum((q - zp) x).
+//     (cp.async.bulk + mbarrier full/empty pairs); it does not wait for the previous
+//     kernel (programmatic dependent launch), so one layer's weights start flowing
+//     while the previous layer drains. An activation warp bulk-copies the token rows
+//     and reduces them to per-(group, token) sums on the tensor core. Eight consumer
+//     warps own 16 output rows each: nibbles become bf16 (128+q) pairs with one LOP3
+//     per two weights and go from registers into mma.sync m16n8k16 (bf16 x bf16 ->
+//     fp32); per group  y += s * (sum((128+q) x) - (128+zp) * sum(x)).
+//   * measured on B200: the legacy mma.sync pipe sustains about one m16n8k16 per 32
+//     cycles per scheduler, which caps this formulation near 4.5 TB/s (M <= 8). The
+//     same data path with the weights as a TMEM-resident tcgen05 operand removes that
+//     cap but is sync-latency bound today (2.2 TB/s); it shares the weight stream
+//     layout with the prefill kernel, so it can replace this loop once it is faster.
 #include <cfloat>
 #include <climits>
 #include <cstdlib>
@@ -38,29 +38,18 @@
 namespace w4a16 {
 namespace {
 
-constexpr int CW = 8;                                 // consumer warps: 128 rows x 2 k-halves, one row per thread
-constexpr int kWarps = CW + 4;                        // + weight producer, 2 MMA issuers, activation warp
-constexpr int NCT = CW * 32;                          // consumer threads
-constexpr int kRowWarps = 4;                          // warps per k-half = TMEM lane quadrants
+constexpr int CW = 8;                                 // consumer warps per CTA: 16 rows of the 128-row tile each
+constexpr int kWarps = CW + 2;                        // + weight producer warp + activation warp
 constexpr int kItemGroups = 2;                        // k groups per weight ring stage
-constexpr int kStageBytes = kItemGroups * kTileGroupBytes;  // 17152
+constexpr int kStageBytes = kItemGroups * kTileGroupBytes;  // 17152: two (tile, group) blocks
 static_assert(kStageBytes % 128 == 0, "ring stages must stay 128-byte aligned");
 constexpr int kXBufs = 3;                             // activation chunk buffers
-constexpr int kXGroupBytes = 4096;                    // B operand of one k group: 16 slabs(8 k) x 16 tokens x 16 B
 constexpr int kFirstChunk = 2;                        // groups in a CTA's first activation chunk (short start-up)
-constexpr int kMaxChunkGroups = 8;
-constexpr int kTokens = 16;                           // N of the MMA
-#ifndef W4A16_NB
-#define W4A16_NB 3
-#endif
-constexpr int NB = W4A16_NB;                          // groups in flight in tensor memory
-constexpr uint32_t kTmemCols = NB <= 3 ? 256 : 512;   // allocation: A NB x 64 columns, D NB x 16 columns
-constexpr uint32_t kTmemA = 0, kTmemD = NB * 64;
-static_assert(NB * 80 <= 512, "tensor memory budget");
-constexpr int kMinCtas = NB <= 3 ? 2 : 1;
+constexpr int kMaxChunkGroups = 32;                   // bound on groups per activation chunk
 constexpr uint32_t kSpinLimit = 1u << 20;             // polls before a wait gives up
 constexpr uint32_t kMagic = 0x43004300u;              // bf16 pair (128.0, 128.0)
 constexpr uint32_t kNibMask = 0x000F000Fu;
+constexpr uint32_t kOnes = 0x3F803F80u;               // bf16 pair (1.0, 1.0)
 constexpr int kConsumerBar = 1;                       // named barrier of the consumer warps
 
 struct SkinnyParams {
@@ -72,16 +61,16 @@ struct SkinnyParams {
   int y_col0;     // first column of this launch's rows inside y
   int M, N, K, G, tiles;
   int chunk_groups;  // k groups per activation chunk (even)
+  int xrow_bytes;    // bytes between token rows inside an activation buffer
+  int xbuf_bytes;    // bytes of one activation buffer
   float* partial;
-  unsigned* counters;  // [tiles * 4 + 1], zero between launches
+  unsigned* counters;  // [tiles * 8 + 1], zero between launches
   int argmax;
   int32_t* ids;
   void* pairs_out;  // M x {float,int}
   int row_offset;
   void* cta_pairs;  // [grid][16] x {float,int}
   int* status;
-  unsigned long long* dbg;  // TEMP: per-CTA timestamps
-  int debug_skip;           // TEMP
   int npeers;  // extra destinations for y (fused all-gather), 0 = none
   uint16_t* y_peers[8];
 };
@@ -99,7 +88,7 @@ __device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
 // Row tiles that this CTA shares with a neighbour come first (the piece at the end of the
 // range, then the piece at its start), whole tiles after, so the cross-CTA reduction of the
 // shared tiles overlaps everybody's main loop instead of sitting at the end of the kernel.
-// Every role (weight producer, activation warp, MMA issuer, consumers) runs the same iterator.
+// Every role (weight producer, activation warp, consumers) runs the same iterator.
 struct Chunk {
   int tile, g, n;      // row tile, first group, number of groups (<= chunk_groups)
   int seg_g0, seg_g1;  // the segment this chunk belongs to: groups [seg_g0, seg_g1) of `tile`
@@ -170,38 +159,25 @@ struct WorkIter {
 };
 
 // dynamic shared memory:
-//   [weight ring D stages][x buffers kXBufs x chunk_groups x 4 KB][half sums 128 x 16 fp32]
-//   [mbarriers][tmem base][flag]
-constexpr int kHalfSumBytes = kTileRows * kTokens * 4 + NB * NCT * 4;  // + per-thread scale of each group in flight
-template <int D>
-__host__ __device__ constexpr int skinny_bar_count() { return 2 * D + 2 * NB + 2 * kXBufs + 1; }
+//   [weight ring D stages][x buffers kXBufs][x sums kXBufs x 32 groups x 16][32 B zeros][mbarriers][flag]
+constexpr int kXsumFloats = kMaxChunkGroups * 16;
 template <int D>
 __host__ __device__ constexpr int skinny_fixed_smem() {
-  return D * kStageBytes + kHalfSumBytes + skinny_bar_count<D>() * 8 + 16;
+  return D * kStageBytes + kXBufs * kXsumFloats * 4 + 32 + (2 * D + 3 * kXBufs) * 8 + 16;
 }
 
-__device__ __forceinline__ unsigned long long gtime() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#define TRACE(role, grp, ev) do { if (p.dbg && blockIdx.x == 7 && lane == 0 && (grp) < 24) p.dbg[4096 + ((role) * 24 + (grp)) * 4 + (ev)] = clock64(); } while (0)
-#define DBG_T(i) do { if (p.dbg && tid == 0) p.dbg[blockIdx.x * 8 + (i)] = gtime(); } while (0)
-
-// MC = token columns each consumer thread reads back (power of two >= M)
-template <int MC, int D>
-__global__ void __launch_bounds__(kWarps * 32, kMinCtas) k_skinny(const SkinnyParams p) {
+template <int NT, int D>
+__global__ void __launch_bounds__(kWarps * 32, 2) k_skinny(const SkinnyParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  constexpr int SLOT = kTileRows * kTokens;  // floats per partial tile
+  constexpr int SLOT = CW * 16 * 8 * NT;  // floats per partial tile
+  constexpr int NCT = CW * 32;            // consumer threads
 
-  const int XB = p.chunk_groups * kXGroupBytes;
   uint8_t* ring = smem;
   uint8_t* xbuf = ring + D * kStageBytes;
-  float* halfsum = reinterpret_cast<float*>(xbuf + kXBufs * XB);  // [MC][128]: sums of the odd groups
-  float* scs = halfsum + kTileRows * kTokens;  // [NB][consumer thread]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(halfsum) + kHalfSumBytes);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + skinny_bar_count<D>());
-  int* sflag = reinterpret_cast<int*>(tmem_slot + 1);
+  float* xsum = reinterpret_cast<float*>(xbuf + kXBufs * p.xbuf_bytes);
+  uint8_t* zeros = reinterpret_cast<uint8_t*>(xsum + kXBufs * kXsumFloats);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(zeros + 32);
+  int* sflag = reinterpret_cast<int*>(bars + 2 * D + 3 * kXBufs);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = p.G, M = p.M;
@@ -211,44 +187,44 @@ __global__ void __launch_bounds__(kWarps * 32, kMinCtas) k_skinny(const SkinnyPa
 
   const uint32_t ring_a = smem_u32(ring);
   const uint32_t xbuf_a = smem_u32(xbuf);
-  const uint32_t wfull_a = smem_u32(bars);            // [D]  weights landed
-  const uint32_t wempty_a = wfull_a + D * 8;          // [D]  stage free again (8 consumer warps)
-  const uint32_t afull_a = wempty_a + D * 8;          // [NB] A operand of a group is in TMEM (8 consumer warps)
-  const uint32_t mdone_a = afull_a + NB * 8;          // [NB] the group's MMAs have completed: D readable, A reusable
-  const uint32_t xfull_a = mdone_a + NB * 8;          // [kXBufs] activation chunk staged
-  const uint32_t xempty_a = xfull_a + kXBufs * 8;     // [kXBufs] both issuers are done with the chunk
-  const uint32_t alldone_a = xempty_a + kXBufs * 8;   // [1]  consumers are finished with tensor memory
+  const uint32_t wfull_a = smem_u32(bars);        // [D]  weights landed
+  const uint32_t wempty_a = wfull_a + D * 8;      // [D]  stage free again (8 consumer warps)
+  const uint32_t xfull_a = wempty_a + D * 8;      // [kXBufs] activation chunk landed
+  const uint32_t xsfull_a = xfull_a + kXBufs * 8; // [kXBufs] its per-group sums are ready
+  const uint32_t xempty_a = xsfull_a + kXBufs * 8;// [kXBufs] buffer free again (8 consumers + activation warp)
 
-  DBG_T(0);
-  // token rows >= M of every B-operand buffer stay zero for the whole kernel
-  for (int i = tid; i < kXBufs * XB / 16; i += kWarps * 32) reinterpret_cast<uint4*>(xbuf)[i] = make_uint4(0, 0, 0, 0);
-  fence_proxy_async();  // the tensor core reads these buffers through the async proxy
+  if (tid < 8) reinterpret_cast<uint32_t*>(zeros)[tid] = 0u;
   if (tid == 0) {
     for (int i = 0; i < D; ++i) {
       mbar_init(wfull_a + i * 8, 1);
       mbar_init(wempty_a + i * 8, CW);
     }
-    for (int i = 0; i < NB; ++i) {
-      mbar_init(afull_a + i * 8, CW);
-      mbar_init(mdone_a + i * 8, 1);
-    }
     for (int i = 0; i < kXBufs; ++i) {
       mbar_init(xfull_a + i * 8, 1);
-      mbar_init(xempty_a + i * 8, 2);
+      mbar_init(xsfull_a + i * 8, 1);
+      mbar_init(xempty_a + i * 8, CW + 1);
     }
-    mbar_init(alldone_a, CW);
     fence_mbar_init();
   }
-  if (warp == CW + 1) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
-  tc_fence_before();
   __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
   pdl_launch_dependents();
 
+  // B-fragment addressing of a lane: token row 8 nt + lane/4, k offset 16 (lane%4) within a
+  // 64-k step. Lanes whose token row does not exist read a block of zeros (all strides 0).
+  const int grow = lane >> 2, t = lane & 3;
+  uint32_t xlane[NT], xstep[NT], xbufoff[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const int mm = nt * 8 + grow;
+    const bool valid = mm < M;
+    xlane[nt] = valid ? xbuf_a + mm * p.xrow_bytes + t * 32 : smem_u32(zeros);
+    xstep[nt] = valid ? 128 : 0;
+    xbufoff[nt] = valid ? p.xbuf_bytes : 0;
+  }
+
   // ================================================================ weight producer
-  // One thread streams this CTA's share of the weight stream, one stage (two k groups of the
-  // 128-row tile, 17 KB, contiguous in memory) per bulk copy. It does not wait for the
+  // One thread streams this CTA's share of the weight stream, one stage (two k groups of all
+  // eight 16-row blocks, 17 KB, contiguous in memory) per bulk copy. It does not wait for the
   // previous kernel: weights never depend on it.
   if (warp == CW) {
     if (lane == 0) {
@@ -268,8 +244,8 @@ __global__ void __launch_bounds__(kWarps * 32, kMinCtas) k_skinny(const SkinnyPa
           }
           mbar_expect_tx(wfull_a + st * 8, ng * kTileGroupBytes);
           bulk_g2s(ring_a + st * kStageBytes,
-                   p.stream + (static_cast<size_t>(c.tile) * G + c.g + gi) * kTileGroupBytes, ng * kTileGroupBytes,
-                   wfull_a + st * 8);
+                   p.stream + (static_cast<size_t>(c.tile) * G + c.g + gi) * kTileGroupBytes,
+                   ng * kTileGroupBytes, wfull_a + st * 8);
           if (++st == D) {
             st = 0;
             ph ^= 1;
@@ -280,105 +256,63 @@ __global__ void __launch_bounds__(kWarps * 32, kMinCtas) k_skinny(const SkinnyPa
     return;
   }
 
-  // ================================================================ MMA issuers
-  // Two threads (one per warp) take the k groups alternately. Per group: 8 x tcgen05.mma
-  // (128 rows x 16 tokens x 16 k) with A from tensor memory and B (activations) from shared
-  // memory, then a commit that tells the consumers the group's fp32 sums are ready and its A
-  // columns may be overwritten.
-  if (warp == CW + 1 || warp == CW + 2) {
-    const int me = warp - (CW + 1);
-    if (lane == 0) {
-      WorkIter it;
-      it.init(u0, u1, G, p.chunk_groups);
-      Chunk c;
-      constexpr uint32_t idesc = umma_idesc_bf16(kTileRows, kTokens);
-      int xb = 0, b = 0, par = 0, tg = 0;
-      uint32_t xph = 0, bph = 0;
-      bool ok = true;
-      while (ok && it.next(c)) {
-        if (!mbar_wait_bounded(xfull_a + xb * 8, xph, kSpinLimit)) {
-          atomicExch(p.status, W4A16_ETIMEOUT);
-          break;
-        }
-        // descriptor of the chunk's first 16-k slab: 8-k core-matrix columns 256 B apart, token
-        // groups 128 B apart; each following slab starts 512 B (32 descriptor units) later
-        uint64_t bdesc = umma_desc_kmajor(xbuf_a + xb * XB, 256, 128);
-        bool issued = false;
-        for (int gi = 0; gi < c.n; ++gi) {
-          if (par == me) {
-            if (!mbar_wait_bounded(afull_a + b * 8, bph, kSpinLimit)) {
-              atomicExch(p.status, W4A16_ETIMEOUT);
-              ok = false;
-              break;
-            }
-            TRACE(2 + me, tg, 0);
-            tc_fence_after();
-            const uint32_t d_t = tmem + kTmemD + b * kTokens, a_t = tmem + kTmemA + b * 64;
-#ifndef EXP_NOMMA
-            umma_bf16_ts(d_t, a_t, bdesc, idesc, 0);
-#pragma unroll
-            for (int s = 1; s < 8; ++s) umma_bf16_ts(d_t, a_t + s * 8, bdesc + s * 32, idesc, 1);
-#endif
-            umma_commit(mdone_a + b * 8);
-            TRACE(2 + me, tg, 1);
-            issued = true;
-          }
-          ++tg;
-          bdesc += 8 * 32;
-          par ^= 1;
-          if (++b == NB) {
-            b = 0;
-            bph ^= 1;
-          }
-        }
-        // the chunk buffer is free once both issuers' MMAs on it have completed
-        if (issued) umma_commit(xempty_a + xb * 8);
-        else mbar_arrive(xempty_a + xb * 8);
-        if (++xb == kXBufs) {
-          xb = 0;
-          xph ^= 1;
-        }
-      }
-    }
-    __syncwarp();
-    if (me == 0) {
-      // tensor memory goes back only after every consumer has read its last sums
-      mbar_wait_bounded_relaxed(alldone_a, 0, kSpinLimit);
-      tc_fence_after();
-      tmem_dealloc(tmem, kTmemCols);
-    }
-    return;
-  }
-
   // ================================================================ activation warp
-  // Waits for the previous kernel (it produced x), then stages x chunk by chunk as the
-  // K-major B operand: core matrices of 8 tokens x 8 k (16 B per token row), laid out
-  // [8-k slab][token group of 8][token][16 B].
-  if (warp == CW + 3) {
+  // Waits for the previous kernel (it produced x), then per chunk: bulk-copies the token rows,
+  // and turns them into per-(group, token) sums with the tensor core (ones(16x16) * X).
+  if (warp == CW + 1) {
     pdl_wait();
     WorkIter it;
     it.init(u0, u1, G, p.chunk_groups);
     Chunk c;
     int xb = 0;
-    uint32_t eph = 1;
+    uint32_t fph = 0, eph = 1;
     while (it.next(c)) {
       if (!mbar_wait_bounded_relaxed(xempty_a + xb * 8, eph, kSpinLimit)) {
         atomicExch(p.status, W4A16_ETIMEOUT);
         break;
       }
-      const int pieces = c.n * 16 * M;  // 16-byte pieces: (8-k slab, token)
-      for (int i = lane; i < pieces; i += 32) {
-        const int m = i % M, kc = i / M;
-        cp_async16(xbuf_a + xb * XB + kc * 256 + (m >> 3) * 128 + (m & 7) * 16,
-                   p.x + static_cast<size_t>(m) * p.K + c.g * kGroup + kc * 8);
+      if (lane == 0) {
+        mbar_expect_tx(xfull_a + xb * 8, M * c.n * 256);
+        for (int m = 0; m < M; ++m)
+          bulk_g2s(xbuf_a + xb * p.xbuf_bytes + m * p.xrow_bytes,
+                   p.x + static_cast<size_t>(m) * p.K + c.g * kGroup, c.n * 256, xfull_a + xb * 8);
       }
-      cp_async_commit();
-      cp_async_wait_all();
-      fence_proxy_async();  // generic-proxy writes -> visible to the tensor core's async-proxy reads
+      if (!mbar_wait_bounded(xfull_a + xb * 8, fph, kSpinLimit)) {
+        atomicExch(p.status, W4A16_ETIMEOUT);
+        break;
+      }
+      for (int gl = 0; gl < c.n; ++gl) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          float ax[4][4];
+          const uint8_t* xa = smem + (xlane[nt] - ring_a) + xb * xbufoff[nt] + gl * 2 * xstep[nt];
+          const uint4 b0 = *reinterpret_cast<const uint4*>(xa);
+          const uint4 b1 = *reinterpret_cast<const uint4*>(xa + 16);
+          const uint4 b2 = *reinterpret_cast<const uint4*>(xa + xstep[nt]);
+          const uint4 b3 = *reinterpret_cast<const uint4*>(xa + xstep[nt] + 16);
+          mma_bf16_16816_zero(ax[0], kOnes, kOnes, kOnes, kOnes, b0.x, b0.y);
+          mma_bf16_16816_zero(ax[1], kOnes, kOnes, kOnes, kOnes, b1.x, b1.y);
+          mma_bf16_16816_zero(ax[2], kOnes, kOnes, kOnes, kOnes, b2.x, b2.y);
+          mma_bf16_16816_zero(ax[3], kOnes, kOnes, kOnes, kOnes, b3.x, b3.y);
+          mma_bf16_16816(ax[0], kOnes, kOnes, kOnes, kOnes, b0.z, b0.w);
+          mma_bf16_16816(ax[1], kOnes, kOnes, kOnes, kOnes, b1.z, b1.w);
+          mma_bf16_16816(ax[2], kOnes, kOnes, kOnes, kOnes, b2.z, b2.w);
+          mma_bf16_16816(ax[3], kOnes, kOnes, kOnes, kOnes, b3.z, b3.w);
+          if (grow == 0) {
+            float* xs = xsum + xb * kXsumFloats + gl * 16 + nt * 8 + 2 * t;
+            xs[0] = (ax[0][0] + ax[1][0]) + (ax[2][0] + ax[3][0]);
+            xs[1] = (ax[0][1] + ax[1][1]) + (ax[2][1] + ax[3][1]);
+          }
+        }
+      }
       __syncwarp();
-      if (lane == 0) mbar_arrive(xfull_a + xb * 8);
+      if (lane == 0) {
+        mbar_arrive(xsfull_a + xb * 8);  // sums published
+        mbar_arrive(xempty_a + xb * 8);  // this warp no longer reads the chunk
+      }
       if (++xb == kXBufs) {
         xb = 0;
+        fph ^= 1;
         eph ^= 1;
       }
     }
@@ -386,81 +320,115 @@ __global__ void __launch_bounds__(kWarps * 32, kMinCtas) k_skinny(const SkinnyPa
   }
 
   // ================================================================ consumer warps
-  // thread = one output row of the 128-row tile (TMEM lane 32 * (warp % 4) + lane) and one half
-  // of every k group: warps 0-3 unpack k 0..63, warps 4-7 k 64..127. The fp32 sums of a group
-  // are folded by the half whose index equals the group's parity, so both halves carry a partial
-  // sum that is combined once per row tile.
-  const int q = warp & (kRowWarps - 1), h = warp / kRowWarps;
-  const int row = q * 32 + lane;
-  const uint32_t tlane = static_cast<uint32_t>(q * 32) << 16;
+  // Byte offsets of this lane's 8-byte weight pieces inside a (tile, group) block: chunk t/2 of
+  // the step, the slot of its row (rotated by four slots in odd chunks, which keeps the 8-byte
+  // loads of a half-warp on distinct banks), half t%2 of the slot.
+  const int wrow = warp * 16 + grow;
+  const int woff_lo = (t >> 1) * kChunkBytes + weight_slot(wrow, t >> 1) * 16 + (t & 1) * 8;
+  const int woff_hi = (t >> 1) * kChunkBytes + weight_slot(wrow + 8, t >> 1) * 16 + (t & 1) * 8;
 
-  float fin[MC];
+  float fin[NT][4];
 #pragma unroll
-  for (int m = 0; m < MC; ++m) fin[m] = 0.f;
-  float best_v[MC];
-  int best_i[MC];
+  for (int nt = 0; nt < NT; ++nt) fin[nt][0] = fin[nt][1] = fin[nt][2] = fin[nt][3] = 0.f;
+
+  float best_v[NT][2];
+  int best_i[NT][2];
 #pragma unroll
-  for (int m = 0; m < MC; ++m) {
-    best_v[m] = -FLT_MAX;
-    best_i[m] = INT_MAX;
-  }
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      best_v[nt][c] = -FLT_MAX;
+      best_i[nt][c] = INT_MAX;
+    }
 
   // Final values of one row tile are in registers: write them out / fold into the argmax.
-  auto finalize = [&](int tile, const float (&v)[MC]) {
-    const int r = tile * kTileRows + row;
-    if (r >= p.N) return;
+  auto finalize = [&](int tile, const float (&v)[NT][4]) {
+    const int rb = tile * CW + warp;
+    if (rb * 16 >= p.N) return;  // zero-padded rows of the last tile
 #pragma unroll
-    for (int m = 0; m < MC; ++m) {
-      if (m >= M) continue;
-      const uint16_t hb = float_to_bf16_bits(v[m]);
-      if (p.y) {
-        const size_t o = static_cast<size_t>(m) * p.ldy + p.y_col0 + r;
-        if (p.y_f32) static_cast<float*>(p.y)[o] = v[m];
-        else static_cast<uint16_t*>(p.y)[o] = hb;
-        for (int qq = 0; qq < p.npeers; ++qq) p.y_peers[qq][o] = hb;
-      }
-      if (p.argmax) {
-        const float lv = bf16_bits_to_float(hb);
-        if (better(lv, r, best_v[m], best_i[m])) {
-          best_v[m] = lv;
-          best_i[m] = r;
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int m = nt * 8 + 2 * t + (j & 1);
+        const int r = rb * 16 + grow + 8 * (j >> 1);
+        if (m >= M) continue;
+        const uint16_t hb = float_to_bf16_bits(v[nt][j]);
+        if (p.y) {
+          const size_t o = static_cast<size_t>(m) * p.ldy + p.y_col0 + r;
+          if (p.y_f32) static_cast<float*>(p.y)[o] = v[nt][j];
+          else static_cast<uint16_t*>(p.y)[o] = hb;
+          for (int q = 0; q < p.npeers; ++q) p.y_peers[q][o] = hb;
+        }
+        if (p.argmax) {
+          const float lv = bf16_bits_to_float(hb);
+          if (better(lv, r, best_v[nt][j & 1], best_i[nt][j & 1])) {
+            best_v[nt][j & 1] = lv;
+            best_i[nt][j & 1] = r;
+          }
         }
       }
-    }
   };
 
-  bool dead = false;
-  // Groups in flight in tensor memory: buffers are used round-robin, `ob` is the oldest one.
-  // sc0..sc2 = this row's scale of the group in each buffer, par0..2 = that group's parity.
-  int npend = 0, b = 0, ob = 0, gpar = 0, opar = 0;
-  uint32_t oph = 0;
-  // The oldest group in flight has completed: its A columns may be overwritten, and the half
-  // responsible for it folds its sums: y += s * sum((q-zp) x).
-  auto retire_oldest = [&]() {
-    if (!dead && !mbar_wait_bounded(mdone_a + ob * 8, oph, kSpinLimit)) {
-      dead = true;
-      atomicExch(p.status, W4A16_ETIMEOUT);
-    }
-    if (opar == h) {
-      tc_fence_after();
-      float d[MC];
-      tmem_ld<MC>(tmem + tlane + kTmemD + ob * kTokens, d);
-      tmem_wait_ld();
-      const float sc = scs[ob * NCT + tid];
+  // The 8 MMAs per token tile of one 128-k group of this warp's 16 rows, on bf16 (128+q) pairs.
+  // `gb` = the (tile, group) block in the ring. Step s covers k chunks 2s and 2s+1; this lane's 16 k
+  // of the step are one 8-byte half of the 16-byte slot of (row, chunk) for its low and high row.
+  auto group_mma = [&](const uint8_t* gb, const uint8_t* const (&xp)[NT], float (&acc)[NT][2][4]) {
 #pragma unroll
-      for (int m = 0; m < MC; ++m) fin[m] = fmaf(sc, d[m], fin[m]);
+    for (int s = 0; s < 2; ++s) {
+      const uint2 qlo = *reinterpret_cast<const uint2*>(gb + s * (2 * kChunkBytes) + woff_lo);
+      const uint2 qhi = *reinterpret_cast<const uint2*>(gb + s * (2 * kChunkBytes) + woff_hi);
+      const uint4 wq = make_uint4(qlo.x, qlo.y, qhi.x, qhi.y);
+      uint32_t a[4][4];  // [mma][register]: rows (lo, hi, lo, hi) x k pairs
+      a[0][0] = (wq.x & kNibMask) | kMagic;
+      a[0][1] = (wq.z & kNibMask) | kMagic;
+      a[0][2] = ((wq.x >> 4) & kNibMask) | kMagic;
+      a[0][3] = ((wq.z >> 4) & kNibMask) | kMagic;
+      a[1][0] = ((wq.x >> 8) & kNibMask) | kMagic;
+      a[1][1] = ((wq.z >> 8) & kNibMask) | kMagic;
+      a[1][2] = ((wq.x >> 12) & kNibMask) | kMagic;
+      a[1][3] = ((wq.z >> 12) & kNibMask) | kMagic;
+      a[2][0] = (wq.y & kNibMask) | kMagic;
+      a[2][1] = (wq.w & kNibMask) | kMagic;
+      a[2][2] = ((wq.y >> 4) & kNibMask) | kMagic;
+      a[2][3] = ((wq.w >> 4) & kNibMask) | kMagic;
+      a[3][0] = ((wq.y >> 8) & kNibMask) | kMagic;
+      a[3][1] = ((wq.w >> 8) & kNibMask) | kMagic;
+      a[3][2] = ((wq.y >> 12) & kNibMask) | kMagic;
+      a[3][3] = ((wq.w >> 12) & kNibMask) | kMagic;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const uint4 bl = *reinterpret_cast<const uint4*>(xp[nt] + s * xstep[nt]);
+        const uint4 bh = *reinterpret_cast<const uint4*>(xp[nt] + s * xstep[nt] + 16);
+        if (s == 0) {
+          mma_bf16_16816_zero(acc[nt][0], a[0][0], a[0][1], a[0][2], a[0][3], bl.x, bl.y);
+          mma_bf16_16816_zero(acc[nt][1], a[1][0], a[1][1], a[1][2], a[1][3], bl.z, bl.w);
+        } else {
+          mma_bf16_16816(acc[nt][0], a[0][0], a[0][1], a[0][2], a[0][3], bl.x, bl.y);
+          mma_bf16_16816(acc[nt][1], a[1][0], a[1][1], a[1][2], a[1][3], bl.z, bl.w);
+        }
+        mma_bf16_16816(acc[nt][0], a[2][0], a[2][1], a[2][2], a[2][3], bh.x, bh.y);
+        mma_bf16_16816(acc[nt][1], a[3][0], a[3][1], a[3][2], a[3][3], bh.z, bh.w);
+      }
     }
-    --npend;
-    opar ^= 1;
-    if (++ob == NB) {
-      ob = 0;
-      oph ^= 1;
+  };
+  // y += s * (acc - (128 + zp) * sum(x)) for the lane's two rows
+  auto group_fix = [&](const uint8_t* gb, const float* xs, const float (&acc)[NT][2][4]) {
+    const uint16_t* scp = reinterpret_cast<const uint16_t*>(gb + kTgScaleOff) + warp * 16 + grow;
+    const uint8_t* zpp = gb + kTgZpOff + warp * 16 + grow;
+    const float s_lo = bf16_bits_to_float(scp[0]), s_hi = bf16_bits_to_float(scp[8]);
+    const float z_lo = __uint_as_float(__byte_perm(zpp[0], 0x43000000u, 0x7044));  // 128 + zp, low row
+    const float z_hi = __uint_as_float(__byte_perm(zpp[8], 0x43000000u, 0x7044));  // high row
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const float2 x2 = *reinterpret_cast<const float2*>(xs + nt * 8 + 2 * t);
+      fin[nt][0] = fmaf(s_lo, fmaf(-z_lo, x2.x, acc[nt][0][0] + acc[nt][1][0]), fin[nt][0]);
+      fin[nt][1] = fmaf(s_lo, fmaf(-z_lo, x2.y, acc[nt][0][1] + acc[nt][1][1]), fin[nt][1]);
+      fin[nt][2] = fmaf(s_hi, fmaf(-z_hi, x2.x, acc[nt][0][2] + acc[nt][1][2]), fin[nt][2]);
+      fin[nt][3] = fmaf(s_hi, fmaf(-z_hi, x2.y, acc[nt][0][3] + acc[nt][1][3]), fin[nt][3]);
     }
   };
 
-  // Split tiles: each row-warp publishes its 32 rows on its own and moves on; whichever warp
-  // turns out to be the last contributor of its rows adds the pieces up at the end of the kernel.
-  // (tile, first/last contributing CTA, arrival ticket) of up to two split tiles, in lane 0.
+  // (tile, first/last contributing CTA, arrival ticket) of up to two split tiles, in lane 0
   int sp_n = 0, sp_tile0 = 0, sp_cf0 = 0, sp_cl0 = 0, sp_tile1 = 0, sp_cf1 = 0, sp_cl1 = 0;
   unsigned sp_old0 = 0, sp_old1 = 0;
   bool waited_pdl = false;
@@ -474,218 +442,192 @@ __global__ void __launch_bounds__(kWarps * 32, kMinCtas) k_skinny(const SkinnyPa
   WorkIter it;
   it.init(u0, u1, G, p.chunk_groups);
   Chunk c;
-  int wst = 0, tg = 0;
-  uint32_t wph = 0;
-  bool first_chunk = true;
+  int wst = 0, xb = 0;
+  uint32_t wph = 0, xph = 0;
+  bool dead = false;
 
   while (it.next(c)) {
-    for (int gi = 0; gi < c.n; ++gi) {
-      if ((gi & 1) == 0) {
-        if (!dead && !mbar_wait_bounded(wfull_a + wst * 8, wph, kSpinLimit)) {
-          dead = true;
-          atomicExch(p.status, W4A16_ETIMEOUT);
+    // ---- one activation chunk: groups [c.g, c.g + c.n) of row tile c.tile ----
+    if (!dead && !mbar_wait_bounded(xfull_a + xb * 8, xph, kSpinLimit)) {
+      dead = true;
+      atomicExch(p.status, W4A16_ETIMEOUT);
+    }
+    const uint8_t* xchunk[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) xchunk[nt] = smem + (xlane[nt] - ring_a) + xb * xbufoff[nt];
+    const float* xs = xsum + xb * kXsumFloats;
+    bool sums_ready = false;
+
+    for (int gi = 0; gi < c.n; gi += kItemGroups) {
+      if (!dead && !mbar_wait_bounded(wfull_a + wst * 8, wph, kSpinLimit)) {
+        dead = true;
+        atomicExch(p.status, W4A16_ETIMEOUT);
+      }
+      const uint8_t* up = ring + wst * kStageBytes;
+      {
+        float acc0[NT][2][4], acc1[NT][2][4];
+        const uint8_t* xp[NT];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) xp[nt] = xchunk[nt] + gi * 2 * xstep[nt];
+        const bool two = gi + 1 < c.n;
+        group_mma(up, xp, acc0);
+        if (two) {
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) xp[nt] += 2 * xstep[nt];
+          group_mma(up + kTileGroupBytes, xp, acc1);
         }
-        if (first_chunk) DBG_T(2);
-        first_chunk = false;
-      }
-      if (q == 0) TRACE(h, tg, 0);
-      const uint8_t* blk = ring + wst * kStageBytes + (gi & 1) * kTileGroupBytes;
-      const uint32_t zp = blk[kTgZpOff + row];
-      const uint32_t zpair = __byte_perm(zp, 0x43434343u, 0x4040);  // bf16 pair (128+zp, 128+zp)
-      if (gpar == h) {
-        scs[b * NCT + tid] = bf16_bits_to_float(reinterpret_cast<const uint16_t*>(blk + kTgScaleOff)[row]);
-      }
-      if (p.debug_skip != 1) {
-#pragma unroll
-        for (int jj = 0; jj < 2; ++jj) {
-          const int j = 2 * h + jj;  // 32-k chunk of the group
-          const uint4 wq = *reinterpret_cast<const uint4*>(blk + j * kChunkBytes + row * 16);
-          const uint32_t w[4] = {wq.x, wq.y, wq.z, wq.w};
-          uint32_t a[16];
-#ifdef EXP_NOUNPACK
-#pragma unroll
-          for (int i = 0; i < 16; ++i) a[i] = w[i & 3] ^ zpair;
-#else
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            a[4 * i + 0] = sub_bf16x2((w[i] & kNibMask) | kMagic, zpair);
-            a[4 * i + 1] = sub_bf16x2(((w[i] >> 4) & kNibMask) | kMagic, zpair);
-            a[4 * i + 2] = sub_bf16x2(((w[i] >> 8) & kNibMask) | kMagic, zpair);
-            a[4 * i + 3] = sub_bf16x2(((w[i] >> 12) & kNibMask) | kMagic, zpair);
+        if (!sums_ready) {
+          if (!dead && !mbar_wait_bounded(xsfull_a + xb * 8, xph, kSpinLimit)) {
+            dead = true;
+            atomicExch(p.status, W4A16_ETIMEOUT);
           }
-#endif
-#ifdef EXP_NOST
-#pragma unroll
-          for (int i = 0; i < 16; ++i) asm volatile("" ::"r"(a[i]));
-#else
-          tmem_st16(tmem + tlane + kTmemA + b * 64 + j * 16, a);
-#endif
+          sums_ready = true;
         }
+        group_fix(up, xs + gi * 16, acc0);
+        if (two) group_fix(up + kTileGroupBytes, xs + (gi + 1) * 16, acc1);
       }
-      // While this group's stores drain into tensor memory, retire the oldest group that is
-      // still in flight (its MMAs were issued two groups ago); that also frees the buffer the
-      // next group will be written to.
-      if (q == 0) TRACE(h, tg, 1);
-      if (npend == NB - 1) retire_oldest();
-      if (q == 0) TRACE(h, tg, 2);
-      tmem_wait_st();
-      tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(afull_a + b * 8);  // this warp's share of the A operand is in place
-      if (q == 0) TRACE(h, tg, 3);
-      ++tg;
-      ++npend;
-      gpar ^= 1;
-      if (++b == NB) b = 0;
-      if ((gi & 1) == 1 || gi == c.n - 1) {
-        if (lane == 0) mbar_arrive(wempty_a + wst * 8);  // (ordered after every lane's reads by the __syncwarp)
-        if (++wst == D) {
-          wst = 0;
-          wph ^= 1;
-        }
+      if (lane == 0) mbar_arrive(wempty_a + wst * 8);  // this warp is done with the stage
+      if (++wst == D) {
+        wst = 0;
+        wph ^= 1;
       }
+    }
+    if (lane == 0) mbar_arrive(xempty_a + xb * 8);  // (the __syncwarp above ordered every lane's reads)
+    if (++xb == kXBufs) {
+      xb = 0;
+      xph ^= 1;
     }
 
     if (c.seg_last) {
       // ---- end of this CTA's segment of row tile c.tile: groups [seg_g0, seg_g1) ----
-      while (npend) retire_oldest();
-      // combine the two halves' sums: odd-group sums travel through shared memory
-      if (h == 1) {
+      before_global_write();
+      const int tile = c.tile;
+      if (c.seg_g0 == 0 && c.seg_g1 == G) {
+        finalize(tile, fin);
+      } else {
+        // split tile: this warp publishes its 16 rows and moves on; no CTA-wide barrier
+        const long long X0 = static_cast<long long>(tile) * G;
+        const int c_first = static_cast<int>(((X0 + 1) * gridDim.x - 1) / U);
+        const int c_last = static_cast<int>(((X0 + G) * gridDim.x - 1) / U);
+        const int which = (u0 / G == tile) ? 0 : 1;
+        float* slot = p.partial + (static_cast<size_t>(blockIdx.x) * 2 + which) * SLOT;
 #pragma unroll
-        for (int m = 0; m < MC; ++m) halfsum[m * kTileRows + row] = fin[m];
-      }
-      named_bar_sync(kConsumerBar, NCT);
-      if (h == 0) {
+        for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int m = 0; m < MC; ++m) fin[m] += halfsum[m * kTileRows + row];
-      }
-      named_bar_sync(kConsumerBar, NCT);  // halfsum may be rewritten by the next segment
-      if (h == 0) {
-        before_global_write();
-        const int tile = c.tile;
-        if (c.seg_g0 == 0 && c.seg_g1 == G) {
-          finalize(tile, fin);
-        } else {
-          const long long X0 = static_cast<long long>(tile) * G;
-          const int c_first = static_cast<int>(((X0 + 1) * gridDim.x - 1) / U);
-          const int c_last = static_cast<int>(((X0 + G) * gridDim.x - 1) / U);
-          const int which = (u0 / G == tile) ? 0 : 1;
-          float* slot = p.partial + (static_cast<size_t>(blockIdx.x) * 2 + which) * SLOT;
-#pragma unroll
-          for (int m = 0; m < MC; ++m) slot[m * kTileRows + row] = fin[m];
-          __syncwarp();
-          if (lane == 0) {
-            __threadfence();  // release: this warp's partial rows (ordered by the __syncwarp) before the ticket
-            const unsigned old = atomicAdd(p.counters + tile * kRowWarps + q, 1u);
-            if (sp_n == 0) {
-              sp_tile0 = tile; sp_cf0 = c_first; sp_cl0 = c_last; sp_old0 = old;
-            } else {
-              sp_tile1 = tile; sp_cf1 = c_first; sp_cl1 = c_last; sp_old1 = old;
-            }
-            ++sp_n;
+          for (int j = 0; j < 4; ++j)
+            slot[(warp * 16 + grow + 8 * (j >> 1)) * 8 * NT + nt * 8 + 2 * t + (j & 1)] = fin[nt][j];
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence();  // release: this warp's partial rows (ordered by the __syncwarp) before the ticket
+          const unsigned old = atomicAdd(p.counters + tile * CW + warp, 1u);
+          if (sp_n == 0) {
+            sp_tile0 = tile; sp_cf0 = c_first; sp_cl0 = c_last; sp_old0 = old;
+          } else {
+            sp_tile1 = tile; sp_cf1 = c_first; sp_cl1 = c_last; sp_old1 = old;
           }
+          ++sp_n;
         }
       }
 #pragma unroll
-      for (int m = 0; m < MC; ++m) fin[m] = 0.f;
+      for (int nt = 0; nt < NT; ++nt) fin[nt][0] = fin[nt][1] = fin[nt][2] = fin[nt][3] = 0.f;
     }
   }
-  DBG_T(3);
-
-  // tensor memory is no longer read by this warp
-  tc_fence_before();
-  __syncwarp();
-  if (lane == 0) mbar_arrive(alldone_a);
-
-  if (dead) {  // let whatever is still in flight land before the CTA exits
-    for (int s = 0; s < D; ++s) mbar_wait_bounded(wfull_a + s * 8, 0, 1u << 16);
-  }
-  if (h == 1 && !p.argmax) return;
 
   // ---- split tiles: the warp that drew the last ticket for its rows adds the pieces up ----
-  if (h == 0) {
+  {
     const int n = __shfl_sync(0xffffffffu, sp_n, 0);
     for (int i = 0; i < n; ++i) {
       const int tile = __shfl_sync(0xffffffffu, i ? sp_tile1 : sp_tile0, 0);
       const int c_first = __shfl_sync(0xffffffffu, i ? sp_cf1 : sp_cf0, 0);
       const int c_last = __shfl_sync(0xffffffffu, i ? sp_cl1 : sp_cl0, 0);
       const unsigned old = __shfl_sync(0xffffffffu, i ? sp_old1 : sp_old0, 0);
-      if (old != static_cast<unsigned>(c_last - c_first)) continue;  // someone else finishes these rows
+      if (old != static_cast<unsigned>(c_last - c_first)) continue;  // another warp finishes these rows
       if (lane == 0) {
-        p.counters[tile * kRowWarps + q] = 0;  // every contributor has arrived: leave it clean
-        __threadfence();                       // acquire side for the reads below
+        p.counters[tile * CW + warp] = 0;  // every contributor has arrived: leave it clean
+        __threadfence();                   // acquire side for the reads below
       }
       __syncwarp();
-      float v[MC];
+      float v[NT][4];
 #pragma unroll
-      for (int m = 0; m < MC; ++m) v[m] = 0.f;
+      for (int nt = 0; nt < NT; ++nt) v[nt][0] = v[nt][1] = v[nt][2] = v[nt][3] = 0.f;
       for (int cc = c_first; cc <= c_last; ++cc) {  // fixed order: bitwise reproducible
         const int cu0 = static_cast<int>(static_cast<long long>(U) * cc / gridDim.x);
         const int wc = (cu0 / G == tile) ? 0 : 1;
         const float* sl = p.partial + (static_cast<size_t>(cc) * 2 + wc) * SLOT;
 #pragma unroll
-        for (int m = 0; m < MC; ++m) v[m] += __ldcg(sl + m * kTileRows + row);
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            v[nt][j] += __ldcg(sl + (warp * 16 + grow + 8 * (j >> 1)) * 8 * NT + nt * 8 + 2 * t + (j & 1));
       }
       finalize(tile, v);
     }
   }
 
+  if (dead) {  // let whatever is still in flight land before the CTA exits
+    for (int s = 0; s < D; ++s) mbar_wait_bounded(wfull_a + s * 8, 0, 1u << 16);
+  }
+
   if (p.argmax) {
-    // ---- fused argmax: thread -> warp -> CTA -> grid, larger value then lower index ----
-    // (only the h == 0 warps hold candidates; the others carry the neutral element)
     before_global_write();
+    // ---- fused argmax: thread -> warp -> CTA -> grid, larger value then lower index ----
 #pragma unroll
-    for (int m = 0; m < MC; ++m)
+    for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-      for (int off = 16; off > 0; off >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best_v[m], off);
-        const int oi = __shfl_xor_sync(0xffffffffu, best_i[m], off);
-        if (better(ov, oi, best_v[m], best_i[m])) {
-          best_v[m] = ov;
-          best_i[m] = oi;
+      for (int cc = 0; cc < 2; ++cc)
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+          const float ov = __shfl_xor_sync(0xffffffffu, best_v[nt][cc], off);
+          const int oi = __shfl_xor_sync(0xffffffffu, best_i[nt][cc], off);
+          if (better(ov, oi, best_v[nt][cc], best_i[nt][cc])) {
+            best_v[nt][cc] = ov;
+            best_i[nt][cc] = oi;
+          }
         }
-      }
     named_bar_sync(kConsumerBar, NCT);
     // per-warp candidates go through the (now idle) weight ring: every stage was consumed
     Pair* cand = reinterpret_cast<Pair*>(ring);  // [CW][16]
-    if (lane == 0) {
+    if (grow == 0) {
 #pragma unroll
-      for (int m = 0; m < MC; ++m) cand[warp * 16 + m] = Pair{best_v[m], best_i[m]};
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) cand[warp * 16 + nt * 8 + 2 * t + cc] = Pair{best_v[nt][cc], best_i[nt][cc]};
     }
     named_bar_sync(kConsumerBar, NCT);
     Pair* cta_pairs = static_cast<Pair*>(p.cta_pairs);
     if (tid < M) {
-      Pair bb{-FLT_MAX, INT_MAX};
+      Pair b{-FLT_MAX, INT_MAX};
       for (int w = 0; w < CW; ++w) {
-        const Pair qq = cand[w * 16 + tid];
-        if (better(qq.v, qq.i, bb.v, bb.i)) bb = qq;
+        const Pair q = cand[w * 16 + tid];
+        if (better(q.v, q.i, b.v, b.i)) b = q;
       }
-      cta_pairs[blockIdx.x * 16 + tid] = bb;
+      cta_pairs[blockIdx.x * 16 + tid] = b;
     }
     named_bar_sync(kConsumerBar, NCT);
     if (tid == 0) {
       __threadfence();
-      const unsigned old = atomicAdd(p.counters + p.tiles * kRowWarps, 1u);
+      const unsigned old = atomicAdd(p.counters + p.tiles * CW, 1u);
       const int last = (old == gridDim.x - 1);
       if (last) {
-        p.counters[p.tiles * kRowWarps] = 0;
+        p.counters[p.tiles * CW] = 0;
         __threadfence();
       }
       *sflag = last;
     }
     named_bar_sync(kConsumerBar, NCT);
     if (*sflag && tid < M) {
-      Pair bb{-FLT_MAX, INT_MAX};
+      Pair b{-FLT_MAX, INT_MAX};
       for (unsigned cc = 0; cc < gridDim.x; ++cc) {
-        Pair qq;
-        qq.v = __ldcg(&cta_pairs[cc * 16 + tid].v);
-        qq.i = __ldcg(&cta_pairs[cc * 16 + tid].i);
-        if (better(qq.v, qq.i, bb.v, bb.i)) bb = qq;
+        Pair q;
+        q.v = __ldcg(&cta_pairs[cc * 16 + tid].v);
+        q.i = __ldcg(&cta_pairs[cc * 16 + tid].i);
+        if (better(q.v, q.i, b.v, b.i)) b = q;
       }
-      const int idx = (bb.i == INT_MAX) ? 0 : bb.i;  // nothing finite: index 0, as a plain scan gives
+      const int idx = (b.i == INT_MAX) ? 0 : b.i;  // nothing finite: index 0, as a plain scan gives
       if (p.ids) p.ids[tid] = idx + p.row_offset;
       if (p.pairs_out)
-        static_cast<Pair*>(p.pairs_out)[tid] = Pair{bb.v, (bb.i == INT_MAX) ? INT_MAX : bb.i + p.row_offset};
+        static_cast<Pair*>(p.pairs_out)[tid] = Pair{b.v, (b.i == INT_MAX) ? INT_MAX : b.i + p.row_offset};
     }
   }
 }
@@ -702,28 +644,24 @@ __global__ void k_pairs_reduce(int32_t* ids, const Pair* pairs, int nranks, int 
 }
 
 // ------------------------------------------------------------------ host side
-}  // namespace
-unsigned long long* g_dbg = nullptr;
-namespace {
 struct Config {
-  int depth;         // weight ring stages (17 KB each)
-  int ctas;          // CTAs per SM
-  int chunk_groups;  // k groups per activation chunk
+  int depth;  // weight ring stages (17 KB each)
+  int ctas;   // CTAs per SM
+  int xbuf;   // bytes of one activation chunk buffer
   int pdl;
 };
 
 const Config& config() {
   static Config c = [] {
-    Config k{3, 2, 4, 1};
+    Config k{4, 2, 8192, 1};
     if (const char* e = getenv("W4A16_DEPTH")) k.depth = atoi(e);
     if (const char* e = getenv("W4A16_CTAS")) k.ctas = atoi(e) >= 2 ? 2 : 1;
-    if (kMinCtas == 1) k.ctas = 1;
-    if (const char* e = getenv("W4A16_CHUNK")) k.chunk_groups = atoi(e);
+    if (const char* e = getenv("W4A16_XBUF")) k.xbuf = atoi(e);
     if (const char* e = getenv("W4A16_PDL")) k.pdl = atoi(e) != 0;
-    if (k.depth != 2 && k.depth != 3 && k.depth != 4 && k.depth != 6) k.depth = 3;
-    if (k.chunk_groups < 2) k.chunk_groups = 2;
-    if (k.chunk_groups > kMaxChunkGroups) k.chunk_groups = kMaxChunkGroups;
-    k.chunk_groups &= ~1;
+    if (k.depth != 3 && k.depth != 4 && k.depth != 6) k.depth = 4;
+    if (k.xbuf < 4096) k.xbuf = 4096;
+    if (k.xbuf > 16384) k.xbuf = 16384;
+    k.xbuf &= ~1023;
     return k;
   }();
   return c;
@@ -731,14 +669,14 @@ const Config& config() {
 
 constexpr int kMaxCtasPerSm = 2;
 
-template <int MC, int D>
+template <int NT, int D>
 int launch_cfg(SkinnyParams& p, int grid, cudaStream_t st) {
-  const int smem = skinny_fixed_smem<D>() + kXBufs * p.chunk_groups * kXGroupBytes;
+  const int smem = skinny_fixed_smem<D>() + kXBufs * p.xbuf_bytes;
   static int attr_set[64] = {};
   int dev = 0;
   W4_CUDA(cudaGetDevice(&dev));
   if (attr_set[dev & 63] < smem) {
-    W4_CUDA(cudaFuncSetAttribute(k_skinny<MC, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    W4_CUDA(cudaFuncSetAttribute(k_skinny<NT, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set[dev & 63] = smem;
   }
   cudaLaunchConfig_t cfg = {};
@@ -751,17 +689,16 @@ int launch_cfg(SkinnyParams& p, int grid, cudaStream_t st) {
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
   cfg.numAttrs = config().pdl ? 1 : 0;
-  W4_CUDA(cudaLaunchKernelEx(&cfg, k_skinny<MC, D>, p));
+  W4_CUDA(cudaLaunchKernelEx(&cfg, k_skinny<NT, D>, p));
   return W4A16_OK;
 }
 
-template <int MC>
+template <int NT>
 int launch_depth(SkinnyParams& p, int grid, cudaStream_t st) {
   switch (config().depth) {
-    case 2: return launch_cfg<MC, 2>(p, grid, st);
-    case 4: return launch_cfg<MC, 4>(p, grid, st);
-    case 6: return launch_cfg<MC, 6>(p, grid, st);
-    default: return launch_cfg<MC, 3>(p, grid, st);
+    case 3: return launch_cfg<NT, 3>(p, grid, st);
+    case 6: return launch_cfg<NT, 6>(p, grid, st);
+    default: return launch_cfg<NT, 4>(p, grid, st);
   }
 }
 
@@ -790,25 +727,23 @@ int launch_skinny(SkinnyParams& p, const w4a16_weights_t* w, const uint16_t* x, 
   p.K = w->in_f;
   p.G = w->num_groups;
   p.tiles = (w->out_f + TR - 1) / TR;
-  p.chunk_groups = config().chunk_groups;
   p.partial = s->partial;
   p.counters = reinterpret_cast<unsigned*>(s->xgsum);
   p.cta_pairs = s->xf;
   p.status = di->status;
-  if (const char* e = getenv("W4A16_DEBUG_SKIP")) p.debug_skip = atoi(e);
-  if (getenv("W4A16_DEBUG_TIME")) {
-    static unsigned long long* dbg = nullptr;
-    if (!dbg) cudaMalloc(&dbg, 4096 * 8 * 8);
-    p.dbg = dbg;
-    g_dbg = dbg;
-  }
+  // groups per activation chunk: what one buffer holds (256 B per token per group), even.
+  // Token rows sit 16 bytes past a multiple of 128 apart, which keeps the B-fragment loads of
+  // neighbouring token rows on different banks.
+  int cg = config().xbuf / (256 * M);
+  if (cg > kMaxChunkGroups) cg = kMaxChunkGroups;
+  cg &= ~1;
+  if (cg < 2) cg = 2;
+  p.chunk_groups = cg;
+  p.xrow_bytes = cg * 256 + 16;
+  p.xbuf_bytes = (M * p.xrow_bytes + 127) & ~127;
   const int grid = grid_for_shape(w->out_f, w->num_groups, di->sms);
   if (int rc = w4a16_scratch_check(s, w->out_f, M)) return rc;
-  if (M == 1) return launch_depth<1>(p, grid, st);
-  if (M == 2) return launch_depth<2>(p, grid, st);
-  if (M <= 4) return launch_depth<4>(p, grid, st);
-  if (M <= 8) return launch_depth<8>(p, grid, st);
-  return launch_depth<16>(p, grid, st);
+  return M <= 8 ? launch_depth<1>(p, grid, st) : launch_depth<2>(p, grid, st);
 }
 
 }  // namespace
@@ -830,8 +765,8 @@ int w4a16_scratch_alloc(w4a16_scratch_t* s, int max_in, int max_out, int min_gro
   s->max_groups = max_in / min_group;
   s->max_splits = di->sms * kMaxCtasPerSm;  // CTAs of the persistent grid
   // two partial tiles per CTA (head and tail of its unit range), widest tile, 16 tokens
-  s->partial_elems = static_cast<size_t>(s->max_splits) * 2 * kTileRows * kTokens;
-  const size_t counters = ((static_cast<size_t>(max_out) / kTileRows + 2) * kRowWarps + 8) * sizeof(unsigned);
+  s->partial_elems = static_cast<size_t>(s->max_splits) * 2 * kTileRows * 16;
+  const size_t counters = ((static_cast<size_t>(max_out) / kTileRows + 2) * CW + 8) * sizeof(unsigned);
   const size_t pairs = static_cast<size_t>(s->max_splits) * 16 * sizeof(Pair);
   void *xf = nullptr, *cn = nullptr, *pa = nullptr;
   cudaError_t e = cudaMalloc(&xf, pairs);
@@ -866,7 +801,7 @@ int w4a16_scratch_check(const w4a16_scratch_t* s, int out_f, int M) {
   const DeviceInfo* di = device_info();
   if (!di) return W4A16_ECUDA;
   const int ctas = di->sms * kMaxCtasPerSm;
-  const size_t need = static_cast<size_t>(ctas) * 2 * kTileRows * kTokens;
+  const size_t need = static_cast<size_t>(ctas) * 2 * kTileRows * 16;
   if (need > s->partial_elems)
     return fail(W4A16_ESCRATCH, "scratch: partial buffer holds %zu floats, %zu needed", s->partial_elems, need);
   if (out_f > s->max_out)
@@ -962,9 +897,3 @@ int w4a16_gemm_skinny_sharded(uint16_t* const* y_peers, int nranks, int rank, in
 }
 
 }  // extern "C"
-
-extern "C" __attribute__((visibility("default"))) int w4a16_debug_read(unsigned long long* host, int n) {
-  if (!w4a16::g_dbg) return -1;
-  cudaDeviceSynchronize();
-  return cudaMemcpy(host, w4a16::g_dbg, size_t(n) * 8, cudaMemcpyDeviceToHost);
-}

@@ -89,7 +89,7 @@ __global__ void k_repack_q(uint8_t* __restrict__ dst, const uint32_t* __restrict
     }
     const int o = so + row_offset;
     *reinterpret_cast<uint4*>(dst + tile_group_offset(o, c >> 2, G) + (c & 3) * kChunkBytes +
-                              (o % kTileRows) * 16) = make_uint4(out[0], out[1], out[2], out[3]);
+                              weight_slot(o % kTileRows, c & 3) * 16) = make_uint4(out[0], out[1], out[2], out[3]);
   }
 }
 
@@ -121,7 +121,7 @@ __global__ void k_dequant_rows(uint16_t* __restrict__ dst, const uint8_t* __rest
     const int o = row0 + r;
     const int ro = o % kTileRows;
     const uint8_t* blk = stream + tile_group_offset(o, c >> 2, G);
-    const uint4 q = *reinterpret_cast<const uint4*>(blk + (c & 3) * kChunkBytes + ro * 16);
+    const uint4 q = *reinterpret_cast<const uint4*>(blk + (c & 3) * kChunkBytes + weight_slot(ro, c & 3) * 16);
     const float s = bf16_bits_to_float(reinterpret_cast<const uint16_t*>(blk + kTgScaleOff)[ro]);
     const float z = static_cast<float>(blk[kTgZpOff + ro]);
     const uint32_t in[4] = {q.x, q.y, q.z, q.w};
