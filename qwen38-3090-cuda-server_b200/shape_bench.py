@@ -4,7 +4,7 @@
     python shape_bench.py --case gemv:17408x5120:1 [--case skinny:34816x5120:9 ...]
                           [--iters 50] [--ring-mb 768] [--json out.json]
 
-case = kind:NxK:M with kind in {gemv, skinny, lmhead}. Each case cycles through a ring of
+case = kind:NxK:M with kind in {gemv, skinny, lmhead, prefill}. Each case cycles through a ring of
 distinct weight copies whose total size exceeds `--ring-mb` (several times the 126 MB L2),
 so every launch streams its weights from HBM. The launches are captured back to back into
 one CUDA graph (as the decode step is) and timed with CUDA events; the figure is the mean
@@ -28,6 +28,8 @@ def run_case(pkg, synth, torch, kind, N, K, M, iters, ring_mb, warmup=5, graph=T
     G = K // 128
     wbytes = N * K // 2 + N * G * 3
     copies = max(1, min(64, -(-ring_mb * (1 << 20) // wbytes))) if ring_mb > 0 else 1
+    if kind == "prefill":
+        copies = 1  # compute bound: one weight copy
     gen = torch.Generator(device="cuda").manual_seed(N * 31 + K)
     ws = []
     for _ in range(copies):
@@ -40,6 +42,7 @@ def run_case(pkg, synth, torch, kind, N, K, M, iters, ring_mb, warmup=5, graph=T
     y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
     ids = torch.zeros(M, dtype=torch.int32, device="cuda")
     s = pkg.gemv_scratch_alloc(K, N, 128, 16)
+    ws = pkg.gemm_workspace_alloc(4096) if kind == "prefill" else None
 
     def launch(i):
         w = ws[i % copies]
@@ -49,6 +52,8 @@ def run_case(pkg, synth, torch, kind, N, K, M, iters, ring_mb, warmup=5, graph=T
             pkg.gemm_mma_w4a16(y, w, x, M, s)
         elif kind == "lmhead":
             pkg.lm_head_argmax(ids, w, x, M, s)
+        elif kind == "prefill":
+            pkg.gemm_w4a16(y, w, x, M, ws)
         else:
             raise SystemExit(f"unknown kind {kind}")
 
@@ -84,8 +89,11 @@ def run_case(pkg, synth, torch, kind, N, K, M, iters, ring_mb, warmup=5, graph=T
     pkg.gemv_scratch_free(s)
     for w in ws:
         pkg.awq_free(w)
+    if ws is not None:
+        pkg.gemm_workspace_free(ws)
     return {"kind": kind, "N": N, "K": K, "M": M, "us": us, "algorithmic_bytes": alg,
-            "tbps": alg / us / 1e6, "ring_copies": copies, "iters": iters, "device_status": status}
+            "tbps": alg / us / 1e6, "tflops": 2.0 * M * N * K / us / 1e6, "ring_copies": copies, "iters": iters,
+            "device_status": status}
 
 
 def main():
@@ -100,9 +108,10 @@ def main():
     pkg = importlib.import_module(PKG)
     synth = importlib.import_module(PKG + ".synth")
     pkg.lib()
-    peak = 6552.0
+    peak, tf_peak = 6552.0, 1605.5
     try:
-        peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
+        mp = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        peak, tf_peak = float(mp["hbm_gbs"]), float(mp["bf16_tflops"])
     except Exception:
         pass
     rows = []
@@ -112,6 +121,12 @@ def main():
         r = run_case(pkg, synth, torch, kind, N, K, int(m), a.iters, a.ring_mb, graph=not a.eager)
         r["frac_of_measured_hbm"] = r["tbps"] * 1e3 / peak
         rows.append(r)
+        if kind == "prefill":
+            r["frac_of_measured_bf16"] = r["tflops"] / tf_peak
+            print(f"{kind:7s} {N:6d}x{K:<6d} M={int(m):4d}  {r['us']:9.2f} us  {r['tflops']:7.1f} TFLOP/s  "
+                  f"{100 * r['frac_of_measured_bf16']:5.1f}% of {tf_peak:.0f} TFLOP/s  status {r['device_status']}",
+                  flush=True)
+            continue
         print(f"{kind:7s} {N:6d}x{K:<6d} M={int(m):2d}  {r['us']:9.2f} us  {r['tbps']:6.3f} TB/s  "
               f"{100 * r['frac_of_measured_hbm']:5.1f}% of {peak:.0f} GB/s  status {r['device_status']}", flush=True)
     if a.json:

@@ -306,3 +306,56 @@ def test_launch_argument_errors(pkg, synth, scratch):
     torch.cuda.synchronize()
     assert pkg.device_status() == 0
     pkg.awq_free(w)
+
+
+# ----------------------------------------------------------------- prefill GEMM
+def _prefill_case(pkg, oracle, synth, N, K, M, seed):
+    (packed, scale, zp), w = _weights(pkg, synth, N, K, seed=seed)
+    x = synth.make_activations(M, K, seed=seed)
+    ws = pkg.gemm_workspace_alloc(1 << 20)
+    c = Guarded((M, N), torch.bfloat16)
+    pkg.gemm_w4a16(c.t, w, dev_bf16(x), M, ws)
+    torch.cuda.synchronize()
+    assert pkg.device_status() == 0 and c.intact()
+    got = synth.bf16_bits_to_f32(host_bits(c.t)).astype(np.float64)
+    assert np.all(np.isfinite(got))
+    pkg.gemm_workspace_free(ws)
+    pkg.awq_free(w)
+    return (packed, scale, zp), x, got
+
+
+@pytest.mark.parametrize("N,K,M", [(128, 128, 1), (128, 256, 256), (256, 512, 300), (1056, 1024, 129), (208, 384, 17)])
+def test_prefill_small_full_check(pkg, oracle, synth, N, K, M):
+    """Every element against the fp64 oracle; tolerance 2e-2 on max|err|/max|ref| as the reference's
+    prefill gate uses for bf16 outputs (tests/gate_gemm.cu:104-105)."""
+    (packed, scale, zp), x, got = _prefill_case(pkg, oracle, synth, N, K, M, seed=N + M)
+    ref = oracle.gemm_f64(packed, scale, zp, x)
+    r = rel_err(got, ref)
+    assert r <= 2e-2, f"relative error {r:.3e}"
+    # and elementwise: bf16 weights + bf16 output rounding
+    tol = 2e-2 * np.abs(ref) + 4e-3 * np.max(np.abs(ref))
+    assert not (np.abs(got - ref) > tol).any()
+
+
+def test_prefill_matches_dequant_then_matmul(pkg, oracle, synth):
+    """The fused kernel multiplies exactly the bf16 weights w4a16_dequant_rows produces: compare with a
+    float64 matmul on the oracle's bf16-rounded weights (tighter than the fp64 path: 1e-2 -> 6e-3, the
+    bf16 rounding of the output)."""
+    N, K, M = 512, 1024, 96
+    (packed, scale, zp), x, got = _prefill_case(pkg, oracle, synth, N, K, M, seed=77)
+    wb = synth.bf16_bits_to_f32(oracle.dequant_bf16(packed, scale, zp)).astype(np.float64)
+    ref = synth.bf16_bits_to_f32(x).astype(np.float64) @ wb.T
+    assert rel_err(got, ref) <= 6e-3
+
+
+@pytest.mark.parametrize("N,K", [(34816, 5120), (5120, 17408)])
+def test_prefill_model_shapes_sampled(pkg, oracle, synth, N, K):
+    """M = 4096 on the model's MLP shapes, 64 sampled (m, n) against fp64 (tests/gate_gemm.cu:78-90)."""
+    M = 4096
+    (packed, scale, zp), x, got = _prefill_case(pkg, oracle, synth, N, K, M, seed=5)
+    rng = np.random.default_rng(99)
+    rows = np.unique(rng.integers(0, N, 64)).astype(np.int64)
+    ms = rng.integers(0, M, 64)
+    ref = oracle.gemm_f64(packed, scale, zp, x[ms], rows=rows)
+    r = rel_err(got[np.ix_(ms, rows)], ref)
+    assert r <= 2e-2, f"relative error {r:.3e}"
