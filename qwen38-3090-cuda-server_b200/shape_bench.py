@@ -42,7 +42,7 @@ def run_case(pkg, synth, torch, kind, N, K, M, iters, ring_mb, warmup=5, graph=T
     y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
     ids = torch.zeros(M, dtype=torch.int32, device="cuda")
     s = pkg.gemv_scratch_alloc(K, N, 128, 16)
-    ws = pkg.gemm_workspace_alloc(4096) if kind == "prefill" else None
+    gws = pkg.gemm_workspace_alloc(4096) if kind == "prefill" else None
 
     def launch(i):
         w = ws[i % copies]
@@ -53,7 +53,7 @@ def run_case(pkg, synth, torch, kind, N, K, M, iters, ring_mb, warmup=5, graph=T
         elif kind == "lmhead":
             pkg.lm_head_argmax(ids, w, x, M, s)
         elif kind == "prefill":
-            pkg.gemm_w4a16(y, w, x, M, ws)
+            pkg.gemm_w4a16(y, w, x, M, gws)
         else:
             raise SystemExit(f"unknown kind {kind}")
 
@@ -89,8 +89,8 @@ def run_case(pkg, synth, torch, kind, N, K, M, iters, ring_mb, warmup=5, graph=T
     pkg.gemv_scratch_free(s)
     for w in ws:
         pkg.awq_free(w)
-    if ws is not None:
-        pkg.gemm_workspace_free(ws)
+    if gws is not None:
+        pkg.gemm_workspace_free(gws)
     return {"kind": kind, "N": N, "K": K, "M": M, "us": us, "algorithmic_bytes": alg,
             "tbps": alg / us / 1e6, "tflops": 2.0 * M * N * K / us / 1e6, "ring_copies": copies, "iters": iters,
             "device_status": status}
