@@ -103,6 +103,15 @@ int w4a16_choose_splits(int out_f, int num_groups);
  * y is bf16 when y_is_f32 == 0, fp32 otherwise. */
 int w4a16_gemv(void* y, int y_is_f32, const w4a16_weights_t* w, const uint16_t* x,
                w4a16_scratch_t* s, void* stream);
+/* No counterpart in the reference. The same GEMV for callers that must not allocate device
+ * memory and so cannot own a w4a16_scratch_t: for example code that runs after the serving
+ * process has given all remaining HBM to its KV cache, or that cannot afford the device-wide
+ * synchronisation an allocation implies. The scratch is a fixed device array inside the library
+ * (about 5.3 MB per GPU, held until exit); layers wider than 65536 rows, or devices with more
+ * than 160 SMs, are refused with W4A16_EINVAL. The first call on a device looks the array up
+ * and clears its counters, so make that call before capturing a stream. All calls share the
+ * array: calls that overlap on the GPU race; calls in stream order are fine. */
+int w4a16_gemv_static(void* y, int y_is_f32, const w4a16_weights_t* w, const uint16_t* x, void* stream);
 /* gemm_small_w4a16 and gemm_mma_w4a16 (gemv_w4a16.cuh:124-125,187-188):
  * Y[M][out_f] = X[M][in_f] W^T, 1 <= M <= 16, row-major bf16, weights read once. */
 int w4a16_gemm_skinny(uint16_t* y, const w4a16_weights_t* w, const uint16_t* x, int M,

@@ -69,6 +69,7 @@ _SIGNATURES = {
     "w4a16_choose_splits": (C.c_int, [C.c_int, C.c_int]),
     "w4a16_gemv": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(Weights), C.c_void_p, C.POINTER(Scratch),
                              C.c_void_p]),
+    "w4a16_gemv_static": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(Weights), C.c_void_p, C.c_void_p]),
     "w4a16_gemm_skinny": (C.c_int, [C.c_void_p, C.POINTER(Weights), C.c_void_p, C.c_int,
                                     C.POINTER(Scratch), C.c_void_p]),
     "w4a16_lm_head_argmax": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.POINTER(Weights),
@@ -178,6 +179,11 @@ def gemv_w4a16(y, w: Weights, x, s: Scratch, stream=None):
 
 def gemv_w4a16_f32(y, w: Weights, x, s: Scratch, stream=None):
     check(lib().w4a16_gemv(_ptr(y), 1, C.byref(w), _ptr(x), C.byref(s), _stream(stream)))
+
+
+def gemv_w4a16_static(y, w: Weights, x, f32: bool = False, stream=None):
+    """The GEMV with the library's built-in scratch: nothing is allocated, no Scratch is passed."""
+    check(lib().w4a16_gemv_static(_ptr(y), 1 if f32 else 0, C.byref(w), _ptr(x), _stream(stream)))
 
 
 def gemm_small_w4a16(y, w: Weights, x, M: int, s: Scratch, stream=None):

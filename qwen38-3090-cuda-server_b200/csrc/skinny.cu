@@ -861,6 +861,55 @@ int w4a16_argmax_pairs_reduce(int32_t* ids, const void* pairs, int nranks, int M
   return W4A16_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// GEMV without any scratch argument and without any allocation, for callers that cannot call
+// cudaMalloc: code that runs after the serving process has handed every remaining byte of HBM
+// to its KV cache, or on a path where the implicit device-wide synchronisation of an allocation
+// is not acceptable. The split-tile partial sums and arrival counters live in this file-scope
+// device array instead; every GPU that loads the library carries it (about 5.3 MB) until exit.
+constexpr int kStaticMaxCtas = 320;     // 2 CTAs x 160 SMs
+constexpr int kStaticMaxOut = 65536;    // widest layer the static scratch serves
+constexpr size_t kStaticPartialBytes = static_cast<size_t>(kStaticMaxCtas) * 2 * kTileRows * 16 * sizeof(float);
+constexpr size_t kStaticCounterBytes = ((kStaticMaxOut / kTileRows + 2) * 8 + 8) * sizeof(unsigned);
+constexpr size_t kStaticPairBytes = static_cast<size_t>(kStaticMaxCtas) * 16 * 8;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticPartialBytes + kStaticCounterBytes + kStaticPairBytes];
+
+int w4a16_gemv_static(void* y, int y_is_f32, const w4a16_weights_t* w, const uint16_t* x, void* stream) {
+  W4_REQUIRE(y != nullptr, "gemv_static: y is null");
+  W4_REQUIRE(w != nullptr, "gemv_static: null weights");
+  W4_REQUIRE(w->out_f <= kStaticMaxOut, "gemv_static: out_f %d exceeds the static scratch limit of %d rows", w->out_f,
+             kStaticMaxOut);
+  const DeviceInfo* di = device_info();
+  if (!di) return W4A16_ECUDA;
+  W4_REQUIRE(di->sms * kMaxCtasPerSm <= kStaticMaxCtas, "gemv_static: %d SMs exceed the static scratch limit of %d CTAs",
+             di->sms, kStaticMaxCtas);
+  // The array's name is only a host-side handle: the device address has to be asked for, once
+  // per device and with that device current. The first call on a device does this (and clears the
+  // counters), so it should come before any stream capture.
+  static unsigned char* base[64] = {};
+  unsigned char* b = base[di->device & 63];
+  if (!b) {
+    void* p0 = nullptr;
+    W4_CUDA(cudaGetSymbolAddress(&p0, g_static_scratch));
+    b = static_cast<unsigned char*>(p0);
+    W4_CUDA(cudaMemsetAsync(b + kStaticPartialBytes, 0, kStaticCounterBytes, static_cast<cudaStream_t>(stream)));
+    base[di->device & 63] = b;
+  }
+  w4a16_scratch_t s = {};
+  s.partial = reinterpret_cast<float*>(b);
+  s.xgsum = reinterpret_cast<float*>(b + kStaticPartialBytes);
+  s.xf = reinterpret_cast<float*>(b + kStaticPartialBytes + kStaticCounterBytes);
+  s.max_out = kStaticMaxOut;
+  s.max_splits = kStaticMaxCtas;
+  s.max_m = 1;
+  s.partial_elems = kStaticPartialBytes / sizeof(float);
+  SkinnyParams p = {};
+  p.y = y;
+  p.y_f32 = y_is_f32 ? 1 : 0;
+  p.ldy = w->out_f;
+  return launch_skinny(p, w, x, 1, &s, static_cast<cudaStream_t>(stream));
+}
+
 int w4a16_shard_rows(int out_f, int nranks, int rank, int* row_begin, int* row_end) {
   W4_REQUIRE(row_begin && row_end, "shard_rows: null output");
   if (nranks < 1 || rank < 0 || rank >= nranks)
