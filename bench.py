@@ -257,11 +257,13 @@ def run_ours(args):
             sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
+        torch.cuda.profiler.start()  # a profiler started with --profile-from-start off sees only the timed steps
         e0.record(stream)
         for _ in range(args.steps):
             step()
         e1.record(stream)
         barrier()
+        torch.cuda.profiler.stop()
         ms_total = e0.elapsed_time(e1)
 
         # ---- end to end: inputs from pinned host memory, result back to the host, every step ----

@@ -38,13 +38,17 @@ extern "C" {
 /* Kernel-private weight container; field-for-field the reference's
  * qwen::W4A16Weights (src/kernels/gemv_w4a16.cuh:50-60). The three buffers are
  * independent allocations, so callers may cudaFree them one by one as the
- * reference's callers do. Private layout (group_size 128):
- *   qweight [out_f/16][in_f/64][32] uint4  one 16-row x 64-k block per 512 B; lane l
- *           holds rows l/4 and l/4+8, k = 16*(l%4)+[0,16), 8 nibbles per word with
- *           k-offset c at nibble (c>>1)+4*(c&1), words ordered {row lo k0-7, row lo
- *           k8-15, row hi k0-7, row hi k8-15}
- *   scale   [out_f/16][G][16] bf16
- *   zp      [out_f/16][G][16] u8    raw stored nibble (value+8) */
+ * reference's callers do. Private layout (group_size 128): all weight data lives
+ * in ONE stream behind `qweight`, so that a CTA fetches a whole 128-row x
+ * 128-k group with one bulk copy; `scale` and `zp` are small placeholder
+ * allocations kept only so that the reference's free-one-by-one pattern works.
+ *   qweight [ceil(out_f/128)][G] blocks of 8576 B, block (t, g) =
+ *             [4 chunks of 32 k][128 slots] uint4   row r of the tile, chunk c sits in
+ *                                                  slot (r + 4*(c&1)) & 127 (bank rotation);
+ *                                                  inside a word k-offset o is nibble
+ *                                                  (o>>1) + 4*(o&1), stored value + 8
+ *             [128] bf16 scales, [128] u8 zero-points (raw stored nibble, value + 8)
+ *           rows past out_f in the last tile are zero. */
 typedef struct w4a16_weights {
   uint32_t* qweight;
   uint16_t* scale; /* bf16 bits */
@@ -54,7 +58,7 @@ typedef struct w4a16_weights {
 
 /* Caller-owned scratch; field-for-field qwen::GemvScratch
  * (src/kernels/gemv_w4a16.cuh:94-110). Here: `partial` holds split-K partial
- * tiles, `xgsum` the per-tile arrival counters (kept zero between calls),
+ * tiles, `xgsum` the per-(tile, warp) arrival counters (zero between calls),
  * `xf` the per-CTA (max, index) pairs of the fused argmax. One call in flight
  * per scratch, as in the reference. */
 typedef struct w4a16_scratch {
