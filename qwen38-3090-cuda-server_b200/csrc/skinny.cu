@@ -7,27 +7,37 @@
 // for lm_head, the separate argmax kernels (src/kernels/elementwise.cu:96-194).
 //
 // Shape of the computation (HBM-bound: every weight byte is read exactly once):
-//   * persistent grid, two CTAs per SM. The (128-row tile, k group) units of the
-//     matrix are dealt out as equal contiguous ranges, so every CTA streams the same
-//     number of bytes whatever N and K are. A row tile whose K range is shared by
-//     several CTAs is finished by the last warp to arrive for its rows, which adds the
-//     partial tiles in a fixed order (bitwise reproducible, no float atomics). Shared
-//     tiles are processed FIRST and each warp publishes its rows without any CTA-wide
-//     barrier, so that reduction overlaps everybody's main loop.
-//   * warp roles: a weight producer streams the CTA's contiguous share of the weight
-//     stream through a ring of shared-memory stages with 1-D bulk async copies
-//     (cp.async.bulk + mbarrier full/empty pairs); it does not wait for the previous
-//     kernel (programmatic dependent launch), so one layer's weights start flowing
-//     while the previous layer drains. An activation warp bulk-copies the token rows
-//     and reduces them to per-(group, token) sums on the tensor core. Eight consumer
-//     warps own 16 output rows each: nibbles become bf16 (128+q) pairs with one LOP3
-//     per two weights and go from registers into mma.sync m16n8k16 (bf16 x bf16 ->
-//     fp32); per group  y += s * (sum((128+q) x) - (128+zp) * sum(x)).
-//   * measured on B200: the legacy mma.sync pipe sustains about one m16n8k16 per 32
-//     cycles per scheduler, which caps this formulation near 4.5 TB/s (M <= 8). The
-//     same data path with the weights as a TMEM-resident tcgen05 operand removes that
-//     cap but is sync-latency bound today (2.2 TB/s); it shares the weight stream
-//     layout with the prefill kernel, so it can replace this loop once it is faster.
+//   * persistent grid, one CTA per SM, small enough (shared memory, registers, 256 of the 512
+//     tensor-memory columns) that the NEXT launch's CTA fits beside it: with programmatic
+//     dependent launch the next layer's weights are already streaming while this layer drains.
+//     The (128-row tile, k group) units of the matrix are dealt out as equal contiguous ranges,
+//     so every CTA streams the same number of bytes whatever N and K are. A row tile whose K
+//     range is shared by several CTAs is finished by the last warp to arrive for its rows, which
+//     adds the partial tiles in a fixed order (bitwise reproducible, no float atomics). Shared
+//     tiles are processed FIRST, so that reduction overlaps everybody's main loop.
+//   * the arithmetic is exact integer work on the 5th-generation tensor cores
+//     (tcgen05.mma kind::i8, 128 x N x 32, int32 accumulators in tensor memory):
+//       - weights: a nibble becomes an int8 with ONE logic instruction per four weights
+//         (w & 0x0F0F0F0F, (w >> 4) & 0x0F0F0F0F) and goes straight from registers into tensor
+//         memory as the A operand (tcgen05.st), one TMEM lane per output row;
+//       - activations: per (token, k group) the 128 bf16 values are turned into block
+//         fixed point, X = rint(x * 2^p) with |X| < 2^22 (exact for every element within 2^-14 of
+//         the group's largest; smaller ones are rounded at 2^-22 of the largest), and X is split
+//         into three signed 8-bit digits that form three rows of the B operand;
+//       - per group:  y += s * 2^-p * ((D0 + 2^8 D1 + 2^16 D2) - zp * sum(X)),  Dj = sum(q * digit_j),
+//         with the integer dot products exact and only this last step in fp32.
+//     This keeps the per-byte instruction count low enough for the ALU pipe (LOP3/SHF issue at
+//     half rate on this part) to keep up with HBM, which the bf16 formulation could not.
+//   * warp roles, all decoupled by mbarrier rings so that no role waits for a round trip:
+//       producer   1 thread  streams this CTA's share of the weight stream with 1-D bulk async
+//                            copies (8576-byte blocks) into a shared-memory ring, and runs an L2
+//                            prefetch a few blocks further ahead
+//       unpack     8 warps   nibbles -> int8 -> tensor memory (two warps per TMEM lane quarter,
+//                            alternating units), and the row's (scale, zero point) into a side ring
+//       activation 1 warp    bf16 x -> digit rows of the B operand in shared memory
+//       mma        1 thread  four tcgen05.mma per unit, tcgen05.commit to release A/B and publish D
+//       fix-up     4 warps   tcgen05.ld of the unit's int32 sums, the fp32 step above, the
+//                            split-tile reduction, output / fused argmax
 #include <cfloat>
 #include <climits>
 #include <cstdlib>
@@ -38,19 +48,55 @@
 namespace w4a16 {
 namespace {
 
-constexpr int CW = 8;                                 // consumer warps per CTA: 16 rows of the 128-row tile each
-constexpr int kWarps = CW + 2;                        // + weight producer warp + activation warp
-constexpr int kItemGroups = 2;                        // k groups per weight ring stage
-constexpr int kStageBytes = kItemGroups * kTileGroupBytes;  // 17152: two (tile, group) blocks
-static_assert(kStageBytes % 128 == 0, "ring stages must stay 128-byte aligned");
-constexpr int kXBufs = 3;                             // activation chunk buffers
-constexpr int kFirstChunk = 2;                        // groups in a CTA's first activation chunk (short start-up)
-constexpr int kMaxChunkGroups = 32;                   // bound on groups per activation chunk
-constexpr uint32_t kSpinLimit = 1u << 20;             // polls before a wait gives up
-constexpr uint32_t kMagic = 0x43004300u;              // bf16 pair (128.0, 128.0)
-constexpr uint32_t kNibMask = 0x000F000Fu;
-constexpr uint32_t kOnes = 0x3F803F80u;               // bf16 pair (1.0, 1.0)
-constexpr int kConsumerBar = 1;                       // named barrier of the consumer warps
+constexpr int CW = 4;                      // fix-up warps per CTA: 32 rows of the 128-row tile each
+constexpr int kWarps = 16;
+constexpr int kThreads = kWarps * 32;
+constexpr int kWUnpack0 = 4;               // warps 4..11 unpack
+constexpr int kWProducer = 12;
+constexpr int kWMma = 13;
+constexpr int kWAct = 14;
+constexpr int kWMma2 = 15;                 // second MMA issuer (odd units)
+constexpr int kSide = 16;                  // depth of the (scale, zp) and (sum, 2^-p) side rings: a slot is
+                                           // rewritten only after the fix-up of its previous unit has finished
+constexpr int kXBufs = 2;                  // raw activation chunk buffers
+constexpr int kFirstChunk = 2;             // groups in a CTA's first activation chunk (short start-up)
+constexpr int kMaxChunkGroups = 16;        // bound on groups per activation chunk
+constexpr uint32_t kSpinLimit = 1u << 20;  // polls before a wait gives up
+constexpr int kFixBar = 1;                 // named barrier of the fix-up warps
+constexpr int kTmemCols = 256;             // half of tensor memory: the next launch's CTA gets the other half
+constexpr int kACols = 32;                 // 128 int8 along k = 32 columns of 32 bits
+
+#ifdef W4A16_TRACE
+// Development aid (compiled only with -DW4A16_TRACE): per-CTA cycle counts of what each role waits for.
+__device__ long long g_trace[256 * 16];
+#define TR_DECL long long tr_t0 = clock64(), tr_acc[4] = {0, 0, 0, 0}
+#define TR_LAP(i) do { const long long t_ = clock64(); tr_acc[i] += t_ - tr_t0; tr_t0 = t_; } while (0)
+#define TR_OUT(base, n) do { for (int i_ = 0; i_ < (n); ++i_) g_trace[blockIdx.x * 16 + (base) + i_] = tr_acc[i_]; } while (0)
+__device__ long long g_tline[256 * 8];
+__device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define TL(i) do { g_tline[blockIdx.x * 8 + (i)] = gtime(); } while (0)
+#else
+#define TL(i)
+#define TR_DECL
+#define TR_LAP(i)
+#define TR_OUT(base, n)
+#endif
+
+// Per token-count geometry. N = rows of the B operand (3 digit rows per token, padded to 16);
+// AD = depth of the A (tensor memory) and B (shared memory) rings, DD = depth of the D ring.
+template <int MT>
+struct Geo {
+  static constexpr int N = MT <= 5 ? 16 : (MT <= 10 ? 32 : 48);
+  static constexpr int AD = N == 48 ? 2 : 4;
+  static constexpr int DD = N == 16 ? 8 : 4;             // also the depth of the "unit done" barrier ring
+  static constexpr int FB = MT == 1 ? 4 : (MT == 2 ? 2 : 1);  // units the fix-up warps take per round
+  static constexpr int kBBytes = N * 128;       // [8 k-chunks of 16][N/8][8 rows][16 B]
+  static constexpr int kLbo = (N / 8) * 128;    // between core matrices along k
+  static constexpr int kDCol0 = AD * kACols;    // first D column
+  static constexpr int kMinCtas = MT <= 5 ? 2 : 1;
+  static_assert(AD * kACols + DD * N <= kTmemCols, "tensor memory budget");
+  static_assert(AD + DD + FB <= kSide && 2 * FB <= DD && AD <= DD, "ring depths");
+};
 
 struct SkinnyParams {
   const uint8_t* stream;  // weight stream, kTileGroupBytes per (row tile, group)
@@ -60,11 +106,18 @@ struct SkinnyParams {
   long long ldy;  // elements between rows of y
   int y_col0;     // first column of this launch's rows inside y
   int M, N, K, G, tiles;
-  int chunk_groups;  // k groups per activation chunk (even)
-  int xrow_bytes;    // bytes between token rows inside an activation buffer
-  int xbuf_bytes;    // bytes of one activation buffer
+  int chunk_groups;  // k groups per activation chunk
+  int xbuf_bytes;    // bytes of one raw activation buffer (M rows of chunk_groups * 256); 0 in cache mode
+  int cache;         // 1: the digit rows of ALL k groups stay in shared memory, converted once per CTA
+  int b_slot;        // bytes between B slots (per group in cache mode, per ring slot otherwise)
+  int b_lbo;         // bytes between the 16-k chunks of a B slot
+  int b_bytes;       // bytes of the whole B region
+  int xs_bytes;      // bytes of the (sum, 2^-p) region
+  uint32_t hint;     // suspend-time hint of the mbarrier waits, ns
+  int depth;         // weight ring stages
+  int l2ahead;       // units of L2 prefetch ahead of the ring
   float* partial;
-  unsigned* counters;  // [tiles * 8 + 1], zero between launches
+  unsigned* counters;  // [tiles * CW + 1], zero between launches
   int argmax;
   int32_t* ids;
   void* pairs_out;  // M x {float,int}
@@ -158,477 +211,731 @@ struct WorkIter {
   }
 };
 
-// dynamic shared memory:
-//   [weight ring D stages][x buffers kXBufs][x sums kXBufs x 32 groups x 16][32 B zeros][mbarriers][flag]
-constexpr int kXsumFloats = kMaxChunkGroups * 16;
-template <int D>
-__host__ __device__ constexpr int skinny_fixed_smem() {
-  return D * kStageBytes + kXBufs * kXsumFloats * 4 + 32 + (2 * D + 3 * kXBufs) * 8 + 16;
+// ---- PTX used only here ------------------------------------------------------------------
+// Bounded wait with a per-launch suspend hint: how long one try_wait may park the thread.
+__device__ __forceinline__ bool wait_h(uint32_t bar, uint32_t parity, uint32_t hint_ns, uint32_t limit) {
+  for (uint32_t i = 0; i < limit; ++i)
+    if (mbar_try_wait(bar, parity, hint_ns)) return true;
+  return false;
+}
+__device__ __forceinline__ void l2_prefetch(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+// Instruction descriptor for kind::i8: signed 8-bit A and B (both K-major), int32 accumulate.
+__host__ __device__ constexpr uint32_t umma_idesc_s8(int M, int N) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(N >> 3) << 17) |
+         (static_cast<uint32_t>(M >> 4) << 24);
+}
+// D[tmem] (+)= A[tmem] * B[smem desc], int8 x int8 -> int32; issued by ONE thread.
+__device__ __forceinline__ void umma_s8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t* d) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t* d) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* d) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7]), "=r"(d[8]),
+        "=r"(d[9]), "=r"(d[10]), "=r"(d[11]), "=r"(d[12]), "=r"(d[13]), "=r"(d[14]), "=r"(d[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+// exact int -> float for |v| < 2^22 without the conversion pipe
+__device__ __forceinline__ float small_int_to_float(uint32_t v) {
+  return __uint_as_float(0x4B400000u + v) - 12582912.0f;
 }
 
-template <int NT, int D>
-__global__ void __launch_bounds__(kWarps * 32, 2) k_skinny(const SkinnyParams p) {
-  extern __shared__ __align__(128) uint8_t smem[];
-  constexpr int SLOT = CW * 16 * 8 * NT;  // floats per partial tile
-  constexpr int NCT = CW * 32;            // consumer threads
+// dynamic shared memory:
+//   [weight ring: depth x 8576][B region: b_bytes][raw x: kXBufs x xbuf_bytes][(scale,zp) ring: kSide x 128 x 4]
+//   [(sum, 2^-p) region: xs_bytes][mbarriers][tmem base, flag]
+// The B operand of one k group is eight 16-k chunks, `b_lbo` bytes apart, each holding the token digit
+// rows as consecutive 16-byte rows (row n at 16 n; an 8-row core matrix every 128 bytes).
+//   ring mode : a chunk holds all N rows (b_lbo = 16 N); rows without a token stay zero.
+//   cache mode: a chunk holds only the 3 M rows in use (b_lbo = 48 M), so the rows the tensor core reads
+//               beyond them are the next chunk's bytes. They only produce accumulator columns nobody
+//               reads, and the whole K range of a token fits: 384 bytes per group for M = 1.
+template <int MT>
+__host__ __device__ constexpr int bar_count(int depth) {
+  return 2 * depth + 2 * Geo<MT>::AD + 2 * Geo<MT>::DD + kXBufs + 1;
+}
+template <int MT>
+__host__ __device__ inline int total_smem(int depth, int b_bytes, int xbuf_bytes, int xs_bytes) {
+  return depth * kTileGroupBytes + b_bytes + kXBufs * xbuf_bytes + kSide * kTileRows * 4 + xs_bytes +
+         bar_count<MT>(depth) * 8 + 16;
+}
 
+// One token's 128 values of one k group (this lane: k = 4 lane .. 4 lane + 3, `rv`) -> three int8 digit
+// rows of the B operand at `bslot` (rows 3m, 3m+1, 3m+2) and (sum of X, 2^-p) at `xs`.
+// K index j of the operand holds k = 8 (j/8) + perm(j%8) with perm = {0,4,1,5,2,6,3,7}: the order in which
+// the two nibble masks deliver a packed word's weights.
+__device__ __forceinline__ void convert_group(uint2 rv, uint8_t* bslot, int lbo, int m, float2* xs, int lane) {
+  const float f0 = __uint_as_float(rv.x << 16), f1 = __uint_as_float(rv.x & 0xFFFF0000u);
+  const float f2 = __uint_as_float(rv.y << 16), f3 = __uint_as_float(rv.y & 0xFFFF0000u);
+  const uint32_t am = max(max(__float_as_uint(fabsf(f0)), __float_as_uint(fabsf(f1))),
+                          max(__float_as_uint(fabsf(f2)), __float_as_uint(fabsf(f3))));
+  const uint32_t e = __reduce_max_sync(0xffffffffu, am) >> 23;
+  // 2^p with p = 148 - e puts the largest magnitude into [2^21, 2^22)
+  const uint32_t me = min(275u - e, 250u);
+  const float mult = (e == 255u) ? 0.f : __uint_as_float(me << 23);
+  const float inv = (e == 255u) ? __uint_as_float(0x7FC00000u) : __uint_as_float((254u - me) << 23);
+  const int X0 = __float2int_rn(f0 * mult), X1 = __float2int_rn(f1 * mult);
+  const int X2 = __float2int_rn(f2 * mult), X3 = __float2int_rn(f3 * mult);
+  const int tot = __reduce_add_sync(0xffffffffu, (X0 + X1) + (X2 + X3));
+  // balanced base-256 digits: X = d0 + 2^8 d1 + 2^16 d2, d0, d1 in [-128, 127], |d2| <= 65
+  const int a0 = (X0 << 24) >> 24, a1 = (X1 << 24) >> 24, a2 = (X2 << 24) >> 24, a3 = (X3 << 24) >> 24;
+  const int r0 = (X0 - a0) >> 8, r1 = (X1 - a1) >> 8, r2 = (X2 - a2) >> 8, r3 = (X3 - a3) >> 8;
+  const int b0 = (r0 << 24) >> 24, b1 = (r1 << 24) >> 24, b2 = (r2 << 24) >> 24, b3 = (r3 << 24) >> 24;
+  const int c0 = (r0 - b0) >> 8, c1 = (r1 - b1) >> 8, c2 = (r2 - b2) >> 8, c3 = (r3 - b3) >> 8;
+  auto pack = [](int v0, int v1, int v2, int v3) {
+    return __byte_perm(__byte_perm(v0, v1, 0x0040), __byte_perm(v2, v3, 0x0040), 0x5410);
+  };
+  const uint32_t P0 = pack(a0, a1, a2, a3), P1 = pack(b0, b1, b2, b3), P2 = pack(c0, c1, c2, c3);
+  const uint32_t Q0 = __shfl_xor_sync(0xffffffffu, P0, 1), Q1 = __shfl_xor_sync(0xffffffffu, P1, 1);
+  const uint32_t Q2 = __shfl_xor_sync(0xffffffffu, P2, 1);
+  // even lane: k offsets 0..3 of its 8-block -> operand bytes {E0,O0,E1,O1}; odd lane: {E2,O2,E3,O3}
+  const uint32_t sel = (lane & 1) ? 0x3726u : 0x5140u;
+  uint8_t* dst = bslot + (lane >> 2) * lbo + 4 * (lane & 3) + 48 * m;
+  *reinterpret_cast<uint32_t*>(dst) = __byte_perm(P0, Q0, sel);
+  *reinterpret_cast<uint32_t*>(dst + 16) = __byte_perm(P1, Q1, sel);
+  *reinterpret_cast<uint32_t*>(dst + 32) = __byte_perm(P2, Q2, sel);
+  if (lane == 0) *xs = make_float2(static_cast<float>(tot), inv);
+}
+
+template <int MT>
+__global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const SkinnyParams p) {
+  using GE = Geo<MT>;
+  constexpr int N = GE::N, AD = GE::AD, DD = GE::DD;
+  constexpr int SLOT = kTileRows * MT;  // floats per partial tile
+  constexpr int NFT = CW * 32;          // fix-up threads
+  extern __shared__ __align__(128) uint8_t smem[];
+
+  const int DS = p.depth;
   uint8_t* ring = smem;
-  uint8_t* xbuf = ring + D * kStageBytes;
-  float* xsum = reinterpret_cast<float*>(xbuf + kXBufs * p.xbuf_bytes);
-  uint8_t* zeros = reinterpret_cast<uint8_t*>(xsum + kXBufs * kXsumFloats);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(zeros + 32);
-  int* sflag = reinterpret_cast<int*>(bars + 2 * D + 3 * kXBufs);
+  uint8_t* bq = ring + DS * kTileGroupBytes;
+  uint8_t* xraw = bq + p.b_bytes;
+  uint8_t* side = xraw + kXBufs * p.xbuf_bytes;
+  uint8_t* xsinv = side + kSide * kTileRows * 4;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(xsinv + p.xs_bytes);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + bar_count<MT>(DS));
+  const bool cache = p.cache != 0;
+  int* sflag = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = p.G, M = p.M;
   const int U = p.tiles * G;
+  if (tid == 0) TL(0);
   const int u0 = static_cast<int>(static_cast<long long>(U) * blockIdx.x / gridDim.x);
   const int u1 = static_cast<int>(static_cast<long long>(U) * (blockIdx.x + 1) / gridDim.x);
 
   const uint32_t ring_a = smem_u32(ring);
-  const uint32_t xbuf_a = smem_u32(xbuf);
-  const uint32_t wfull_a = smem_u32(bars);        // [D]  weights landed
-  const uint32_t wempty_a = wfull_a + D * 8;      // [D]  stage free again (8 consumer warps)
-  const uint32_t xfull_a = wempty_a + D * 8;      // [kXBufs] activation chunk landed
-  const uint32_t xsfull_a = xfull_a + kXBufs * 8; // [kXBufs] its per-group sums are ready
-  const uint32_t xempty_a = xsfull_a + kXBufs * 8;// [kXBufs] buffer free again (8 consumers + activation warp)
+  const uint32_t bq_a = smem_u32(bq);
+  const uint32_t xraw_a = smem_u32(xraw);
+  const uint32_t side_a = smem_u32(side);
+  const uint32_t xsinv_a = smem_u32(xsinv);
+  const uint32_t wfull_a = smem_u32(bars);          // [DS] weights landed (tx bytes)
+  const uint32_t wempty_a = wfull_a + DS * 8;       // [DS] stage free again (4 unpack warps)
+  const uint32_t afull_a = wempty_a + DS * 8;       // [AD] A slot written (4 unpack warps)
+  const uint32_t bfull_a = afull_a + AD * 8;        // [AD] B slot written (activation warp)
+  const uint32_t done_a = bfull_a + AD * 8;         // [DD] unit n's MMAs have completed (tcgen05.commit): its sums are
+                                                    //      in D slot n % DD, its A and B slots n % AD are free again
+  const uint32_t dempty_a = done_a + DD * 8;        // [DD] D slot read out (4 fix-up warps)
+  const uint32_t xfull_a = dempty_a + DD * 8;       // [kXBufs] raw activation chunk landed
+  const uint32_t bready_a = xfull_a + kXBufs * 8;   // cache mode: every group's digit rows are written
+  constexpr int kTeam = kWarps - 2;                 // warps that convert in cache mode (all but producer, mma)
 
-  if (tid < 8) reinterpret_cast<uint32_t*>(zeros)[tid] = 0u;
+  // rows of B that carry no token stay zero for the whole kernel
+  for (int i = tid; i < p.b_bytes / 16; i += kThreads) reinterpret_cast<uint4*>(bq)[i] = make_uint4(0, 0, 0, 0);
   if (tid == 0) {
-    for (int i = 0; i < D; ++i) {
+    for (int i = 0; i < DS; ++i) {
       mbar_init(wfull_a + i * 8, 1);
-      mbar_init(wempty_a + i * 8, CW);
+      mbar_init(wempty_a + i * 8, 4);
     }
-    for (int i = 0; i < kXBufs; ++i) {
-      mbar_init(xfull_a + i * 8, 1);
-      mbar_init(xsfull_a + i * 8, 1);
-      mbar_init(xempty_a + i * 8, CW + 1);
+    for (int i = 0; i < AD; ++i) {
+      mbar_init(afull_a + i * 8, 4);
+      mbar_init(bfull_a + i * 8, 1);
     }
+    for (int i = 0; i < DD; ++i) {
+      mbar_init(done_a + i * 8, 1);
+      mbar_init(dempty_a + i * 8, CW);
+    }
+    for (int i = 0; i < kXBufs; ++i) mbar_init(xfull_a + i * 8, 1);
+    mbar_init(bready_a, kTeam);
     fence_mbar_init();
   }
+  if (warp == kWMma) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+  fence_proxy_async();  // the zeroed B ring is read by the tensor core (async proxy)
+  tc_fence_before();
   __syncthreads();
+  tc_fence_after();
   pdl_launch_dependents();
+  const uint32_t tmem = *tmem_slot;
+  if (tid == 0) TL(1);
+#ifdef W4A16_TRACE
+  const long long tr_kernel0 = clock64();
+#endif
 
-  // B-fragment addressing of a lane: token row 8 nt + lane/4, k offset 16 (lane%4) within a
-  // 64-k step. Lanes whose token row does not exist read a block of zeros (all strides 0).
-  const int grow = lane >> 2, t = lane & 3;
-  uint32_t xlane[NT], xstep[NT], xbufoff[NT];
+  bool team_ok = true;
+  if (cache && warp != kWProducer && warp != kWMma) {
+    // ================================================================ cache mode: convert every k group once
+    // All warps but the producer and the MMA issuer take part (their own work cannot start before the
+    // activations exist anyway). x comes straight from global memory (L2), four groups in flight per warp.
+    pdl_wait();  // the previous kernel produced x
+    if (tid == 0) TL(2);
+    const int ti = warp < kWProducer ? warp : warp - 2;
+    const int total = G * M;  // (group, token) items, group-major; item i belongs to warp i % kTeam
+    constexpr int kBatch = 12;
+    for (int i0 = ti; i0 < total; i0 += kBatch * kTeam) {
+      uint2 rv[kBatch];  // all loads of the round are in flight before the first conversion
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
-    const int mm = nt * 8 + grow;
-    const bool valid = mm < M;
-    xlane[nt] = valid ? xbuf_a + mm * p.xrow_bytes + t * 32 : smem_u32(zeros);
-    xstep[nt] = valid ? 128 : 0;
-    xbufoff[nt] = valid ? p.xbuf_bytes : 0;
+      for (int j = 0; j < kBatch; ++j) {
+        const int i = i0 + j * kTeam;
+        if (i < total) {
+          const int g = i / M, m = i - g * M;
+          rv[j] = __ldcg(reinterpret_cast<const uint2*>(p.x + static_cast<size_t>(m) * p.K + g * kGroup) + lane);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        const int i = i0 + j * kTeam;
+        if (i < total) {
+          const int g = i / M, m = i - g * M;
+          convert_group(rv[j], bq + g * p.b_slot, p.b_lbo, m, reinterpret_cast<float2*>(xsinv) + g * MT + m, lane);
+        }
+      }
+    }
+    fence_proxy_async();  // B was written through the generic proxy, the tensor core reads it through the async one
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bready_a);
+    if (tid == 0) TL(3);
+#ifdef W4A16_TRACE
+    if (tid == 0) g_trace[blockIdx.x * 16 + 12] = clock64() - tr_kernel0;  // conversion done
+#endif
+    // the fix-up warps read the (sum, 2^-p) entries other warps wrote
+    if (warp < CW && !wait_h(bready_a, 0, p.hint, kSpinLimit)) {
+      atomicExch(p.status, W4A16_ETIMEOUT);
+      team_ok = false;
+    }
   }
 
-  // ================================================================ weight producer
-  // One thread streams this CTA's share of the weight stream, one stage (two k groups of all
-  // eight 16-row blocks, 17 KB, contiguous in memory) per bulk copy. It does not wait for the
-  // previous kernel: weights never depend on it.
-  if (warp == CW) {
+  if (warp == kWProducer) {
+    // ================================================================ weight producer
+    // One thread streams this CTA's share of the weight stream, one (tile, group) block per bulk
+    // copy. It does not wait for the previous kernel: weights never depend on it. A second cursor
+    // runs `l2ahead` blocks further and only pulls them into L2, so HBM stays busy while this
+    // kernel waits for its activations, and the ring refills at L2 speed afterwards.
     if (lane == 0) {
-      WorkIter it;
+      WorkIter it, pf;
       it.init(u0, u1, G, p.chunk_groups);
-      Chunk c;
-      int st = 0;
+      pf.init(u0, u1, G, p.chunk_groups);
+      Chunk c, pc;
+      int ahead = 0;
+      bool pf_more = p.l2ahead > 0;
+      auto prefetch = [&]() {
+        while (pf_more && ahead < p.l2ahead) {
+          if (!pf.next(pc)) {
+            pf_more = false;
+            break;
+          }
+          l2_prefetch(p.stream + (static_cast<size_t>(pc.tile) * G + pc.g) * kTileGroupBytes, pc.n * kTileGroupBytes);
+          ahead += pc.n;
+        }
+      };
+      prefetch();
+      int st = 0, issued = 0;
       uint32_t ph = 1;  // a fresh "empty" barrier reads as already released
       bool ok = true;
+      TR_DECL;
       while (ok && it.next(c)) {
-        for (int gi = 0; gi < c.n; gi += kItemGroups) {
-          const int ng = (c.n - gi < kItemGroups) ? c.n - gi : kItemGroups;
+        for (int gi = 0; gi < c.n; ++gi) {
+          TR_LAP(1);
           if (!mbar_wait_bounded_relaxed(wempty_a + st * 8, ph, kSpinLimit)) {
             atomicExch(p.status, W4A16_ETIMEOUT);
             ok = false;
             break;
           }
-          mbar_expect_tx(wfull_a + st * 8, ng * kTileGroupBytes);
-          bulk_g2s(ring_a + st * kStageBytes,
-                   p.stream + (static_cast<size_t>(c.tile) * G + c.g + gi) * kTileGroupBytes,
-                   ng * kTileGroupBytes, wfull_a + st * 8);
-          if (++st == D) {
+          TR_LAP(0);
+          mbar_expect_tx(wfull_a + st * 8, kTileGroupBytes);
+          bulk_g2s(ring_a + st * kTileGroupBytes,
+                   p.stream + (static_cast<size_t>(c.tile) * G + c.g + gi) * kTileGroupBytes, kTileGroupBytes,
+                   wfull_a + st * 8);
+          ++issued;
+          --ahead;
+          if (++st == DS) {
             st = 0;
             ph ^= 1;
           }
         }
+        prefetch();
+      }
+      TR_OUT(0, 2);  // producer: [0] waiting for a free stage, [1] everything else
+      // every copy this thread started has to land before the CTA may exit
+      for (int i = 0; i < DS && i < issued; ++i) {
+        const int k = issued - 1 - i;  // the last copy into stage k % DS
+        mbar_wait_bounded_relaxed(wfull_a + (k % DS) * 8, static_cast<uint32_t>(k / DS) & 1u, 1u << 14);
       }
     }
-    return;
-  }
-
-  // ================================================================ activation warp
-  // Waits for the previous kernel (it produced x), then per chunk: bulk-copies the token rows,
-  // and turns them into per-(group, token) sums with the tensor core (ones(16x16) * X).
-  if (warp == CW + 1) {
+  } else if (warp == kWMma || warp == kWMma2) {
+    // ================================================================ MMA issuers
+    // Two threads, even and odd units. Issuing four small MMAs and a commit costs one thread several
+    // hundred cycles, more than a unit's share of the HBM time; two issuers run side by side.
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_s8(128, N);
+      const int mine = (warp == kWMma) ? 0 : 1;
+      bool ok = true;
+      if (cache && !wait_h(bready_a, 0, p.hint, kSpinLimit)) {
+        atomicExch(p.status, W4A16_ETIMEOUT);
+        ok = false;
+      }
+      WorkIter it;
+      it.init(u0, u1, G, p.chunk_groups);
+      Chunk c;
+      const uint32_t lbo = p.b_lbo;
+      // descriptor of B slot 0, first 32-k step; other slots and steps only move the address field
+      const uint64_t desc0 = umma_desc_kmajor(bq_a, lbo, 128);
+      const uint32_t step16 = (2 * lbo) >> 4, slot16 = static_cast<uint32_t>(p.b_slot) >> 4;
+      int n = 0;
+      TR_DECL;
+      while (ok && it.next(c)) {
+        for (int gl = 0; gl < c.n; ++gl, ++n) {
+          if ((n & 1) != mine) continue;
+          const int a = n & (AD - 1), d = n & (DD - 1);
+          const uint32_t aph = static_cast<uint32_t>(n / AD) & 1u;
+          TR_LAP(3);
+          // A written (its writers also saw the D slot drained), and in ring mode B written
+          bool w_ok = wait_h(afull_a + a * 8, aph, p.hint, kSpinLimit);
+          TR_LAP(0);
+          w_ok = w_ok && (cache || wait_h(bfull_a + a * 8, aph, p.hint, kSpinLimit));
+          TR_LAP(1);
+          if (!w_ok) {
+            atomicExch(p.status, W4A16_ETIMEOUT);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t d_t = tmem + GE::kDCol0 + d * N;
+          const uint32_t a_t = tmem + a * kACols;
+          const uint64_t db = desc0 + static_cast<uint32_t>(cache ? c.g + gl : a) * slot16;
+          umma_s8_ts(d_t, a_t, db, idesc, 0);
+          umma_s8_ts(d_t, a_t + 8, db + step16, idesc, 1);
+          umma_s8_ts(d_t, a_t + 16, db + 2 * step16, idesc, 1);
+          umma_s8_ts(d_t, a_t + 24, db + 3 * step16, idesc, 1);
+          umma_commit(done_a + d * 8);
+        }
+      }
+      if (mine == 0) TR_OUT(2, 4);  // mma: waiting for [2] A, [3] B; [5] issuing
+    }
+  } else if (warp == kWAct && !cache) {
+    // ================================================================ activation warp (ring mode)
+    // Waits for the previous kernel (it produced x), then per chunk bulk-copies the token rows and
+    // per unit turns each token's 128 values into three int8 digit rows of the B slot.
     pdl_wait();
     WorkIter it;
     it.init(u0, u1, G, p.chunk_groups);
-    Chunk c;
-    int xb = 0;
-    uint32_t fph = 0, eph = 1;
-    while (it.next(c)) {
-      if (!mbar_wait_bounded_relaxed(xempty_a + xb * 8, eph, kSpinLimit)) {
-        atomicExch(p.status, W4A16_ETIMEOUT);
-        break;
-      }
+    Chunk c, cn;
+    const int rowb = p.chunk_groups * 256;
+    auto issue = [&](const Chunk& ch, int xb) {
       if (lane == 0) {
-        mbar_expect_tx(xfull_a + xb * 8, M * c.n * 256);
+        fence_proxy_async();  // this warp's reads of the buffer come before the copy's writes
+        mbar_expect_tx(xfull_a + xb * 8, M * ch.n * 256);
         for (int m = 0; m < M; ++m)
-          bulk_g2s(xbuf_a + xb * p.xbuf_bytes + m * p.xrow_bytes,
-                   p.x + static_cast<size_t>(m) * p.K + c.g * kGroup, c.n * 256, xfull_a + xb * 8);
+          bulk_g2s(xraw_a + xb * p.xbuf_bytes + m * rowb, p.x + static_cast<size_t>(m) * p.K + ch.g * kGroup,
+                   ch.n * 256, xfull_a + xb * 8);
       }
-      if (!mbar_wait_bounded(xfull_a + xb * 8, fph, kSpinLimit)) {
+    };
+    bool have = it.next(c);
+    if (have) issue(c, 0);
+    int xb = 0, n = 0;
+    uint32_t xph0 = 0, xph1 = 0;
+    bool ok = true;
+    while (ok && have) {
+      const bool more = it.next(cn);
+      __syncwarp();
+      if (more) issue(cn, xb ^ 1);
+      if (!wait_h(xfull_a + xb * 8, xb ? xph1 : xph0, p.hint, kSpinLimit)) {
         atomicExch(p.status, W4A16_ETIMEOUT);
+        ok = false;
         break;
       }
-      for (int gl = 0; gl < c.n; ++gl) {
+      for (int gl = 0; gl < c.n && ok; ++gl, ++n) {
+        const int a = n & (AD - 1);
+        if (n >= AD && !wait_h(done_a + ((n - AD) & (DD - 1)) * 8, static_cast<uint32_t>((n - AD) / DD) & 1u, p.hint, kSpinLimit)) {
+          atomicExch(p.status, W4A16_ETIMEOUT);
+          ok = false;
+          break;
+        }
+        for (int m = 0; m < M; ++m) {
+          const uint2 rv = *reinterpret_cast<const uint2*>(xraw + xb * p.xbuf_bytes + m * rowb + gl * 256 + lane * 8);
+          convert_group(rv, bq + a * p.b_slot, p.b_lbo, m,
+                        reinterpret_cast<float2*>(xsinv) + (n & (kSide - 1)) * 16 + m, lane);
+        }
+        fence_proxy_async();  // B was written through the generic proxy, the tensor core reads it through the async one
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bfull_a + a * 8);
+      }
+      if (xb) xph1 ^= 1; else xph0 ^= 1;
+      xb ^= 1;
+      c = cn;
+      have = more;
+    }
+    if (!ok && lane == 0) {  // a copy into the other buffer may still be in flight
+      mbar_wait_bounded_relaxed(xfull_a + (xb ^ 1) * 8, (xb ^ 1) ? xph1 : xph0, 1u << 14);
+    }
+  } else if (warp >= kWUnpack0 && warp < kWUnpack0 + 8) {
+    // ================================================================ unpack warps
+    // Thread = one row of the tile = one TMEM lane. Per unit: the row's 64 bytes (four 16-byte
+    // slots) -> 32 registers of int8 -> 32 TMEM columns of the A slot.
+    const int q = warp & 3, pair = (warp - kWUnpack0) >> 2, r = q * 32 + lane;
+    const uint32_t lane_t = tmem + (static_cast<uint32_t>(q * 32) << 16);
+    uint32_t woff[4];
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          float ax[4][4];
-          const uint8_t* xa = smem + (xlane[nt] - ring_a) + xb * xbufoff[nt] + gl * 2 * xstep[nt];
-          const uint4 b0 = *reinterpret_cast<const uint4*>(xa);
-          const uint4 b1 = *reinterpret_cast<const uint4*>(xa + 16);
-          const uint4 b2 = *reinterpret_cast<const uint4*>(xa + xstep[nt]);
-          const uint4 b3 = *reinterpret_cast<const uint4*>(xa + xstep[nt] + 16);
-          mma_bf16_16816_zero(ax[0], kOnes, kOnes, kOnes, kOnes, b0.x, b0.y);
-          mma_bf16_16816_zero(ax[1], kOnes, kOnes, kOnes, kOnes, b1.x, b1.y);
-          mma_bf16_16816_zero(ax[2], kOnes, kOnes, kOnes, kOnes, b2.x, b2.y);
-          mma_bf16_16816_zero(ax[3], kOnes, kOnes, kOnes, kOnes, b3.x, b3.y);
-          mma_bf16_16816(ax[0], kOnes, kOnes, kOnes, kOnes, b0.z, b0.w);
-          mma_bf16_16816(ax[1], kOnes, kOnes, kOnes, kOnes, b1.z, b1.w);
-          mma_bf16_16816(ax[2], kOnes, kOnes, kOnes, kOnes, b2.z, b2.w);
-          mma_bf16_16816(ax[3], kOnes, kOnes, kOnes, kOnes, b3.z, b3.w);
-          if (grow == 0) {
-            float* xs = xsum + xb * kXsumFloats + gl * 16 + nt * 8 + 2 * t;
-            xs[0] = (ax[0][0] + ax[1][0]) + (ax[2][0] + ax[3][0]);
-            xs[1] = (ax[0][1] + ax[1][1]) + (ax[2][1] + ax[3][1]);
+    for (int c4 = 0; c4 < 4; ++c4) woff[c4] = c4 * kChunkBytes + weight_slot(r, c4) * 16;
+    const int units = u1 - u0;
+    int st = 0;
+    uint32_t wph = 0;
+    TR_DECL;
+    for (int n = 0; n < units; ++n) {
+      if ((n & 1) == pair) {
+        const int a = n & (AD - 1);
+        TR_LAP(3);
+        if (!wait_h(wfull_a + st * 8, wph, p.hint, kSpinLimit)) {
+          atomicExch(p.status, W4A16_ETIMEOUT);
+          break;
+        }
+        TR_LAP(0);
+        const uint32_t base = ring_a + st * kTileGroupBytes;
+        uint4 w[4];
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) w[c4] = lds128(base + woff[c4]);
+        uint32_t sz;
+        {
+          uint32_t sc, zp;
+          asm volatile("ld.shared.u16 %0, [%1];" : "=r"(sc) : "r"(base + kTgScaleOff + 2 * r));
+          asm volatile("ld.shared.u8 %0, [%1];" : "=r"(zp) : "r"(base + kTgZpOff + r));
+          sz = (sc << 16) | zp;
+        }
+        TR_LAP(2);
+        // the A slot's previous unit has been multiplied, and the D slot this unit will fill has been read out
+        if ((n >= AD && !wait_h(done_a + ((n - AD) & (DD - 1)) * 8, static_cast<uint32_t>((n - AD) / DD) & 1u, p.hint, kSpinLimit)) ||
+            (n >= DD && !wait_h(dempty_a + (n & (DD - 1)) * 8, static_cast<uint32_t>(n / DD - 1) & 1u, p.hint, kSpinLimit))) {
+          atomicExch(p.status, W4A16_ETIMEOUT);
+          break;
+        }
+        TR_LAP(1);
+        tc_fence_after();
+        uint32_t v[32];
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+          const uint32_t ww[4] = {w[c4].x, w[c4].y, w[c4].z, w[c4].w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            v[c4 * 8 + 2 * i] = ww[i] & 0x0F0F0F0Fu;
+            v[c4 * 8 + 2 * i + 1] = (ww[i] >> 4) & 0x0F0F0F0Fu;
           }
         }
-      }
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(xsfull_a + xb * 8);  // sums published
-        mbar_arrive(xempty_a + xb * 8);  // this warp no longer reads the chunk
-      }
-      if (++xb == kXBufs) {
-        xb = 0;
-        fph ^= 1;
-        eph ^= 1;
-      }
-    }
-    return;
-  }
-
-  // ================================================================ consumer warps
-  // Byte offsets of this lane's 8-byte weight pieces inside a (tile, group) block: chunk t/2 of
-  // the step, the slot of its row (rotated by four slots in odd chunks, which keeps the 8-byte
-  // loads of a half-warp on distinct banks), half t%2 of the slot.
-  const int wrow = warp * 16 + grow;
-  const int woff_lo = (t >> 1) * kChunkBytes + weight_slot(wrow, t >> 1) * 16 + (t & 1) * 8;
-  const int woff_hi = (t >> 1) * kChunkBytes + weight_slot(wrow + 8, t >> 1) * 16 + (t & 1) * 8;
-
-  float fin[NT][4];
-#pragma unroll
-  for (int nt = 0; nt < NT; ++nt) fin[nt][0] = fin[nt][1] = fin[nt][2] = fin[nt][3] = 0.f;
-
-  float best_v[NT][2];
-  int best_i[NT][2];
-#pragma unroll
-  for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      best_v[nt][c] = -FLT_MAX;
-      best_i[nt][c] = INT_MAX;
-    }
-
-  // Final values of one row tile are in registers: write them out / fold into the argmax.
-  auto finalize = [&](int tile, const float (&v)[NT][4]) {
-    const int rb = tile * CW + warp;
-    if (rb * 16 >= p.N) return;  // zero-padded rows of the last tile
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int m = nt * 8 + 2 * t + (j & 1);
-        const int r = rb * 16 + grow + 8 * (j >> 1);
-        if (m >= M) continue;
-        const uint16_t hb = float_to_bf16_bits(v[nt][j]);
-        if (p.y) {
-          const size_t o = static_cast<size_t>(m) * p.ldy + p.y_col0 + r;
-          if (p.y_f32) static_cast<float*>(p.y)[o] = v[nt][j];
-          else static_cast<uint16_t*>(p.y)[o] = hb;
-          for (int q = 0; q < p.npeers; ++q) p.y_peers[q][o] = hb;
-        }
-        if (p.argmax) {
-          const float lv = bf16_bits_to_float(hb);
-          if (better(lv, r, best_v[nt][j & 1], best_i[nt][j & 1])) {
-            best_v[nt][j & 1] = lv;
-            best_i[nt][j & 1] = r;
-          }
+        const uint32_t a_t = lane_t + a * kACols;
+        tmem_st16(a_t, reinterpret_cast<const uint32_t(&)[16]>(v[0]));
+        tmem_st16(a_t + 16, reinterpret_cast<const uint32_t(&)[16]>(v[16]));
+        sts32(side_a + ((n & (kSide - 1)) * kTileRows + r) * 4, sz);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(afull_a + a * 8);
+          mbar_arrive(wempty_a + st * 8);
         }
       }
-  };
-
-  // The 8 MMAs per token tile of one 128-k group of this warp's 16 rows, on bf16 (128+q) pairs.
-  // `gb` = the (tile, group) block in the ring. Step s covers k chunks 2s and 2s+1; this lane's 16 k
-  // of the step are one 8-byte half of the 16-byte slot of (row, chunk) for its low and high row.
-  auto group_mma = [&](const uint8_t* gb, const uint8_t* const (&xp)[NT], float (&acc)[NT][2][4]) {
-#pragma unroll
-    for (int s = 0; s < 2; ++s) {
-      const uint2 qlo = *reinterpret_cast<const uint2*>(gb + s * (2 * kChunkBytes) + woff_lo);
-      const uint2 qhi = *reinterpret_cast<const uint2*>(gb + s * (2 * kChunkBytes) + woff_hi);
-      const uint4 wq = make_uint4(qlo.x, qlo.y, qhi.x, qhi.y);
-      uint32_t a[4][4];  // [mma][register]: rows (lo, hi, lo, hi) x k pairs
-      a[0][0] = (wq.x & kNibMask) | kMagic;
-      a[0][1] = (wq.z & kNibMask) | kMagic;
-      a[0][2] = ((wq.x >> 4) & kNibMask) | kMagic;
-      a[0][3] = ((wq.z >> 4) & kNibMask) | kMagic;
-      a[1][0] = ((wq.x >> 8) & kNibMask) | kMagic;
-      a[1][1] = ((wq.z >> 8) & kNibMask) | kMagic;
-      a[1][2] = ((wq.x >> 12) & kNibMask) | kMagic;
-      a[1][3] = ((wq.z >> 12) & kNibMask) | kMagic;
-      a[2][0] = (wq.y & kNibMask) | kMagic;
-      a[2][1] = (wq.w & kNibMask) | kMagic;
-      a[2][2] = ((wq.y >> 4) & kNibMask) | kMagic;
-      a[2][3] = ((wq.w >> 4) & kNibMask) | kMagic;
-      a[3][0] = ((wq.y >> 8) & kNibMask) | kMagic;
-      a[3][1] = ((wq.w >> 8) & kNibMask) | kMagic;
-      a[3][2] = ((wq.y >> 12) & kNibMask) | kMagic;
-      a[3][3] = ((wq.w >> 12) & kNibMask) | kMagic;
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        const uint4 bl = *reinterpret_cast<const uint4*>(xp[nt] + s * xstep[nt]);
-        const uint4 bh = *reinterpret_cast<const uint4*>(xp[nt] + s * xstep[nt] + 16);
-        if (s == 0) {
-          mma_bf16_16816_zero(acc[nt][0], a[0][0], a[0][1], a[0][2], a[0][3], bl.x, bl.y);
-          mma_bf16_16816_zero(acc[nt][1], a[1][0], a[1][1], a[1][2], a[1][3], bl.z, bl.w);
-        } else {
-          mma_bf16_16816(acc[nt][0], a[0][0], a[0][1], a[0][2], a[0][3], bl.x, bl.y);
-          mma_bf16_16816(acc[nt][1], a[1][0], a[1][1], a[1][2], a[1][3], bl.z, bl.w);
-        }
-        mma_bf16_16816(acc[nt][0], a[2][0], a[2][1], a[2][2], a[2][3], bh.x, bh.y);
-        mma_bf16_16816(acc[nt][1], a[3][0], a[3][1], a[3][2], a[3][3], bh.z, bh.w);
-      }
-    }
-  };
-  // y += s * (acc - (128 + zp) * sum(x)) for the lane's two rows
-  auto group_fix = [&](const uint8_t* gb, const float* xs, const float (&acc)[NT][2][4]) {
-    const uint16_t* scp = reinterpret_cast<const uint16_t*>(gb + kTgScaleOff) + warp * 16 + grow;
-    const uint8_t* zpp = gb + kTgZpOff + warp * 16 + grow;
-    const float s_lo = bf16_bits_to_float(scp[0]), s_hi = bf16_bits_to_float(scp[8]);
-    const float z_lo = __uint_as_float(__byte_perm(zpp[0], 0x43000000u, 0x7044));  // 128 + zp, low row
-    const float z_hi = __uint_as_float(__byte_perm(zpp[8], 0x43000000u, 0x7044));  // high row
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      const float2 x2 = *reinterpret_cast<const float2*>(xs + nt * 8 + 2 * t);
-      fin[nt][0] = fmaf(s_lo, fmaf(-z_lo, x2.x, acc[nt][0][0] + acc[nt][1][0]), fin[nt][0]);
-      fin[nt][1] = fmaf(s_lo, fmaf(-z_lo, x2.y, acc[nt][0][1] + acc[nt][1][1]), fin[nt][1]);
-      fin[nt][2] = fmaf(s_hi, fmaf(-z_hi, x2.x, acc[nt][0][2] + acc[nt][1][2]), fin[nt][2]);
-      fin[nt][3] = fmaf(s_hi, fmaf(-z_hi, x2.y, acc[nt][0][3] + acc[nt][1][3]), fin[nt][3]);
-    }
-  };
-
-  // (tile, first/last contributing CTA, arrival ticket) of up to two split tiles, in lane 0
-  int sp_n = 0, sp_tile0 = 0, sp_cf0 = 0, sp_cl0 = 0, sp_tile1 = 0, sp_cf1 = 0, sp_cl1 = 0;
-  unsigned sp_old0 = 0, sp_old1 = 0;
-  bool waited_pdl = false;
-  auto before_global_write = [&]() {
-    if (!waited_pdl) {
-      pdl_wait();  // outputs and the shared scratch belong to the previous kernel until now
-      waited_pdl = true;
-    }
-  };
-
-  WorkIter it;
-  it.init(u0, u1, G, p.chunk_groups);
-  Chunk c;
-  int wst = 0, xb = 0;
-  uint32_t wph = 0, xph = 0;
-  bool dead = false;
-
-  while (it.next(c)) {
-    // ---- one activation chunk: groups [c.g, c.g + c.n) of row tile c.tile ----
-    if (!dead && !mbar_wait_bounded(xfull_a + xb * 8, xph, kSpinLimit)) {
-      dead = true;
-      atomicExch(p.status, W4A16_ETIMEOUT);
-    }
-    const uint8_t* xchunk[NT];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) xchunk[nt] = smem + (xlane[nt] - ring_a) + xb * xbufoff[nt];
-    const float* xs = xsum + xb * kXsumFloats;
-    bool sums_ready = false;
-
-    for (int gi = 0; gi < c.n; gi += kItemGroups) {
-      if (!dead && !mbar_wait_bounded(wfull_a + wst * 8, wph, kSpinLimit)) {
-        dead = true;
-        atomicExch(p.status, W4A16_ETIMEOUT);
-      }
-      const uint8_t* up = ring + wst * kStageBytes;
-      {
-        float acc0[NT][2][4], acc1[NT][2][4];
-        const uint8_t* xp[NT];
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) xp[nt] = xchunk[nt] + gi * 2 * xstep[nt];
-        const bool two = gi + 1 < c.n;
-        group_mma(up, xp, acc0);
-        if (two) {
-#pragma unroll
-          for (int nt = 0; nt < NT; ++nt) xp[nt] += 2 * xstep[nt];
-          group_mma(up + kTileGroupBytes, xp, acc1);
-        }
-        if (!sums_ready) {
-          if (!dead && !mbar_wait_bounded(xsfull_a + xb * 8, xph, kSpinLimit)) {
-            dead = true;
-            atomicExch(p.status, W4A16_ETIMEOUT);
-          }
-          sums_ready = true;
-        }
-        group_fix(up, xs + gi * 16, acc0);
-        if (two) group_fix(up + kTileGroupBytes, xs + (gi + 1) * 16, acc1);
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(wempty_a + wst * 8);  // this warp is done with the stage
-      if (++wst == D) {
-        wst = 0;
+      if (++st == DS) {
+        st = 0;
         wph ^= 1;
       }
     }
-    if (lane == 0) mbar_arrive(xempty_a + xb * 8);  // (the __syncwarp above ordered every lane's reads)
-    if (++xb == kXBufs) {
-      xb = 0;
-      xph ^= 1;
+    TR_LAP(3);
+    if (warp == kWUnpack0 && lane == 0) TR_OUT(6, 4);  // unpack: waiting for [6] weights, [7] a free A slot; [8] loads, [9] unpack + store
+  } else if (warp < CW) {
+    // ================================================================ fix-up warps
+    const int q = warp, r = q * 32 + lane;
+    const uint32_t lane_t = tmem + (static_cast<uint32_t>(q * 32) << 16) + GE::kDCol0;
+
+    float fin[MT];
+    float best_v[MT];
+    int best_i[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      fin[m] = 0.f;
+      best_v[m] = -FLT_MAX;
+      best_i[m] = INT_MAX;
     }
 
-    if (c.seg_last) {
-      // ---- end of this CTA's segment of row tile c.tile: groups [seg_g0, seg_g1) ----
-      before_global_write();
-      const int tile = c.tile;
-      if (c.seg_g0 == 0 && c.seg_g1 == G) {
-        finalize(tile, fin);
-      } else {
-        // split tile: this warp publishes its 16 rows and moves on; no CTA-wide barrier
-        const long long X0 = static_cast<long long>(tile) * G;
-        const int c_first = static_cast<int>(((X0 + 1) * gridDim.x - 1) / U);
-        const int c_last = static_cast<int>(((X0 + G) * gridDim.x - 1) / U);
-        const int which = (u0 / G == tile) ? 0 : 1;
-        float* slot = p.partial + (static_cast<size_t>(blockIdx.x) * 2 + which) * SLOT;
+    // Final values of one row tile are in registers: write them out / fold into the argmax.
+    auto finalize = [&](int tile, const float(&v)[MT]) {
+      const int row = tile * kTileRows + r;
+      if (row >= p.N) return;  // zero-padded rows of the last tile
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
+      for (int m = 0; m < MT; ++m) {
+        if (m >= M) continue;
+        const uint16_t hb = float_to_bf16_bits(v[m]);
+        if (p.y) {
+          const size_t o = static_cast<size_t>(m) * p.ldy + p.y_col0 + row;
+          if (p.y_f32) static_cast<float*>(p.y)[o] = v[m];
+          else static_cast<uint16_t*>(p.y)[o] = hb;
+          for (int pq = 0; pq < p.npeers; ++pq) p.y_peers[pq][o] = hb;
+        }
+        if (p.argmax) {
+          const float lv = bf16_bits_to_float(hb);
+          if (better(lv, row, best_v[m], best_i[m])) {
+            best_v[m] = lv;
+            best_i[m] = row;
+          }
+        }
+      }
+    };
+
+    // (tile, first/last contributing CTA, arrival ticket) of up to two split tiles, in lane 0
+    int sp_n = 0, sp_tile0 = 0, sp_cf0 = 0, sp_cl0 = 0, sp_tile1 = 0, sp_cf1 = 0, sp_cl1 = 0;
+    unsigned sp_old0 = 0, sp_old1 = 0;
+    bool waited_pdl = cache;  // the cache-mode conversion above already waited
+    auto before_global_write = [&]() {
+      if (!waited_pdl) {
+        pdl_wait();  // outputs and the shared scratch belong to the previous kernel until now
+        waited_pdl = true;
+      }
+    };
+
+    WorkIter it;
+    it.init(u0, u1, G, p.chunk_groups);
+    Chunk c;
+    int n = 0;
+    bool ok = team_ok;
+    constexpr int FB = GE::FB;
+    constexpr int NLD = MT == 1 ? 4 : (MT == 2 ? 8 : N);
+    TR_DECL;
+    while (ok && it.next(c)) {
+      // FB units per round: one wait per issuer (a commit covers everything its thread issued before),
+      // the rounds' tensor-memory loads in flight together, one wait for all of them.
+      for (int gl = 0; gl < c.n; gl += FB) {
+        const int nb = (c.n - gl < FB) ? c.n - gl : FB;
+        TR_LAP(1);
+        {
+          const int l1 = n + nb - 1, l2 = n + nb - 2;
+          bool w_ok = wait_h(done_a + (l1 & (DD - 1)) * 8, static_cast<uint32_t>(l1 / DD) & 1u, p.hint, kSpinLimit);
+          if (nb > 1)
+            w_ok = w_ok && wait_h(done_a + (l2 & (DD - 1)) * 8, static_cast<uint32_t>(l2 / DD) & 1u, p.hint, kSpinLimit);
+          if (!w_ok) {
+            atomicExch(p.status, W4A16_ETIMEOUT);
+            ok = false;
+            break;
+          }
+        }
+        TR_LAP(0);
+#ifdef W4A16_TRACE
+        if (tid == 0 && n == 0) TL(4);
+#endif
+        tc_fence_after();
+        uint32_t dv[FB][NLD];
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            slot[(warp * 16 + grow + 8 * (j >> 1)) * 8 * NT + nt * 8 + 2 * t + (j & 1)] = fin[nt][j];
+        for (int j = 0; j < FB; ++j)
+          if (j < nb) {
+            const uint32_t d_t = lane_t + ((n + j) & (DD - 1)) * N;
+            if constexpr (MT == 1) tmem_ld4(d_t, dv[j]);
+            else if constexpr (MT == 2) tmem_ld8(d_t, dv[j]);
+            else {
+#pragma unroll
+              for (int i = 0; i < N / 16; ++i) tmem_ld16(d_t + 16 * i, dv[j] + 16 * i);
+            }
+          }
+        tmem_wait_ld();
+        tc_fence_before();
         __syncwarp();
         if (lane == 0) {
-          __threadfence();  // release: this warp's partial rows (ordered by the __syncwarp) before the ticket
-          const unsigned old = atomicAdd(p.counters + tile * CW + warp, 1u);
-          if (sp_n == 0) {
-            sp_tile0 = tile; sp_cf0 = c_first; sp_cl0 = c_last; sp_old0 = old;
-          } else {
-            sp_tile1 = tile; sp_cf1 = c_first; sp_cl1 = c_last; sp_old1 = old;
-          }
-          ++sp_n;
-        }
-      }
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) fin[nt][0] = fin[nt][1] = fin[nt][2] = fin[nt][3] = 0.f;
+          for (int j = 0; j < FB; ++j)
+            if (j < nb) mbar_arrive(dempty_a + ((n + j) & (DD - 1)) * 8);
+        }
+#pragma unroll
+        for (int j = 0; j < FB; ++j)
+          if (j < nb) {
+            const uint32_t xs_a = xsinv_a + (cache ? (c.g + gl + j) * MT : ((n + j) & (kSide - 1)) * 16) * 8;
+            const uint32_t sz = lds32(side_a + (((n + j) & (kSide - 1)) * kTileRows + r) * 4);
+            const float s = __uint_as_float(sz & 0xFFFF0000u);
+            const float z = static_cast<float>(sz & 0xFFu);
+#pragma unroll
+            for (int m = 0; m < MT; ++m)
+              if (m < M) {
+                const uint2 t = lds64(xs_a + m * 8);  // (sum of X, 2^-p)
+                const float d0 = small_int_to_float(dv[j][3 * m]), d1 = small_int_to_float(dv[j][3 * m + 1]);
+                const float d2 = small_int_to_float(dv[j][3 * m + 2]);
+                const float dot = fmaf(d2, 65536.f, fmaf(d1, 256.f, d0));
+                fin[m] = fmaf(s * __uint_as_float(t.y), fmaf(-z, __uint_as_float(t.x), dot), fin[m]);
+              }
+          }
+        n += nb;
+      }
+      if (!ok) break;
+      if (c.seg_last) {
+        // ---- end of this CTA's segment of row tile c.tile: groups [seg_g0, seg_g1) ----
+        before_global_write();
+        const int tile = c.tile;
+        if (c.seg_g0 == 0 && c.seg_g1 == G) {
+          finalize(tile, fin);
+        } else {
+          // split tile: this warp publishes its 32 rows and moves on; no CTA-wide barrier
+          const long long X0 = static_cast<long long>(tile) * G;
+          const int c_first = static_cast<int>(((X0 + 1) * gridDim.x - 1) / U);
+          const int c_last = static_cast<int>(((X0 + G) * gridDim.x - 1) / U);
+          const int which = (u0 / G == tile) ? 0 : 1;
+          float* slot = p.partial + (static_cast<size_t>(blockIdx.x) * 2 + which) * SLOT;
+#pragma unroll
+          for (int m = 0; m < MT; ++m)
+            if (m < M) slot[m * kTileRows + r] = fin[m];
+          __syncwarp();
+          if (lane == 0) {
+            __threadfence();  // release: this warp's partial rows (ordered by the __syncwarp) before the ticket
+            const unsigned old = atomicAdd(p.counters + tile * CW + warp, 1u);
+            if (sp_n == 0) {
+              sp_tile0 = tile; sp_cf0 = c_first; sp_cl0 = c_last; sp_old0 = old;
+            } else {
+              sp_tile1 = tile; sp_cf1 = c_first; sp_cl1 = c_last; sp_old1 = old;
+            }
+            ++sp_n;
+          }
+        }
+#pragma unroll
+        for (int m = 0; m < MT; ++m) fin[m] = 0.f;
+      }
     }
-  }
 
-  // ---- split tiles: the warp that drew the last ticket for its rows adds the pieces up ----
-  {
-    const int n = __shfl_sync(0xffffffffu, sp_n, 0);
-    for (int i = 0; i < n; ++i) {
-      const int tile = __shfl_sync(0xffffffffu, i ? sp_tile1 : sp_tile0, 0);
-      const int c_first = __shfl_sync(0xffffffffu, i ? sp_cf1 : sp_cf0, 0);
-      const int c_last = __shfl_sync(0xffffffffu, i ? sp_cl1 : sp_cl0, 0);
-      const unsigned old = __shfl_sync(0xffffffffu, i ? sp_old1 : sp_old0, 0);
-      if (old != static_cast<unsigned>(c_last - c_first)) continue;  // another warp finishes these rows
+    TR_LAP(1);
+    if (tid == 0) TL(5);
+    if (warp == 0 && lane == 0) TR_OUT(10, 2);  // fix-up: [10] waiting for D, [11] everything else in the main loop
+    // ---- split tiles: the warp that drew the last ticket for its rows adds the pieces up ----
+    if (ok) {
+      const int ns = __shfl_sync(0xffffffffu, sp_n, 0);
+      for (int i = 0; i < ns; ++i) {
+        const int tile = __shfl_sync(0xffffffffu, i ? sp_tile1 : sp_tile0, 0);
+        const int c_first = __shfl_sync(0xffffffffu, i ? sp_cf1 : sp_cf0, 0);
+        const int c_last = __shfl_sync(0xffffffffu, i ? sp_cl1 : sp_cl0, 0);
+        const unsigned old = __shfl_sync(0xffffffffu, i ? sp_old1 : sp_old0, 0);
+        if (old != static_cast<unsigned>(c_last - c_first)) continue;  // another warp finishes these rows
+        if (lane == 0) {
+          p.counters[tile * CW + warp] = 0;  // every contributor has arrived: leave it clean
+          __threadfence();                   // acquire side for the reads below
+        }
+        __syncwarp();
+        float v[MT];
+#pragma unroll
+        for (int m = 0; m < MT; ++m) v[m] = 0.f;
+        for (int cc = c_first; cc <= c_last; ++cc) {  // fixed order: bitwise reproducible
+          const int cu0 = static_cast<int>(static_cast<long long>(U) * cc / gridDim.x);
+          const int wc = (cu0 / G == tile) ? 0 : 1;
+          const float* sl = p.partial + (static_cast<size_t>(cc) * 2 + wc) * SLOT;
+#pragma unroll
+          for (int m = 0; m < MT; ++m)
+            if (m < M) v[m] += __ldcg(sl + m * kTileRows + r);
+        }
+        finalize(tile, v);
+      }
+    }
+
+    if (p.argmax) {
+      before_global_write();
+      // ---- fused argmax: thread -> warp -> CTA -> grid, larger value then lower index ----
+#pragma unroll
+      for (int m = 0; m < MT; ++m)
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          const float ov = __shfl_xor_sync(0xffffffffu, best_v[m], off);
+          const int oi = __shfl_xor_sync(0xffffffffu, best_i[m], off);
+          if (better(ov, oi, best_v[m], best_i[m])) {
+            best_v[m] = ov;
+            best_i[m] = oi;
+          }
+        }
+      named_bar_sync(kFixBar, NFT);
+      // per-warp candidates go through the (now idle) side ring: every unit has been read
+      Pair* cand = reinterpret_cast<Pair*>(side);  // [CW][16]
       if (lane == 0) {
-        p.counters[tile * CW + warp] = 0;  // every contributor has arrived: leave it clean
-        __threadfence();                   // acquire side for the reads below
+#pragma unroll
+        for (int m = 0; m < MT; ++m) cand[warp * 16 + m] = Pair{best_v[m], best_i[m]};
       }
-      __syncwarp();
-      float v[NT][4];
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt) v[nt][0] = v[nt][1] = v[nt][2] = v[nt][3] = 0.f;
-      for (int cc = c_first; cc <= c_last; ++cc) {  // fixed order: bitwise reproducible
-        const int cu0 = static_cast<int>(static_cast<long long>(U) * cc / gridDim.x);
-        const int wc = (cu0 / G == tile) ? 0 : 1;
-        const float* sl = p.partial + (static_cast<size_t>(cc) * 2 + wc) * SLOT;
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            v[nt][j] += __ldcg(sl + (warp * 16 + grow + 8 * (j >> 1)) * 8 * NT + nt * 8 + 2 * t + (j & 1));
-      }
-      finalize(tile, v);
-    }
-  }
-
-  if (dead) {  // let whatever is still in flight land before the CTA exits
-    for (int s = 0; s < D; ++s) mbar_wait_bounded(wfull_a + s * 8, 0, 1u << 16);
-  }
-
-  if (p.argmax) {
-    before_global_write();
-    // ---- fused argmax: thread -> warp -> CTA -> grid, larger value then lower index ----
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc)
-#pragma unroll
-        for (int off = 4; off < 32; off <<= 1) {
-          const float ov = __shfl_xor_sync(0xffffffffu, best_v[nt][cc], off);
-          const int oi = __shfl_xor_sync(0xffffffffu, best_i[nt][cc], off);
-          if (better(ov, oi, best_v[nt][cc], best_i[nt][cc])) {
-            best_v[nt][cc] = ov;
-            best_i[nt][cc] = oi;
-          }
+      named_bar_sync(kFixBar, NFT);
+      Pair* cta_pairs = static_cast<Pair*>(p.cta_pairs);
+      if (tid < M) {
+        Pair b{-FLT_MAX, INT_MAX};
+        for (int w = 0; w < CW; ++w) {
+          const Pair qv = cand[w * 16 + tid];
+          if (better(qv.v, qv.i, b.v, b.i)) b = qv;
         }
-    named_bar_sync(kConsumerBar, NCT);
-    // per-warp candidates go through the (now idle) weight ring: every stage was consumed
-    Pair* cand = reinterpret_cast<Pair*>(ring);  // [CW][16]
-    if (grow == 0) {
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-        for (int cc = 0; cc < 2; ++cc) cand[warp * 16 + nt * 8 + 2 * t + cc] = Pair{best_v[nt][cc], best_i[nt][cc]};
-    }
-    named_bar_sync(kConsumerBar, NCT);
-    Pair* cta_pairs = static_cast<Pair*>(p.cta_pairs);
-    if (tid < M) {
-      Pair b{-FLT_MAX, INT_MAX};
-      for (int w = 0; w < CW; ++w) {
-        const Pair q = cand[w * 16 + tid];
-        if (better(q.v, q.i, b.v, b.i)) b = q;
+        cta_pairs[blockIdx.x * 16 + tid] = b;
       }
-      cta_pairs[blockIdx.x * 16 + tid] = b;
-    }
-    named_bar_sync(kConsumerBar, NCT);
-    if (tid == 0) {
-      __threadfence();
-      const unsigned old = atomicAdd(p.counters + p.tiles * CW, 1u);
-      const int last = (old == gridDim.x - 1);
-      if (last) {
-        p.counters[p.tiles * CW] = 0;
+      named_bar_sync(kFixBar, NFT);
+      if (tid == 0) {
         __threadfence();
+        const unsigned old = atomicAdd(p.counters + p.tiles * CW, 1u);
+        const int last = (old == gridDim.x - 1);
+        if (last) {
+          p.counters[p.tiles * CW] = 0;
+          __threadfence();
+        }
+        *sflag = last;
       }
-      *sflag = last;
-    }
-    named_bar_sync(kConsumerBar, NCT);
-    if (*sflag && tid < M) {
-      Pair b{-FLT_MAX, INT_MAX};
-      for (unsigned cc = 0; cc < gridDim.x; ++cc) {
-        Pair q;
-        q.v = __ldcg(&cta_pairs[cc * 16 + tid].v);
-        q.i = __ldcg(&cta_pairs[cc * 16 + tid].i);
-        if (better(q.v, q.i, b.v, b.i)) b = q;
+      named_bar_sync(kFixBar, NFT);
+      if (*sflag && tid < M) {
+        Pair b{-FLT_MAX, INT_MAX};
+        for (unsigned cc = 0; cc < gridDim.x; ++cc) {
+          Pair qv;
+          qv.v = __ldcg(&cta_pairs[cc * 16 + tid].v);
+          qv.i = __ldcg(&cta_pairs[cc * 16 + tid].i);
+          if (better(qv.v, qv.i, b.v, b.i)) b = qv;
+        }
+        const int idx = (b.i == INT_MAX) ? 0 : b.i;  // nothing finite: index 0, as a plain scan gives
+        if (p.ids) p.ids[tid] = idx + p.row_offset;
+        if (p.pairs_out)
+          static_cast<Pair*>(p.pairs_out)[tid] = Pair{b.v, (b.i == INT_MAX) ? INT_MAX : b.i + p.row_offset};
       }
-      const int idx = (b.i == INT_MAX) ? 0 : b.i;  // nothing finite: index 0, as a plain scan gives
-      if (p.ids) p.ids[tid] = idx + p.row_offset;
-      if (p.pairs_out)
-        static_cast<Pair*>(p.pairs_out)[tid] = Pair{b.v, (b.i == INT_MAX) ? INT_MAX : b.i + p.row_offset};
     }
+  }
+
+  // every role ends here: tensor memory goes back only after all its readers and writers are done
+  tc_fence_before();
+  __syncthreads();
+#ifdef W4A16_TRACE
+  if (tid == 0) {
+    TL(6);
+    g_trace[blockIdx.x * 16 + 13] = clock64() - tr_kernel0;  // whole CTA
+    g_trace[blockIdx.x * 16 + 14] = u1 - u0;
+  }
+#endif
+  if (warp == kWMma) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
   }
 }
 
@@ -645,43 +952,73 @@ __global__ void k_pairs_reduce(int32_t* ids, const Pair* pairs, int nranks, int 
 
 // ------------------------------------------------------------------ host side
 struct Config {
-  int depth;  // weight ring stages (17 KB each)
-  int ctas;   // CTAs per SM
-  int xbuf;   // bytes of one activation chunk buffer
+  int depth;     // weight ring stages (8576 B each)
+  int l2ahead;   // blocks of L2 prefetch ahead of the ring
   int pdl;
+  int cache_kb;  // largest B region (KB) for which all k groups are kept converted in shared memory
+  int smem_kb;   // shared-memory target per CTA that still lets the next launch's CTA fit beside it
+  int hint;      // suspend-time hint of the in-kernel mbarrier waits, ns
 };
 
 const Config& config() {
   static Config c = [] {
-    Config k{4, 2, 8192, 1};
+    Config k{9, 16, 1, 56, 112, 2000};
     if (const char* e = getenv("W4A16_DEPTH")) k.depth = atoi(e);
-    if (const char* e = getenv("W4A16_CTAS")) k.ctas = atoi(e) >= 2 ? 2 : 1;
-    if (const char* e = getenv("W4A16_XBUF")) k.xbuf = atoi(e);
+    if (const char* e = getenv("W4A16_L2AHEAD")) k.l2ahead = atoi(e);
     if (const char* e = getenv("W4A16_PDL")) k.pdl = atoi(e) != 0;
-    if (k.depth != 3 && k.depth != 4 && k.depth != 6) k.depth = 4;
-    if (k.xbuf < 4096) k.xbuf = 4096;
-    if (k.xbuf > 16384) k.xbuf = 16384;
-    k.xbuf &= ~1023;
+    if (const char* e = getenv("W4A16_BCACHE_KB")) k.cache_kb = atoi(e);
+    if (const char* e = getenv("W4A16_SMEM_KB")) k.smem_kb = atoi(e);
+    if (const char* e = getenv("W4A16_HINT")) k.hint = atoi(e);
+    if (k.hint < 0) k.hint = 0;
+    if (k.depth < 3) k.depth = 3;
+    if (k.depth > 20) k.depth = 20;
+    if (k.l2ahead < 0) k.l2ahead = 0;
+    if (k.l2ahead > 256) k.l2ahead = 256;
+    if (k.cache_kb < 0) k.cache_kb = 0;
     return k;
   }();
   return c;
 }
 
-constexpr int kMaxCtasPerSm = 2;
+constexpr int kMaxCtasPerSm = 2;  // what the scratch is sized for (the grid itself is one CTA per SM)
 
-template <int NT, int D>
-int launch_cfg(SkinnyParams& p, int grid, cudaStream_t st) {
-  const int smem = skinny_fixed_smem<D>() + kXBufs * p.xbuf_bytes;
+template <int MT>
+int launch_cfg(SkinnyParams& p, int grid, cudaStream_t st, int smem_optin) {
+  using GE = Geo<MT>;
+  const int M = p.M, G = p.G;
+  const int cache_bytes = G * 384 * M + 256;
+  p.cache = cache_bytes <= config().cache_kb * 1024;
+  if (p.cache) {
+    p.b_slot = 384 * M;
+    p.b_lbo = 48 * M;
+    p.b_bytes = cache_bytes;
+    p.xs_bytes = G * MT * 8;
+    p.xbuf_bytes = 0;
+  } else {
+    p.b_slot = GE::kBBytes;
+    p.b_lbo = GE::kLbo;
+    p.b_bytes = GE::AD * GE::kBBytes;
+    p.xs_bytes = kSide * 16 * 8;
+  }
+  // ring depth: as configured, but inside the per-CTA target (two launches side by side) when possible
+  int limit = config().smem_kb * 1024;
+  if (limit > smem_optin) limit = smem_optin;
+  int smem = total_smem<MT>(p.depth, p.b_bytes, p.xbuf_bytes, p.xs_bytes);
+  while (smem > limit && p.depth > 4) {
+    --p.depth;
+    smem = total_smem<MT>(p.depth, p.b_bytes, p.xbuf_bytes, p.xs_bytes);
+  }
+  if (smem > smem_optin) return fail(W4A16_EINVAL, "decode kernel needs %d bytes of shared memory, device offers %d", smem, smem_optin);
   static int attr_set[64] = {};
   int dev = 0;
   W4_CUDA(cudaGetDevice(&dev));
   if (attr_set[dev & 63] < smem) {
-    W4_CUDA(cudaFuncSetAttribute(k_skinny<NT, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    W4_CUDA(cudaFuncSetAttribute(k_skinny<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set[dev & 63] = smem;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(kWarps * 32);
+  cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute at[1];
@@ -689,17 +1026,8 @@ int launch_cfg(SkinnyParams& p, int grid, cudaStream_t st) {
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
   cfg.numAttrs = config().pdl ? 1 : 0;
-  W4_CUDA(cudaLaunchKernelEx(&cfg, k_skinny<NT, D>, p));
+  W4_CUDA(cudaLaunchKernelEx(&cfg, k_skinny<MT>, p));
   return W4A16_OK;
-}
-
-template <int NT>
-int launch_depth(SkinnyParams& p, int grid, cudaStream_t st) {
-  switch (config().depth) {
-    case 3: return launch_cfg<NT, 3>(p, grid, st);
-    case 6: return launch_cfg<NT, 6>(p, grid, st);
-    default: return launch_cfg<NT, 4>(p, grid, st);
-  }
 }
 
 int tile_rows() { return kTileRows; }
@@ -707,8 +1035,7 @@ int tile_rows() { return kTileRows; }
 int grid_for_shape(int out_f, int G, int sms) {
   const int tiles = (out_f + tile_rows() - 1) / tile_rows();
   const long long U = static_cast<long long>(tiles) * G;
-  const long long want = static_cast<long long>(sms) * config().ctas;
-  return static_cast<int>(U < want ? U : want);
+  return static_cast<int>(U < sms ? U : sms);
 }
 
 int launch_skinny(SkinnyParams& p, const w4a16_weights_t* w, const uint16_t* x, int M, w4a16_scratch_t* s,
@@ -731,19 +1058,22 @@ int launch_skinny(SkinnyParams& p, const w4a16_weights_t* w, const uint16_t* x, 
   p.counters = reinterpret_cast<unsigned*>(s->xgsum);
   p.cta_pairs = s->xf;
   p.status = di->status;
-  // groups per activation chunk: what one buffer holds (256 B per token per group), even.
-  // Token rows sit 16 bytes past a multiple of 128 apart, which keeps the B-fragment loads of
-  // neighbouring token rows on different banks.
-  int cg = config().xbuf / (256 * M);
+  p.depth = config().depth;
+  p.hint = static_cast<uint32_t>(config().hint);
+  p.l2ahead = config().l2ahead;
+  // groups per raw activation chunk: about 2 KB per buffer (256 B per token per group)
+  int cg = 2048 / (256 * M);
   if (cg > kMaxChunkGroups) cg = kMaxChunkGroups;
-  cg &= ~1;
   if (cg < 2) cg = 2;
   p.chunk_groups = cg;
-  p.xrow_bytes = cg * 256 + 16;
-  p.xbuf_bytes = (M * p.xrow_bytes + 127) & ~127;
+  p.xbuf_bytes = M * cg * 256;
   const int grid = grid_for_shape(w->out_f, w->num_groups, di->sms);
   if (int rc = w4a16_scratch_check(s, w->out_f, M)) return rc;
-  return M <= 8 ? launch_depth<1>(p, grid, st) : launch_depth<2>(p, grid, st);
+  if (M == 1) return launch_cfg<1>(p, grid, st, di->smem_optin);
+  if (M == 2) return launch_cfg<2>(p, grid, st, di->smem_optin);
+  if (M <= 5) return launch_cfg<5>(p, grid, st, di->smem_optin);
+  if (M <= 10) return launch_cfg<10>(p, grid, st, di->smem_optin);
+  return launch_cfg<16>(p, grid, st, di->smem_optin);
 }
 
 }  // namespace
@@ -752,6 +1082,19 @@ int launch_skinny(SkinnyParams& p, const w4a16_weights_t* w, const uint16_t* x, 
 using namespace w4a16;
 
 extern "C" {
+
+#ifdef W4A16_TRACE
+__attribute__((visibility("default"))) int w4a16_debug_trace(long long* dst, int n) {
+  W4_CUDA(cudaDeviceSynchronize());
+  W4_CUDA(cudaMemcpyFromSymbol(dst, g_trace, sizeof(long long) * n));
+  return 0;
+}
+__attribute__((visibility("default"))) int w4a16_debug_timeline(long long* dst, int n) {
+  W4_CUDA(cudaDeviceSynchronize());
+  W4_CUDA(cudaMemcpyFromSymbol(dst, g_tline, sizeof(long long) * n));
+  return 0;
+}
+#endif
 
 int w4a16_scratch_alloc(w4a16_scratch_t* s, int max_in, int max_out, int min_group, int max_m) {
   W4_REQUIRE(s != nullptr, "scratch_alloc: null struct");
