@@ -53,18 +53,22 @@ constexpr int kWarps = 16;
 constexpr int kThreads = kWarps * 32;
 constexpr int kWUnpack0 = 4;               // warps 4..11 unpack
 constexpr int kWProducer = 12;
-constexpr int kWMma = 13;
-constexpr int kWAct = 14;
-constexpr int kWMma2 = 15;                 // second MMA issuer (odd units)
-constexpr int kSide = 16;                  // depth of the (scale, zp) and (sum, 2^-p) side rings: a slot is
-                                           // rewritten only after the fix-up of its previous unit has finished
-constexpr int kXBufs = 2;                  // raw activation chunk buffers
-constexpr int kFirstChunk = 2;             // groups in a CTA's first activation chunk (short start-up)
-constexpr int kMaxChunkGroups = 16;        // bound on groups per activation chunk
+constexpr int kWMma = 13;                  // MMA issuer of the even steps; owns the tensor-memory allocation
+constexpr int kWAct = 14;                  // activation warp of ring mode
+constexpr int kWMma2 = 15;                 // MMA issuer of the odd steps
+constexpr int kTeam = kWarps - 2;          // warps that convert activations in cache mode (all but producer, kWMma)
+constexpr int kStepGroups = 2;             // k groups per step: every hand-off between roles moves two groups
+constexpr int kStageBytes = kStepGroups * kTileGroupBytes;  // 17152
+constexpr int kSide = 16;                  // groups in the (scale, zp) side ring
+constexpr int kXsRing = 32;                // groups in the (sum, 2^-p) ring of ring mode
+constexpr int kXBufs = 2;                  // raw activation chunk buffers (ring mode)
+constexpr int kFirstChunk = 2;             // groups in a CTA's first chunk (short start-up)
+constexpr int kMaxChunkGroups = 16;        // bound on groups per chunk
 constexpr uint32_t kSpinLimit = 1u << 20;  // polls before a wait gives up
 constexpr int kFixBar = 1;                 // named barrier of the fix-up warps
-constexpr int kTmemCols = 256;             // half of tensor memory: the next launch's CTA gets the other half
-constexpr int kACols = 32;                 // 128 int8 along k = 32 columns of 32 bits
+constexpr int kTmemCols = 512;             // all of tensor memory; the next launch's CTA, resident beside this one,
+                                           // gets it when this CTA exits (it cannot multiply before that anyway)
+constexpr int kAColsG = 32;                // 128 int8 along k = 32 columns of 32 bits per group
 
 #ifdef W4A16_TRACE
 // Development aid (compiled only with -DW4A16_TRACE): per-CTA cycle counts of what each role waits for.
@@ -82,20 +86,26 @@ __device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u6
 #define TR_OUT(base, n)
 #endif
 
-// Per token-count geometry. N = rows of the B operand (3 digit rows per token, padded to 16);
-// AD = depth of the A (tensor memory) and B (shared memory) rings, DD = depth of the D ring.
+// Per token-count geometry. N = rows of the B operand (3 digit rows per token, padded to 16).
+// Ring depths are in steps: AD2 for A (tensor memory) and, in ring mode, B (shared memory);
+// DD2 for D (tensor memory) and for the ring of "step done" barriers.
 template <int MT>
 struct Geo {
   static constexpr int N = MT <= 5 ? 16 : (MT <= 10 ? 32 : 48);
-  static constexpr int AD = N == 48 ? 2 : 4;
-  static constexpr int DD = N == 16 ? 8 : 4;             // also the depth of the "unit done" barrier ring
-  static constexpr int FB = MT == 1 ? 4 : (MT == 2 ? 2 : 1);  // units the fix-up warps take per round
-  static constexpr int kBBytes = N * 128;       // [8 k-chunks of 16][N/8][8 rows][16 B]
-  static constexpr int kLbo = (N / 8) * 128;    // between core matrices along k
-  static constexpr int kDCol0 = AD * kACols;    // first D column
+  static constexpr int AD2 = N == 48 ? 2 : 4;
+  static constexpr int DD2 = N == 16 ? 8 : 4;
+  static constexpr int kAColsS = kStepGroups * kAColsG;  // A columns per step
+  static constexpr int kDColsS = kStepGroups * N;        // D columns per step
+  static constexpr int kDCol0 = AD2 * kAColsS;           // first D column
+  static constexpr int RG = MT == 1 ? 4 : 2;             // groups the fix-up warps take per round
+  static constexpr int GB = MT == 1 ? 4 : (MT == 2 ? 2 : 1);  // groups whose tensor-memory loads are in flight together
+  static constexpr int kBGroup = N * 128;                // ring mode: bytes of one group's B block
+  static constexpr int kLbo = (N / 8) * 128;             // ring mode: between core matrices along k
   static constexpr int kMinCtas = MT <= 5 ? 2 : 1;
-  static_assert(AD * kACols + DD * N <= kTmemCols, "tensor memory budget");
-  static_assert(AD + DD + FB <= kSide && 2 * FB <= DD && AD <= DD, "ring depths");
+  static_assert(kDCol0 + DD2 * kDColsS <= kTmemCols, "tensor memory budget");
+  static_assert(AD2 <= DD2 && RG / kStepGroups <= DD2 / 2, "ring depths");
+  static_assert(kStepGroups * DD2 <= kSide, "a (scale, zp) slot is read before the D slot of its step is released");
+  static_assert(kStepGroups * (AD2 + DD2 + RG / kStepGroups) <= kXsRing, "(sum, 2^-p) ring depth");
 };
 
 struct SkinnyParams {
@@ -212,6 +222,13 @@ struct WorkIter {
 };
 
 // ---- PTX used only here ------------------------------------------------------------------
+// One lane of the (converged) warp; unlike a test of the lane index this keeps the code around it
+// warp-uniform for the compiler, so tensor-core operands stay in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
 // Bounded wait with a per-launch suspend hint: how long one try_wait may park the thread.
 __device__ __forceinline__ bool wait_h(uint32_t bar, uint32_t parity, uint32_t hint_ns, uint32_t limit) {
   for (uint32_t i = 0; i < limit; ++i)
@@ -274,7 +291,7 @@ __device__ __forceinline__ float small_int_to_float(uint32_t v) {
 }
 
 // dynamic shared memory:
-//   [weight ring: depth x 8576][B region: b_bytes][raw x: kXBufs x xbuf_bytes][(scale,zp) ring: kSide x 128 x 4]
+//   [weight ring: depth x 17152][B region: b_bytes][raw x: kXBufs x xbuf_bytes][(scale,zp) ring: kSide x 128 x 4]
 //   [(sum, 2^-p) region: xs_bytes][mbarriers][tmem base, flag]
 // The B operand of one k group is eight 16-k chunks, `b_lbo` bytes apart, each holding the token digit
 // rows as consecutive 16-byte rows (row n at 16 n; an 8-row core matrix every 128 bytes).
@@ -284,40 +301,43 @@ __device__ __forceinline__ float small_int_to_float(uint32_t v) {
 //               reads, and the whole K range of a token fits: 384 bytes per group for M = 1.
 template <int MT>
 __host__ __device__ constexpr int bar_count(int depth) {
-  return 2 * depth + 2 * Geo<MT>::AD + 2 * Geo<MT>::DD + kXBufs + 1;
+  return 2 * depth + 2 * Geo<MT>::AD2 + 2 * Geo<MT>::DD2 + kXBufs + 2;
 }
 template <int MT>
 __host__ __device__ inline int total_smem(int depth, int b_bytes, int xbuf_bytes, int xs_bytes) {
-  return depth * kTileGroupBytes + b_bytes + kXBufs * xbuf_bytes + kSide * kTileRows * 4 + xs_bytes +
+  return depth * kStageBytes + b_bytes + kXBufs * xbuf_bytes + kSide * kTileRows * 4 + xs_bytes +
          bar_count<MT>(depth) * 8 + 16;
 }
 
 // One token's 128 values of one k group (this lane: k = 4 lane .. 4 lane + 3, `rv`) -> three int8 digit
 // rows of the B operand at `bslot` (rows 3m, 3m+1, 3m+2) and (sum of X, 2^-p) at `xs`.
+//   X = rint(x * 2^p), p chosen per group so that the largest |X| lies in [2^21, 2^22).
+//   The fp32 magic constant 1.5 * 2^23 makes the FMA deliver X in the low mantissa bits; adding 0x808080
+//   turns the balanced base-256 digits (d0, d1 in [-128,127], |d2| <= 64) into plain bytes, the XOR
+//   with 0x808080 turns those bytes back into signed digits: X = d0 + 2^8 d1 + 2^16 d2.
 // K index j of the operand holds k = 8 (j/8) + perm(j%8) with perm = {0,4,1,5,2,6,3,7}: the order in which
 // the two nibble masks deliver a packed word's weights.
 __device__ __forceinline__ void convert_group(uint2 rv, uint8_t* bslot, int lbo, int m, float2* xs, int lane) {
-  const float f0 = __uint_as_float(rv.x << 16), f1 = __uint_as_float(rv.x & 0xFFFF0000u);
-  const float f2 = __uint_as_float(rv.y << 16), f3 = __uint_as_float(rv.y & 0xFFFF0000u);
-  const uint32_t am = max(max(__float_as_uint(fabsf(f0)), __float_as_uint(fabsf(f1))),
-                          max(__float_as_uint(fabsf(f2)), __float_as_uint(fabsf(f3))));
-  const uint32_t e = __reduce_max_sync(0xffffffffu, am) >> 23;
-  // 2^p with p = 148 - e puts the largest magnitude into [2^21, 2^22)
+  const uint32_t mx = __vmaxu2(rv.x & 0x7FFF7FFFu, rv.y & 0x7FFF7FFFu);
+  const uint32_t am = max(mx & 0xFFFFu, mx >> 16);               // bf16 bits of the lane's largest magnitude
+  const uint32_t e = __reduce_max_sync(0xffffffffu, am) >> 7;    // its biased exponent, group-wide
+  // 2^p with p = 148 - e puts the largest magnitude into [2^21, 2^22); tiny groups are capped at 2^123
   const uint32_t me = min(275u - e, 250u);
   const float mult = (e == 255u) ? 0.f : __uint_as_float(me << 23);
-  const float inv = (e == 255u) ? __uint_as_float(0x7FC00000u) : __uint_as_float((254u - me) << 23);
-  const int X0 = __float2int_rn(f0 * mult), X1 = __float2int_rn(f1 * mult);
-  const int X2 = __float2int_rn(f2 * mult), X3 = __float2int_rn(f3 * mult);
-  const int tot = __reduce_add_sync(0xffffffffu, (X0 + X1) + (X2 + X3));
-  // balanced base-256 digits: X = d0 + 2^8 d1 + 2^16 d2, d0, d1 in [-128, 127], |d2| <= 65
-  const int a0 = (X0 << 24) >> 24, a1 = (X1 << 24) >> 24, a2 = (X2 << 24) >> 24, a3 = (X3 << 24) >> 24;
-  const int r0 = (X0 - a0) >> 8, r1 = (X1 - a1) >> 8, r2 = (X2 - a2) >> 8, r3 = (X3 - a3) >> 8;
-  const int b0 = (r0 << 24) >> 24, b1 = (r1 << 24) >> 24, b2 = (r2 << 24) >> 24, b3 = (r3 << 24) >> 24;
-  const int c0 = (r0 - b0) >> 8, c1 = (r1 - b1) >> 8, c2 = (r2 - b2) >> 8, c3 = (r3 - b3) >> 8;
-  auto pack = [](int v0, int v1, int v2, int v3) {
-    return __byte_perm(__byte_perm(v0, v1, 0x0040), __byte_perm(v2, v3, 0x0040), 0x5410);
-  };
-  const uint32_t P0 = pack(a0, a1, a2, a3), P1 = pack(b0, b1, b2, b3), P2 = pack(c0, c1, c2, c3);
+  const float inv = (e == 255u) ? __uint_as_float(0x7FC00000u) : __uint_as_float((254u - me) << 23);  // NaN for inf/NaN input
+  const float f0 = __uint_as_float(rv.x << 16), f1 = __uint_as_float(rv.x & 0xFFFF0000u);
+  const float f2 = __uint_as_float(rv.y << 16), f3 = __uint_as_float(rv.y & 0xFFFF0000u);
+  constexpr float kMagic = 12582912.0f;  // 0x4B400000
+  const uint32_t u0 = __float_as_uint(fmaf(f0, mult, kMagic)), u1 = __float_as_uint(fmaf(f1, mult, kMagic));
+  const uint32_t u2 = __float_as_uint(fmaf(f2, mult, kMagic)), u3 = __float_as_uint(fmaf(f3, mult, kMagic));
+  const int tot = __reduce_add_sync(0xffffffffu, static_cast<int>((u0 + u1) + (u2 + u3) - 4u * 0x4B400000u));
+  constexpr uint32_t kOff = 0x00808080u - 0x4B400000u;
+  const uint32_t D0 = (u0 + kOff) ^ 0x00808080u, D1 = (u1 + kOff) ^ 0x00808080u;
+  const uint32_t D2 = (u2 + kOff) ^ 0x00808080u, D3 = (u3 + kOff) ^ 0x00808080u;
+  // 4 x 3 byte transpose: digit planes of the lane's four k
+  const uint32_t t01 = __byte_perm(D0, D1, 0x5140), t23 = __byte_perm(D2, D3, 0x5140);
+  const uint32_t P0 = __byte_perm(t01, t23, 0x5410), P1 = __byte_perm(t01, t23, 0x7632);
+  const uint32_t P2 = __byte_perm(__byte_perm(D0, D1, 0x0062), __byte_perm(D2, D3, 0x0062), 0x5410);
   const uint32_t Q0 = __shfl_xor_sync(0xffffffffu, P0, 1), Q1 = __shfl_xor_sync(0xffffffffu, P1, 1);
   const uint32_t Q2 = __shfl_xor_sync(0xffffffffu, P2, 1);
   // even lane: k offsets 0..3 of its 8-block -> operand bytes {E0,O0,E1,O1}; odd lane: {E2,O2,E3,O3}
@@ -332,44 +352,50 @@ __device__ __forceinline__ void convert_group(uint2 rv, uint8_t* bslot, int lbo,
 template <int MT>
 __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const SkinnyParams p) {
   using GE = Geo<MT>;
-  constexpr int N = GE::N, AD = GE::AD, DD = GE::DD;
+  constexpr int N = GE::N, AD2 = GE::AD2, DD2 = GE::DD2;
   constexpr int SLOT = kTileRows * MT;  // floats per partial tile
   constexpr int NFT = CW * 32;          // fix-up threads
   extern __shared__ __align__(128) uint8_t smem[];
 
   const int DS = p.depth;
   uint8_t* ring = smem;
-  uint8_t* bq = ring + DS * kTileGroupBytes;
+  uint8_t* bq = ring + DS * kStageBytes;
   uint8_t* xraw = bq + p.b_bytes;
   uint8_t* side = xraw + kXBufs * p.xbuf_bytes;
   uint8_t* xsinv = side + kSide * kTileRows * 4;
   uint64_t* bars = reinterpret_cast<uint64_t*>(xsinv + p.xs_bytes);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + bar_count<MT>(DS));
-  const bool cache = p.cache != 0;
   int* sflag = reinterpret_cast<int*>(tmem_slot + 1);
+  const bool cache = p.cache != 0;
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // the same value, but provably warp-uniform
   const int G = p.G, M = p.M;
   const int U = p.tiles * G;
   if (tid == 0) TL(0);
   const int u0 = static_cast<int>(static_cast<long long>(U) * blockIdx.x / gridDim.x);
   const int u1 = static_cast<int>(static_cast<long long>(U) * (blockIdx.x + 1) / gridDim.x);
 
+  // cache mode keeps the digit rows of the groups this CTA multiplies, (g_first + j) % G for j < min(G, u1 - u0),
+  // in slot j
+  const int g_first = u0 % G;
+  auto cache_slot = [&](int g) { return g - g_first + (g < g_first ? G : 0); };
+
   const uint32_t ring_a = smem_u32(ring);
   const uint32_t bq_a = smem_u32(bq);
   const uint32_t xraw_a = smem_u32(xraw);
   const uint32_t side_a = smem_u32(side);
   const uint32_t xsinv_a = smem_u32(xsinv);
-  const uint32_t wfull_a = smem_u32(bars);          // [DS] weights landed (tx bytes)
-  const uint32_t wempty_a = wfull_a + DS * 8;       // [DS] stage free again (4 unpack warps)
-  const uint32_t afull_a = wempty_a + DS * 8;       // [AD] A slot written (4 unpack warps)
-  const uint32_t bfull_a = afull_a + AD * 8;        // [AD] B slot written (activation warp)
-  const uint32_t done_a = bfull_a + AD * 8;         // [DD] unit n's MMAs have completed (tcgen05.commit): its sums are
-                                                    //      in D slot n % DD, its A and B slots n % AD are free again
-  const uint32_t dempty_a = done_a + DD * 8;        // [DD] D slot read out (4 fix-up warps)
-  const uint32_t xfull_a = dempty_a + DD * 8;       // [kXBufs] raw activation chunk landed
-  const uint32_t bready_a = xfull_a + kXBufs * 8;   // cache mode: every group's digit rows are written
-  constexpr int kTeam = kWarps - 2;                 // warps that convert in cache mode (all but producer, mma)
+  const uint32_t wfull_a = smem_u32(bars);          // [DS]  weights of a step landed (tx bytes)
+  const uint32_t wempty_a = wfull_a + DS * 8;       // [DS]  stage free again (4 unpack warps)
+  const uint32_t afull_a = wempty_a + DS * 8;       // [AD2] A slot written (4 unpack warps)
+  const uint32_t bfull_a = afull_a + AD2 * 8;       // [AD2] ring mode: B slot written (activation warp)
+  const uint32_t done_a = bfull_a + AD2 * 8;        // [DD2] step t's MMAs have completed (tcgen05.commit): its sums are
+                                                    //       in D slot t % DD2, its A and B slots t % AD2 are free again
+  const uint32_t dempty_a = done_a + DD2 * 8;       // [DD2] D slot read out (4 fix-up warps)
+  const uint32_t xfull_a = dempty_a + DD2 * 8;      // [kXBufs] ring mode: raw activation chunk landed
+  const uint32_t bready_a = xfull_a + kXBufs * 8;   // cache mode: every needed group's digit rows are written
+  const uint32_t tmemrdy_a = bready_a + 8;          // tensor memory allocated, base address published
 
   // rows of B that carry no token stay zero for the whole kernel
   for (int i = tid; i < p.b_bytes / 16; i += kThreads) reinterpret_cast<uint4*>(bq)[i] = make_uint4(0, 0, 0, 0);
@@ -378,47 +404,56 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
       mbar_init(wfull_a + i * 8, 1);
       mbar_init(wempty_a + i * 8, 4);
     }
-    for (int i = 0; i < AD; ++i) {
+    for (int i = 0; i < AD2; ++i) {
       mbar_init(afull_a + i * 8, 4);
       mbar_init(bfull_a + i * 8, 1);
     }
-    for (int i = 0; i < DD; ++i) {
+    for (int i = 0; i < DD2; ++i) {
       mbar_init(done_a + i * 8, 1);
       mbar_init(dempty_a + i * 8, CW);
     }
     for (int i = 0; i < kXBufs; ++i) mbar_init(xfull_a + i * 8, 1);
     mbar_init(bready_a, kTeam);
+    mbar_init(tmemrdy_a, 1);
     fence_mbar_init();
   }
-  if (warp == kWMma) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
-  fence_proxy_async();  // the zeroed B ring is read by the tensor core (async proxy)
-  tc_fence_before();
+  fence_proxy_async();  // the zeroed B region is read by the tensor core (async proxy)
   __syncthreads();
-  tc_fence_after();
   pdl_launch_dependents();
-  const uint32_t tmem = *tmem_slot;
   if (tid == 0) TL(1);
 #ifdef W4A16_TRACE
   const long long tr_kernel0 = clock64();
 #endif
 
+  // The previous launch's CTA on this SM may still hold tensor memory: only this warp waits for it.
+  if (warp == kWMma) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(tmemrdy_a);
+  }
+
   bool team_ok = true;
   if (cache && warp != kWProducer && warp != kWMma) {
-    // ================================================================ cache mode: convert every k group once
-    // All warps but the producer and the MMA issuer take part (their own work cannot start before the
-    // activations exist anyway). x comes straight from global memory (L2), four groups in flight per warp.
+    // ================================================================ cache mode: convert the k groups this CTA needs
+    // All warps but the producer and the allocating warp take part (their own work cannot start before
+    // the activations exist anyway). x comes straight from global memory (L2); a round's loads are all in
+    // flight before its first conversion.
     pdl_wait();  // the previous kernel produced x
     if (tid == 0) TL(2);
     const int ti = warp < kWProducer ? warp : warp - 2;
-    const int total = G * M;  // (group, token) items, group-major; item i belongs to warp i % kTeam
-    constexpr int kBatch = 12;
+    const int cnt = (u1 - u0 < G) ? u1 - u0 : G;
+    const int total = cnt * M;  // (group, token) items; item i belongs to warp i % kTeam
+    constexpr int kBatch = 4;
     for (int i0 = ti; i0 < total; i0 += kBatch * kTeam) {
-      uint2 rv[kBatch];  // all loads of the round are in flight before the first conversion
+      uint2 rv[kBatch];
 #pragma unroll
       for (int j = 0; j < kBatch; ++j) {
         const int i = i0 + j * kTeam;
         if (i < total) {
-          const int g = i / M, m = i - g * M;
+          const int gj = i / M, m = i - gj * M;
+          int g = g_first + gj;
+          if (g >= G) g -= G;
           rv[j] = __ldcg(reinterpret_cast<const uint2*>(p.x + static_cast<size_t>(m) * p.K + g * kGroup) + lane);
         }
       }
@@ -426,8 +461,10 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
       for (int j = 0; j < kBatch; ++j) {
         const int i = i0 + j * kTeam;
         if (i < total) {
-          const int g = i / M, m = i - g * M;
-          convert_group(rv[j], bq + g * p.b_slot, p.b_lbo, m, reinterpret_cast<float2*>(xsinv) + g * MT + m, lane);
+          const int gj = i / M, m = i - gj * M;
+          int g = g_first + gj;
+          if (g >= G) g -= G;
+          convert_group(rv[j], bq + gj * p.b_slot, p.b_lbo, m, reinterpret_cast<float2*>(xsinv) + gj * MT + m, lane);
         }
       }
     }
@@ -445,12 +482,24 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
     }
   }
 
+  // This CTA owns all 512 columns, so its tensor-memory addresses start at 0: a compile-time constant
+  // keeps every tcgen05 address warp-uniform. (Checked once; anything else is reported, not used.)
+  constexpr uint32_t tmem = 0;
+  const bool uses_tmem = warp < kWProducer || warp == kWMma || warp == kWMma2;
+  if (uses_tmem) {
+    if (!wait_h(tmemrdy_a, 0, p.hint, kSpinLimit) || *reinterpret_cast<volatile uint32_t*>(tmem_slot) != 0u) {
+      atomicExch(p.status, W4A16_ETIMEOUT);
+      team_ok = false;
+    }
+    tc_fence_after();
+  }
+
   if (warp == kWProducer) {
     // ================================================================ weight producer
-    // One thread streams this CTA's share of the weight stream, one (tile, group) block per bulk
-    // copy. It does not wait for the previous kernel: weights never depend on it. A second cursor
-    // runs `l2ahead` blocks further and only pulls them into L2, so HBM stays busy while this
-    // kernel waits for its activations, and the ring refills at L2 speed afterwards.
+    // One thread streams this CTA's share of the weight stream, one step (two consecutive (tile, group)
+    // blocks, 17 KB) per bulk copy. It does not wait for the previous kernel: weights never depend on it.
+    // A second cursor runs `l2ahead` blocks further and only pulls them into L2, so HBM stays busy while
+    // this kernel waits for its activations, and the ring refills at L2 speed afterwards.
     if (lane == 0) {
       WorkIter it, pf;
       it.init(u0, u1, G, p.chunk_groups);
@@ -474,7 +523,8 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
       bool ok = true;
       TR_DECL;
       while (ok && it.next(c)) {
-        for (int gi = 0; gi < c.n; ++gi) {
+        for (int gl = 0; gl < c.n; gl += kStepGroups) {
+          const int ng = (c.n - gl < kStepGroups) ? c.n - gl : kStepGroups;
           TR_LAP(1);
           if (!mbar_wait_bounded_relaxed(wempty_a + st * 8, ph, kSpinLimit)) {
             atomicExch(p.status, W4A16_ETIMEOUT);
@@ -482,12 +532,11 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
             break;
           }
           TR_LAP(0);
-          mbar_expect_tx(wfull_a + st * 8, kTileGroupBytes);
-          bulk_g2s(ring_a + st * kTileGroupBytes,
-                   p.stream + (static_cast<size_t>(c.tile) * G + c.g + gi) * kTileGroupBytes, kTileGroupBytes,
-                   wfull_a + st * 8);
+          mbar_expect_tx(wfull_a + st * 8, ng * kTileGroupBytes);
+          bulk_g2s(ring_a + st * kStageBytes, p.stream + (static_cast<size_t>(c.tile) * G + c.g + gl) * kTileGroupBytes,
+                   ng * kTileGroupBytes, wfull_a + st * 8);
           ++issued;
-          --ahead;
+          ahead -= ng;
           if (++st == DS) {
             st = 0;
             ph ^= 1;
@@ -504,9 +553,9 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
     }
   } else if (warp == kWMma || warp == kWMma2) {
     // ================================================================ MMA issuers
-    // Two threads, even and odd units. Issuing four small MMAs and a commit costs one thread several
-    // hundred cycles, more than a unit's share of the HBM time; two issuers run side by side.
-    if (lane == 0) {
+    // Two threads, even and odd steps. Issuing a step's eight small MMAs and its commit costs one thread
+    // more than the step's share of the HBM time; two issuers run side by side.
+    if (team_ok) {
       constexpr uint32_t idesc = umma_idesc_s8(128, N);
       const int mine = (warp == kWMma) ? 0 : 1;
       bool ok = true;
@@ -518,16 +567,17 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
       it.init(u0, u1, G, p.chunk_groups);
       Chunk c;
       const uint32_t lbo = p.b_lbo;
-      // descriptor of B slot 0, first 32-k step; other slots and steps only move the address field
+      // descriptor of the B region's first block, first 32-k step; other blocks and steps only move the address field
       const uint64_t desc0 = umma_desc_kmajor(bq_a, lbo, 128);
       const uint32_t step16 = (2 * lbo) >> 4, slot16 = static_cast<uint32_t>(p.b_slot) >> 4;
-      int n = 0;
+      int t = 0;
       TR_DECL;
       while (ok && it.next(c)) {
-        for (int gl = 0; gl < c.n; ++gl, ++n) {
-          if ((n & 1) != mine) continue;
-          const int a = n & (AD - 1), d = n & (DD - 1);
-          const uint32_t aph = static_cast<uint32_t>(n / AD) & 1u;
+        for (int gl = 0; gl < c.n; gl += kStepGroups, ++t) {
+          if ((t & 1) != mine) continue;
+          const int ng = (c.n - gl < kStepGroups) ? c.n - gl : kStepGroups;
+          const int a = t & (AD2 - 1), d = t & (DD2 - 1);
+          const uint32_t aph = static_cast<uint32_t>(t / AD2) & 1u;
           TR_LAP(3);
           // A written (its writers also saw the D slot drained), and in ring mode B written
           bool w_ok = wait_h(afull_a + a * 8, aph, p.hint, kSpinLimit);
@@ -540,22 +590,32 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
             break;
           }
           tc_fence_after();
-          const uint32_t d_t = tmem + GE::kDCol0 + d * N;
-          const uint32_t a_t = tmem + a * kACols;
-          const uint64_t db = desc0 + static_cast<uint32_t>(cache ? c.g + gl : a) * slot16;
-          umma_s8_ts(d_t, a_t, db, idesc, 0);
-          umma_s8_ts(d_t, a_t + 8, db + step16, idesc, 1);
-          umma_s8_ts(d_t, a_t + 16, db + 2 * step16, idesc, 1);
-          umma_s8_ts(d_t, a_t + 24, db + 3 * step16, idesc, 1);
-          umma_commit(done_a + d * 8);
+          const uint32_t d_t = tmem + GE::kDCol0 + d * GE::kDColsS;
+          const uint32_t a_t = tmem + a * GE::kAColsS;
+          const uint64_t db0 = desc0 + static_cast<uint32_t>(cache ? cache_slot(c.g + gl) : a * kStepGroups) * slot16;
+          const uint64_t db1 = desc0 + static_cast<uint32_t>(cache ? cache_slot(c.g + gl + 1) : a * kStepGroups + 1) * slot16;
+          if (elect_one()) {
+            umma_s8_ts(d_t, a_t, db0, idesc, 0);
+            umma_s8_ts(d_t, a_t + 8, db0 + step16, idesc, 1);
+            umma_s8_ts(d_t, a_t + 16, db0 + 2 * step16, idesc, 1);
+            umma_s8_ts(d_t, a_t + 24, db0 + 3 * step16, idesc, 1);
+            if (ng == 2) {
+              umma_s8_ts(d_t + N, a_t + kAColsG, db1, idesc, 0);
+              umma_s8_ts(d_t + N, a_t + kAColsG + 8, db1 + step16, idesc, 1);
+              umma_s8_ts(d_t + N, a_t + kAColsG + 16, db1 + 2 * step16, idesc, 1);
+              umma_s8_ts(d_t + N, a_t + kAColsG + 24, db1 + 3 * step16, idesc, 1);
+            }
+            umma_commit(done_a + d * 8);
+          }
+          __syncwarp();
         }
       }
-      if (mine == 0) TR_OUT(2, 4);  // mma: waiting for [2] A, [3] B; [5] issuing
+      if (mine == 0 && lane == 0) TR_OUT(2, 4);  // mma: waiting for [2] A, [3] B; [5] issuing
     }
   } else if (warp == kWAct && !cache) {
     // ================================================================ activation warp (ring mode)
     // Waits for the previous kernel (it produced x), then per chunk bulk-copies the token rows and
-    // per unit turns each token's 128 values into three int8 digit rows of the B slot.
+    // per step turns each token's 128 values per group into three int8 digit rows of the B slot.
     pdl_wait();
     WorkIter it;
     it.init(u0, u1, G, p.chunk_groups);
@@ -572,7 +632,7 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
     };
     bool have = it.next(c);
     if (have) issue(c, 0);
-    int xb = 0, n = 0;
+    int xb = 0, n = 0, t = 0;
     uint32_t xph0 = 0, xph1 = 0;
     bool ok = true;
     while (ok && have) {
@@ -584,18 +644,22 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
         ok = false;
         break;
       }
-      for (int gl = 0; gl < c.n && ok; ++gl, ++n) {
-        const int a = n & (AD - 1);
-        if (n >= AD && !wait_h(done_a + ((n - AD) & (DD - 1)) * 8, static_cast<uint32_t>((n - AD) / DD) & 1u, p.hint, kSpinLimit)) {
+      for (int gl = 0; gl < c.n && ok; gl += kStepGroups, ++t) {
+        const int ng = (c.n - gl < kStepGroups) ? c.n - gl : kStepGroups;
+        const int a = t & (AD2 - 1);
+        if (t >= AD2 && !wait_h(done_a + ((t - AD2) & (DD2 - 1)) * 8, static_cast<uint32_t>((t - AD2) / DD2) & 1u, p.hint,
+                                kSpinLimit)) {
           atomicExch(p.status, W4A16_ETIMEOUT);
           ok = false;
           break;
         }
-        for (int m = 0; m < M; ++m) {
-          const uint2 rv = *reinterpret_cast<const uint2*>(xraw + xb * p.xbuf_bytes + m * rowb + gl * 256 + lane * 8);
-          convert_group(rv, bq + a * p.b_slot, p.b_lbo, m,
-                        reinterpret_cast<float2*>(xsinv) + (n & (kSide - 1)) * 16 + m, lane);
-        }
+        for (int j = 0; j < ng; ++j, ++n)
+          for (int m = 0; m < M; ++m) {
+            const uint2 rv =
+                *reinterpret_cast<const uint2*>(xraw + xb * p.xbuf_bytes + m * rowb + (gl + j) * 256 + lane * 8);
+            convert_group(rv, bq + (a * kStepGroups + j) * p.b_slot, p.b_lbo, m,
+                          reinterpret_cast<float2*>(xsinv) + (n & (kXsRing - 1)) * 16 + m, lane);
+          }
         fence_proxy_async();  // B was written through the generic proxy, the tensor core reads it through the async one
         __syncwarp();
         if (lane == 0) mbar_arrive(bfull_a + a * 8);
@@ -610,71 +674,88 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
     }
   } else if (warp >= kWUnpack0 && warp < kWUnpack0 + 8) {
     // ================================================================ unpack warps
-    // Thread = one row of the tile = one TMEM lane. Per unit: the row's 64 bytes (four 16-byte
-    // slots) -> 32 registers of int8 -> 32 TMEM columns of the A slot.
+    // Thread = one row of the tile = one TMEM lane. Per group: the row's 64 bytes (four 16-byte slots)
+    // -> 32 registers of int8 -> 32 TMEM columns of the A slot. Two warps per lane quarter, alternating steps.
     const int q = warp & 3, pair = (warp - kWUnpack0) >> 2, r = q * 32 + lane;
     const uint32_t lane_t = tmem + (static_cast<uint32_t>(q * 32) << 16);
     uint32_t woff[4];
 #pragma unroll
     for (int c4 = 0; c4 < 4; ++c4) woff[c4] = c4 * kChunkBytes + weight_slot(r, c4) * 16;
-    const int units = u1 - u0;
-    int st = 0;
+    WorkIter it;
+    it.init(u0, u1, G, p.chunk_groups);
+    Chunk c;
+    int st = 0, t = 0, n = 0;
     uint32_t wph = 0;
+    bool ok = team_ok;
     TR_DECL;
-    for (int n = 0; n < units; ++n) {
-      if ((n & 1) == pair) {
-        const int a = n & (AD - 1);
-        TR_LAP(3);
-        if (!wait_h(wfull_a + st * 8, wph, p.hint, kSpinLimit)) {
-          atomicExch(p.status, W4A16_ETIMEOUT);
-          break;
-        }
-        TR_LAP(0);
-        const uint32_t base = ring_a + st * kTileGroupBytes;
-        uint4 w[4];
+    while (ok && it.next(c)) {
+      for (int gl = 0; gl < c.n; gl += kStepGroups, ++t) {
+        const int ng = (c.n - gl < kStepGroups) ? c.n - gl : kStepGroups;
+        if ((t & 1) == pair) {
+          const int a = t & (AD2 - 1);
+          TR_LAP(3);
+          if (!wait_h(wfull_a + st * 8, wph, p.hint, kSpinLimit)) {
+            atomicExch(p.status, W4A16_ETIMEOUT);
+            ok = false;
+            break;
+          }
+          TR_LAP(0);
+          const uint32_t base = ring_a + st * kStageBytes;
+          uint4 w[4];
 #pragma unroll
-        for (int c4 = 0; c4 < 4; ++c4) w[c4] = lds128(base + woff[c4]);
-        uint32_t sz;
-        {
-          uint32_t sc, zp;
-          asm volatile("ld.shared.u16 %0, [%1];" : "=r"(sc) : "r"(base + kTgScaleOff + 2 * r));
-          asm volatile("ld.shared.u8 %0, [%1];" : "=r"(zp) : "r"(base + kTgZpOff + r));
-          sz = (sc << 16) | zp;
-        }
-        TR_LAP(2);
-        // the A slot's previous unit has been multiplied, and the D slot this unit will fill has been read out
-        if ((n >= AD && !wait_h(done_a + ((n - AD) & (DD - 1)) * 8, static_cast<uint32_t>((n - AD) / DD) & 1u, p.hint, kSpinLimit)) ||
-            (n >= DD && !wait_h(dempty_a + (n & (DD - 1)) * 8, static_cast<uint32_t>(n / DD - 1) & 1u, p.hint, kSpinLimit))) {
-          atomicExch(p.status, W4A16_ETIMEOUT);
-          break;
-        }
-        TR_LAP(1);
-        tc_fence_after();
-        uint32_t v[32];
+          for (int c4 = 0; c4 < 4; ++c4) w[c4] = lds128(base + woff[c4]);
+          TR_LAP(2);
+          // the A slot's previous step has been multiplied, and the D slot this step will fill has been read out
+          if ((t >= AD2 && !wait_h(done_a + ((t - AD2) & (DD2 - 1)) * 8, static_cast<uint32_t>((t - AD2) / DD2) & 1u,
+                                   p.hint, kSpinLimit)) ||
+              (t >= DD2 && !wait_h(dempty_a + (t & (DD2 - 1)) * 8, static_cast<uint32_t>(t / DD2 - 1) & 1u, p.hint,
+                                   kSpinLimit))) {
+            atomicExch(p.status, W4A16_ETIMEOUT);
+            ok = false;
+            break;
+          }
+          TR_LAP(1);
+          tc_fence_after();
 #pragma unroll
-        for (int c4 = 0; c4 < 4; ++c4) {
-          const uint32_t ww[4] = {w[c4].x, w[c4].y, w[c4].z, w[c4].w};
+          for (int j = 0; j < kStepGroups; ++j) {
+            if (j < ng) {
+              const uint32_t gb = base + j * kTileGroupBytes;
+              if (j > 0) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            v[c4 * 8 + 2 * i] = ww[i] & 0x0F0F0F0Fu;
-            v[c4 * 8 + 2 * i + 1] = (ww[i] >> 4) & 0x0F0F0F0Fu;
+                for (int c4 = 0; c4 < 4; ++c4) w[c4] = lds128(gb + woff[c4]);
+              }
+              uint32_t sc, zp;
+              asm volatile("ld.shared.u16 %0, [%1];" : "=r"(sc) : "r"(gb + kTgScaleOff + 2 * r));
+              asm volatile("ld.shared.u8 %0, [%1];" : "=r"(zp) : "r"(gb + kTgZpOff + r));
+              uint32_t v[32];
+#pragma unroll
+              for (int c4 = 0; c4 < 4; ++c4) {
+                const uint32_t ww[4] = {w[c4].x, w[c4].y, w[c4].z, w[c4].w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  v[c4 * 8 + 2 * i] = ww[i] & 0x0F0F0F0Fu;
+                  v[c4 * 8 + 2 * i + 1] = (ww[i] >> 4) & 0x0F0F0F0Fu;
+                }
+              }
+              const uint32_t a_t = lane_t + a * GE::kAColsS + j * kAColsG;
+              tmem_st16(a_t, reinterpret_cast<const uint32_t(&)[16]>(v[0]));
+              tmem_st16(a_t + 16, reinterpret_cast<const uint32_t(&)[16]>(v[16]));
+              sts32(side_a + (((n + j) & (kSide - 1)) * kTileRows + r) * 4, (sc << 16) | zp);
+            }
+          }
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(afull_a + a * 8);
+            mbar_arrive(wempty_a + st * 8);
           }
         }
-        const uint32_t a_t = lane_t + a * kACols;
-        tmem_st16(a_t, reinterpret_cast<const uint32_t(&)[16]>(v[0]));
-        tmem_st16(a_t + 16, reinterpret_cast<const uint32_t(&)[16]>(v[16]));
-        sts32(side_a + ((n & (kSide - 1)) * kTileRows + r) * 4, sz);
-        tmem_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(afull_a + a * 8);
-          mbar_arrive(wempty_a + st * 8);
+        n += ng;
+        if (++st == DS) {
+          st = 0;
+          wph ^= 1;
         }
-      }
-      if (++st == DS) {
-        st = 0;
-        wph ^= 1;
       }
     }
     TR_LAP(3);
@@ -732,22 +813,23 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
     WorkIter it;
     it.init(u0, u1, G, p.chunk_groups);
     Chunk c;
-    int n = 0;
+    int n = 0, t = 0;
     bool ok = team_ok;
-    constexpr int FB = GE::FB;
+    constexpr int RG = GE::RG, GB = GE::GB;
     constexpr int NLD = MT == 1 ? 4 : (MT == 2 ? 8 : N);
     TR_DECL;
     while (ok && it.next(c)) {
-      // FB units per round: one wait per issuer (a commit covers everything its thread issued before),
-      // the rounds' tensor-memory loads in flight together, one wait for all of them.
-      for (int gl = 0; gl < c.n; gl += FB) {
-        const int nb = (c.n - gl < FB) ? c.n - gl : FB;
+      // RG groups (RG/2 steps) per round: one wait per issuer (a commit covers everything its thread issued
+      // before), GB groups' tensor-memory loads in flight together.
+      for (int gl = 0; gl < c.n; gl += RG) {
+        const int rg = (c.n - gl < RG) ? c.n - gl : RG;
+        const int ns = (rg + kStepGroups - 1) / kStepGroups;
         TR_LAP(1);
         {
-          const int l1 = n + nb - 1, l2 = n + nb - 2;
-          bool w_ok = wait_h(done_a + (l1 & (DD - 1)) * 8, static_cast<uint32_t>(l1 / DD) & 1u, p.hint, kSpinLimit);
-          if (nb > 1)
-            w_ok = w_ok && wait_h(done_a + (l2 & (DD - 1)) * 8, static_cast<uint32_t>(l2 / DD) & 1u, p.hint, kSpinLimit);
+          const int l1 = t + ns - 1, l2 = t + ns - 2;
+          bool w_ok = wait_h(done_a + (l1 & (DD2 - 1)) * 8, static_cast<uint32_t>(l1 / DD2) & 1u, p.hint, kSpinLimit);
+          if (ns > 1)
+            w_ok = w_ok && wait_h(done_a + (l2 & (DD2 - 1)) * 8, static_cast<uint32_t>(l2 / DD2) & 1u, p.hint, kSpinLimit);
           if (!w_ok) {
             atomicExch(p.status, W4A16_ETIMEOUT);
             ok = false;
@@ -759,44 +841,57 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
         if (tid == 0 && n == 0) TL(4);
 #endif
         tc_fence_after();
-        uint32_t dv[FB][NLD];
 #pragma unroll
-        for (int j = 0; j < FB; ++j)
-          if (j < nb) {
-            const uint32_t d_t = lane_t + ((n + j) & (DD - 1)) * N;
-            if constexpr (MT == 1) tmem_ld4(d_t, dv[j]);
-            else if constexpr (MT == 2) tmem_ld8(d_t, dv[j]);
-            else {
+        for (int k0 = 0; k0 < RG; k0 += GB) {
+          if (k0 < rg) {
+            uint32_t dv[GB][NLD];
+            uint32_t sz[GB];
 #pragma unroll
-              for (int i = 0; i < N / 16; ++i) tmem_ld16(d_t + 16 * i, dv[j] + 16 * i);
+            for (int j = 0; j < GB; ++j) {
+              const int k = k0 + j;
+              if (k < rg) {
+                const uint32_t d_t = lane_t + ((t + (k >> 1)) & (DD2 - 1)) * GE::kDColsS + (k & 1) * N;
+                if constexpr (MT == 1) tmem_ld4(d_t, dv[j]);
+                else if constexpr (MT == 2) tmem_ld8(d_t, dv[j]);
+                else {
+#pragma unroll
+                  for (int i = 0; i < N / 16; ++i) tmem_ld16(d_t + 16 * i, dv[j] + 16 * i);
+                }
+                sz[j] = lds32(side_a + (((n + k) & (kSide - 1)) * kTileRows + r) * 4);
+              }
+            }
+            tmem_wait_ld();
+            if (k0 + GB >= rg) {  // the round's last loads are in registers: release its D slots
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) {
+#pragma unroll
+                for (int sidx = 0; sidx < RG / kStepGroups; ++sidx)
+                  if (sidx < ns) mbar_arrive(dempty_a + ((t + sidx) & (DD2 - 1)) * 8);
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < GB; ++j) {
+              const int k = k0 + j;
+              if (k < rg) {
+                const uint32_t xs_a = xsinv_a + (cache ? cache_slot(c.g + gl + k) * MT : ((n + k) & (kXsRing - 1)) * 16) * 8;
+                const float s = __uint_as_float(sz[j] & 0xFFFF0000u);
+                const float z = static_cast<float>(sz[j] & 0xFFu);
+#pragma unroll
+                for (int m = 0; m < MT; ++m)
+                  if (m < M) {
+                    const uint2 tt = lds64(xs_a + m * 8);  // (sum of X, 2^-p)
+                    const float d0 = small_int_to_float(dv[j][3 * m]), d1 = small_int_to_float(dv[j][3 * m + 1]);
+                    const float d2 = small_int_to_float(dv[j][3 * m + 2]);
+                    const float dot = fmaf(d2, 65536.f, fmaf(d1, 256.f, d0));
+                    fin[m] = fmaf(s * __uint_as_float(tt.y), fmaf(-z, __uint_as_float(tt.x), dot), fin[m]);
+                  }
+              }
             }
           }
-        tmem_wait_ld();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-#pragma unroll
-          for (int j = 0; j < FB; ++j)
-            if (j < nb) mbar_arrive(dempty_a + ((n + j) & (DD - 1)) * 8);
         }
-#pragma unroll
-        for (int j = 0; j < FB; ++j)
-          if (j < nb) {
-            const uint32_t xs_a = xsinv_a + (cache ? (c.g + gl + j) * MT : ((n + j) & (kSide - 1)) * 16) * 8;
-            const uint32_t sz = lds32(side_a + (((n + j) & (kSide - 1)) * kTileRows + r) * 4);
-            const float s = __uint_as_float(sz & 0xFFFF0000u);
-            const float z = static_cast<float>(sz & 0xFFu);
-#pragma unroll
-            for (int m = 0; m < MT; ++m)
-              if (m < M) {
-                const uint2 t = lds64(xs_a + m * 8);  // (sum of X, 2^-p)
-                const float d0 = small_int_to_float(dv[j][3 * m]), d1 = small_int_to_float(dv[j][3 * m + 1]);
-                const float d2 = small_int_to_float(dv[j][3 * m + 2]);
-                const float dot = fmaf(d2, 65536.f, fmaf(d1, 256.f, d0));
-                fin[m] = fmaf(s * __uint_as_float(t.y), fmaf(-z, __uint_as_float(t.x), dot), fin[m]);
-              }
-          }
-        n += nb;
+        n += rg;
+        t += ns;
       }
       if (!ok) break;
       if (c.seg_last) {
@@ -935,7 +1030,7 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
 #endif
   if (warp == kWMma) {
     tc_fence_after();
-    tmem_dealloc(tmem, kTmemCols);
+    tmem_dealloc(*reinterpret_cast<volatile uint32_t*>(tmem_slot), kTmemCols);
   }
 }
 
@@ -952,7 +1047,7 @@ __global__ void k_pairs_reduce(int32_t* ids, const Pair* pairs, int nranks, int 
 
 // ------------------------------------------------------------------ host side
 struct Config {
-  int depth;     // weight ring stages (8576 B each)
+  int depth;     // weight ring stages (two blocks, 17152 B, each)
   int l2ahead;   // blocks of L2 prefetch ahead of the ring
   int pdl;
   int cache_kb;  // largest B region (KB) for which all k groups are kept converted in shared memory
@@ -962,7 +1057,7 @@ struct Config {
 
 const Config& config() {
   static Config c = [] {
-    Config k{9, 16, 1, 56, 112, 2000};
+    Config k{5, 0, 1, 56, 112, 2000};
     if (const char* e = getenv("W4A16_DEPTH")) k.depth = atoi(e);
     if (const char* e = getenv("W4A16_L2AHEAD")) k.l2ahead = atoi(e);
     if (const char* e = getenv("W4A16_PDL")) k.pdl = atoi(e) != 0;
@@ -970,7 +1065,7 @@ const Config& config() {
     if (const char* e = getenv("W4A16_SMEM_KB")) k.smem_kb = atoi(e);
     if (const char* e = getenv("W4A16_HINT")) k.hint = atoi(e);
     if (k.hint < 0) k.hint = 0;
-    if (k.depth < 3) k.depth = 3;
+    if (k.depth < 2) k.depth = 2;
     if (k.depth > 20) k.depth = 20;
     if (k.l2ahead < 0) k.l2ahead = 0;
     if (k.l2ahead > 256) k.l2ahead = 256;
@@ -986,25 +1081,28 @@ template <int MT>
 int launch_cfg(SkinnyParams& p, int grid, cudaStream_t st, int smem_optin) {
   using GE = Geo<MT>;
   const int M = p.M, G = p.G;
-  const int cache_bytes = G * 384 * M + 256;
+  const long long U = static_cast<long long>(p.tiles) * G;
+  const int per_cta = static_cast<int>((U + grid - 1) / grid);  // most (tile, group) units any CTA gets
+  const int cache_groups = per_cta < G ? per_cta : G;
+  const int cache_bytes = cache_groups * 384 * M + 256;
   p.cache = cache_bytes <= config().cache_kb * 1024;
   if (p.cache) {
     p.b_slot = 384 * M;
     p.b_lbo = 48 * M;
     p.b_bytes = cache_bytes;
-    p.xs_bytes = G * MT * 8;
+    p.xs_bytes = cache_groups * MT * 8;
     p.xbuf_bytes = 0;
   } else {
-    p.b_slot = GE::kBBytes;
+    p.b_slot = GE::kBGroup;
     p.b_lbo = GE::kLbo;
-    p.b_bytes = GE::AD * GE::kBBytes;
-    p.xs_bytes = kSide * 16 * 8;
+    p.b_bytes = GE::AD2 * kStepGroups * GE::kBGroup;
+    p.xs_bytes = kXsRing * 16 * 8;
   }
   // ring depth: as configured, but inside the per-CTA target (two launches side by side) when possible
   int limit = config().smem_kb * 1024;
   if (limit > smem_optin) limit = smem_optin;
   int smem = total_smem<MT>(p.depth, p.b_bytes, p.xbuf_bytes, p.xs_bytes);
-  while (smem > limit && p.depth > 4) {
+  while (smem > limit && p.depth > 2) {
     --p.depth;
     smem = total_smem<MT>(p.depth, p.b_bytes, p.xbuf_bytes, p.xs_bytes);
   }
@@ -1062,7 +1160,7 @@ int launch_skinny(SkinnyParams& p, const w4a16_weights_t* w, const uint16_t* x, 
   p.hint = static_cast<uint32_t>(config().hint);
   p.l2ahead = config().l2ahead;
   // groups per raw activation chunk: about 2 KB per buffer (256 B per token per group)
-  int cg = 2048 / (256 * M);
+  int cg = (2048 / (256 * M)) & ~1;
   if (cg > kMaxChunkGroups) cg = kMaxChunkGroups;
   if (cg < 2) cg = 2;
   p.chunk_groups = cg;
