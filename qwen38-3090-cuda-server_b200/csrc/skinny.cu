@@ -72,13 +72,13 @@ constexpr int kAColsG = 32;                // 128 int8 along k = 32 columns of 3
 
 #ifdef W4A16_TRACE
 // Development aid (compiled only with -DW4A16_TRACE): per-CTA cycle counts of what each role waits for.
-__device__ long long g_trace[256 * 16];
-#define TR_DECL long long tr_t0 = clock64(), tr_acc[4] = {0, 0, 0, 0}
+__device__ long long g_trace[256 * 24];
+#define TR_DECL long long tr_t0 = clock64(), tr_acc[6] = {0, 0, 0, 0, 0, 0}
 #define TR_LAP(i) do { const long long t_ = clock64(); tr_acc[i] += t_ - tr_t0; tr_t0 = t_; } while (0)
-#define TR_OUT(base, n) do { for (int i_ = 0; i_ < (n); ++i_) g_trace[blockIdx.x * 16 + (base) + i_] = tr_acc[i_]; } while (0)
-__device__ long long g_tline[256 * 8];
+#define TR_OUT(base, n) do { for (int i_ = 0; i_ < (n); ++i_) g_trace[blockIdx.x * 24 + (base) + i_] = tr_acc[i_]; } while (0)
+__device__ long long g_tline[8 * 256 * 8];  // [launch % 8][CTA][event]
 __device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define TL(i) do { g_tline[blockIdx.x * 8 + (i)] = gtime(); } while (0)
+#define TL(i) do { g_tline[((p.trace_id & 7) * 256 + blockIdx.x) * 8 + (i)] = gtime(); } while (0)
 #else
 #define TL(i)
 #define TR_DECL
@@ -123,6 +123,7 @@ struct SkinnyParams {
   int b_lbo;         // bytes between the 16-k chunks of a B slot
   int b_bytes;       // bytes of the whole B region
   int xs_bytes;      // bytes of the (sum, 2^-p) region
+  int trace_id;      // launch counter (development trace only)
   uint32_t hint;     // suspend-time hint of the mbarrier waits, ns
   int depth;         // weight ring stages
   int l2ahead;       // units of L2 prefetch ahead of the ring
@@ -473,7 +474,7 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
     if (lane == 0) mbar_arrive(bready_a);
     if (tid == 0) TL(3);
 #ifdef W4A16_TRACE
-    if (tid == 0) g_trace[blockIdx.x * 16 + 12] = clock64() - tr_kernel0;  // conversion done
+    if (tid == 0) g_trace[blockIdx.x * 24 + 20] = clock64() - tr_kernel0;  // conversion done
 #endif
     // the fix-up warps read the (sum, 2^-p) entries other warps wrote
     if (warp < CW && !wait_h(bready_a, 0, p.hint, kSpinLimit)) {
@@ -693,7 +694,7 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
         const int ng = (c.n - gl < kStepGroups) ? c.n - gl : kStepGroups;
         if ((t & 1) == pair) {
           const int a = t & (AD2 - 1);
-          TR_LAP(3);
+          TR_LAP(5);
           if (!wait_h(wfull_a + st * 8, wph, p.hint, kSpinLimit)) {
             atomicExch(p.status, W4A16_ETIMEOUT);
             ok = false;
@@ -743,13 +744,16 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
               sts32(side_a + (((n + j) & (kSide - 1)) * kTileRows + r) * 4, (sc << 16) | zp);
             }
           }
+          TR_LAP(3);
           tmem_wait_st();
+          TR_LAP(4);
           tc_fence_before();
           __syncwarp();
           if (lane == 0) {
             mbar_arrive(afull_a + a * 8);
             mbar_arrive(wempty_a + st * 8);
           }
+          TR_LAP(5);
         }
         n += ng;
         if (++st == DS) {
@@ -758,8 +762,7 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
         }
       }
     }
-    TR_LAP(3);
-    if (warp == kWUnpack0 && lane == 0) TR_OUT(6, 4);  // unpack: waiting for [6] weights, [7] a free A slot; [8] loads, [9] unpack + store
+    if (warp == kWUnpack0 && lane == 0) TR_OUT(14, 6);  // unpack: waiting for [6] weights, [7] a free A slot; [8] loads, [9] unpack + store
   } else if (warp < CW) {
     // ================================================================ fix-up warps
     const int q = warp, r = q * 32 + lane;
@@ -860,7 +863,9 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
                 sz[j] = lds32(side_a + (((n + k) & (kSide - 1)) * kTileRows + r) * 4);
               }
             }
+            TR_LAP(2);
             tmem_wait_ld();
+            TR_LAP(3);
             if (k0 + GB >= rg) {  // the round's last loads are in registers: release its D slots
               tc_fence_before();
               __syncwarp();
@@ -890,6 +895,7 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
             }
           }
         }
+        TR_LAP(4);
         n += rg;
         t += ns;
       }
@@ -929,7 +935,7 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
 
     TR_LAP(1);
     if (tid == 0) TL(5);
-    if (warp == 0 && lane == 0) TR_OUT(10, 2);  // fix-up: [10] waiting for D, [11] everything else in the main loop
+    if (warp == 0 && lane == 0) TR_OUT(8, 5);  // fix-up: [10] waiting for D, [11] everything else in the main loop
     // ---- split tiles: the warp that drew the last ticket for its rows adds the pieces up ----
     if (ok) {
       const int ns = __shfl_sync(0xffffffffu, sp_n, 0);
@@ -1024,8 +1030,8 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
 #ifdef W4A16_TRACE
   if (tid == 0) {
     TL(6);
-    g_trace[blockIdx.x * 16 + 13] = clock64() - tr_kernel0;  // whole CTA
-    g_trace[blockIdx.x * 16 + 14] = u1 - u0;
+    g_trace[blockIdx.x * 24 + 21] = clock64() - tr_kernel0;  // whole CTA
+    g_trace[blockIdx.x * 24 + 22] = u1 - u0;
   }
 #endif
   if (warp == kWMma) {
@@ -1156,6 +1162,8 @@ int launch_skinny(SkinnyParams& p, const w4a16_weights_t* w, const uint16_t* x, 
   p.counters = reinterpret_cast<unsigned*>(s->xgsum);
   p.cta_pairs = s->xf;
   p.status = di->status;
+  static int launch_counter = 0;
+  p.trace_id = launch_counter++;
   p.depth = config().depth;
   p.hint = static_cast<uint32_t>(config().hint);
   p.l2ahead = config().l2ahead;
