@@ -54,58 +54,46 @@ constexpr int kThreads = kWarps * 32;
 constexpr int kWUnpack0 = 4;               // warps 4..11 unpack
 constexpr int kWProducer = 12;
 constexpr int kWMma = 13;                  // MMA issuer of the even steps; owns the tensor-memory allocation
-constexpr int kWAct = 14;                  // activation warp of ring mode
 constexpr int kWMma2 = 15;                 // MMA issuer of the odd steps
-constexpr int kTeam = kWarps - 2;          // warps that convert activations in cache mode (all but producer, kWMma)
+constexpr int kTeam = kWarps - 2;          // warps that convert activations (all but producer, kWMma)
 constexpr int kStepGroups = 2;             // k groups per step: every hand-off between roles moves two groups
 constexpr int kStageBytes = kStepGroups * kTileGroupBytes;  // 17152
-constexpr int kSide = 16;                  // groups in the (scale, zp) side ring
-constexpr int kXsRing = 32;                // groups in the (sum, 2^-p) ring of ring mode
-constexpr int kXBufs = 2;                  // raw activation chunk buffers (ring mode)
-constexpr int kFirstChunk = 2;             // groups in a CTA's first chunk (short start-up)
-constexpr int kMaxChunkGroups = 16;        // bound on groups per chunk
+constexpr int kSide = 16;                  // (scale, zp) side ring: 8 steps x 2 groups
+constexpr int kTable = 64;                 // step table entries (ring)
 constexpr uint32_t kSpinLimit = 1u << 20;  // polls before a wait gives up
 constexpr int kFixBar = 1;                 // named barrier of the fix-up warps
 constexpr int kTmemCols = 512;             // all of tensor memory; the next launch's CTA, resident beside this one,
                                            // gets it when this CTA exits (it cannot multiply before that anyway)
 constexpr int kAColsG = 32;                // 128 int8 along k = 32 columns of 32 bits per group
+constexpr int kMaxBatch = 10;              // tokens per launch; larger M runs as two launches
 
 #ifdef W4A16_TRACE
-// Development aid (compiled only with -DW4A16_TRACE): per-CTA cycle counts of what each role waits for.
-__device__ long long g_trace[256 * 24];
-#define TR_DECL long long tr_t0 = clock64(), tr_acc[6] = {0, 0, 0, 0, 0, 0}
-#define TR_LAP(i) do { const long long t_ = clock64(); tr_acc[i] += t_ - tr_t0; tr_t0 = t_; } while (0)
-#define TR_OUT(base, n) do { for (int i_ = 0; i_ < (n); ++i_) g_trace[blockIdx.x * 24 + (base) + i_] = tr_acc[i_]; } while (0)
+// Development aid (compiled only with -DW4A16_TRACE): per-CTA timestamps of a launch's phases.
 __device__ long long g_tline[8 * 256 * 8];  // [launch % 8][CTA][event]
 __device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
 #define TL(i) do { g_tline[((p.trace_id & 7) * 256 + blockIdx.x) * 8 + (i)] = gtime(); } while (0)
+__device__ int g_where[8];  // first bounded wait that gave up: site, step, CTA, warp
+#define GAVE_UP(site, step) do { if (atomicCAS(&g_where[0], 0, (site)) == 0) { g_where[1] = (step); g_where[2] = blockIdx.x; g_where[3] = threadIdx.x >> 5; g_where[4] = p.trace_id; } } while (0)
 #else
 #define TL(i)
-#define TR_DECL
-#define TR_LAP(i)
-#define TR_OUT(base, n)
+#define GAVE_UP(site, step)
 #endif
 
-// Per token-count geometry. N = rows of the B operand (3 digit rows per token, padded to 16).
-// Ring depths are in steps: AD2 for A (tensor memory) and, in ring mode, B (shared memory);
-// DD2 for D (tensor memory) and for the ring of "step done" barriers.
+// Per token-count geometry. N = rows of the B operand the tensor core reads (3 digit rows per token are
+// real). Ring depths are in steps: AD2 for A, DD2 for D and for the ring of "step done" barriers.
 template <int MT>
 struct Geo {
-  static constexpr int N = MT <= 5 ? 16 : (MT <= 10 ? 32 : 48);
-  static constexpr int AD2 = N == 48 ? 2 : 4;
+  static constexpr int N = MT <= 5 ? 16 : 32;
+  static constexpr int AD2 = 4;
   static constexpr int DD2 = N == 16 ? 8 : 4;
   static constexpr int kAColsS = kStepGroups * kAColsG;  // A columns per step
   static constexpr int kDColsS = kStepGroups * N;        // D columns per step
   static constexpr int kDCol0 = AD2 * kAColsS;           // first D column
-  static constexpr int RG = MT == 1 ? 4 : 2;             // groups the fix-up warps take per round
   static constexpr int GB = MT == 1 ? 4 : (MT == 2 ? 2 : 1);  // groups whose tensor-memory loads are in flight together
-  static constexpr int kBGroup = N * 128;                // ring mode: bytes of one group's B block
-  static constexpr int kLbo = (N / 8) * 128;             // ring mode: between core matrices along k
-  static constexpr int kMinCtas = MT <= 5 ? 2 : 1;
+  static constexpr int kMinCtas = MT <= 2 ? 2 : 1;       // M <= 2 leaves room for the next launch's CTA
   static_assert(kDCol0 + DD2 * kDColsS <= kTmemCols, "tensor memory budget");
-  static_assert(AD2 <= DD2 && RG / kStepGroups <= DD2 / 2, "ring depths");
+  static_assert(AD2 <= DD2 && 2 <= DD2 / 2, "ring depths");
   static_assert(kStepGroups * DD2 <= kSide, "a (scale, zp) slot is read before the D slot of its step is released");
-  static_assert(kStepGroups * (AD2 + DD2 + RG / kStepGroups) <= kXsRing, "(sum, 2^-p) ring depth");
 };
 
 struct SkinnyParams {
@@ -116,17 +104,11 @@ struct SkinnyParams {
   long long ldy;  // elements between rows of y
   int y_col0;     // first column of this launch's rows inside y
   int M, N, K, G, tiles;
-  int chunk_groups;  // k groups per activation chunk
-  int xbuf_bytes;    // bytes of one raw activation buffer (M rows of chunk_groups * 256); 0 in cache mode
-  int cache;         // 1: the digit rows of ALL k groups stay in shared memory, converted once per CTA
-  int b_slot;        // bytes between B slots (per group in cache mode, per ring slot otherwise)
-  int b_lbo;         // bytes between the 16-k chunks of a B slot
-  int b_bytes;       // bytes of the whole B region
+  int b_bytes;       // bytes of the B region (digit rows of the groups this CTA multiplies)
   int xs_bytes;      // bytes of the (sum, 2^-p) region
   int trace_id;      // launch counter (development trace only)
   uint32_t hint;     // suspend-time hint of the mbarrier waits, ns
   int depth;         // weight ring stages
-  int l2ahead;       // units of L2 prefetch ahead of the ring
   float* partial;
   unsigned* counters;  // [tiles * CW + 1], zero between launches
   int argmax;
@@ -149,26 +131,22 @@ __device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
 }
 
 // ---- the order in which a CTA walks its unit range [u0,u1) -------------------------------
-// Row tiles that this CTA shares with a neighbour come first (the piece at the end of the
-// range, then the piece at its start), whole tiles after, so the cross-CTA reduction of the
-// shared tiles overlaps everybody's main loop instead of sitting at the end of the kernel.
-// Every role (weight producer, activation warp, consumers) runs the same iterator.
-struct Chunk {
-  int tile, g, n;      // row tile, first group, number of groups (<= chunk_groups)
-  int seg_g0, seg_g1;  // the segment this chunk belongs to: groups [seg_g0, seg_g1) of `tile`
-  bool seg_last;       // last chunk of its segment
+// A segment is a run of consecutive k groups of one row tile. Row tiles that this CTA shares with a
+// neighbour come first (the piece at the end of the range, then the piece at its start), whole tiles
+// after, so the cross-CTA reduction of the shared tiles overlaps everybody's main loop instead of
+// sitting at the end of the kernel. A segment of L groups is ceil(L/2) steps.
+struct Seg {
+  int tile, g0, L;
+  bool whole;  // the segment is the tile's full K range
 };
 
-struct WorkIter {
-  int G, CG, t_first, t_last, head_g0, tail_g1;
-  bool single, head_partial, tail_partial, first;
+struct SegIter {
+  int G, t_first, t_last, head_g0, tail_g1;
+  bool single, head_partial, tail_partial;
   int phase, t;
-  int s_tile, s_g0, s_g1, g;  // current segment and cursor
-  bool have;
 
-  __device__ void init(int u0, int u1, int G_, int CG_) {
+  __device__ void init(int u0, int u1, int G_) {
     G = G_;
-    CG = CG_;
     t_first = u0 / G;
     t_last = (u1 - 1) / G;
     head_g0 = u0 - t_first * G;
@@ -178,22 +156,19 @@ struct WorkIter {
     tail_partial = single ? false : (tail_g1 != G);
     phase = 0;
     t = t_first;
-    have = false;
-    first = true;
-    s_tile = s_g0 = s_g1 = g = 0;
   }
-  __device__ bool next_segment() {
+  __device__ bool next(Seg& s) {
     if (phase == 0) {
       phase = 1;
       if (tail_partial) {
-        s_tile = t_last; s_g0 = 0; s_g1 = tail_g1;
+        s.tile = t_last; s.g0 = 0; s.L = tail_g1; s.whole = false;
         return true;
       }
     }
     if (phase == 1) {
       phase = 2;
       if (head_partial) {
-        s_tile = t_first; s_g0 = head_g0; s_g1 = single ? tail_g1 : G;
+        s.tile = t_first; s.g0 = head_g0; s.L = (single ? tail_g1 : G) - head_g0; s.whole = false;
         return true;
       }
     }
@@ -201,26 +176,29 @@ struct WorkIter {
       const int tt = t++;
       if (tt == t_first && head_partial) continue;
       if (tt == t_last && tail_partial) continue;
-      s_tile = tt; s_g0 = 0; s_g1 = G;
+      s.tile = tt; s.g0 = 0; s.L = G; s.whole = true;
       return true;
     }
     return false;
   }
-  __device__ bool next(Chunk& c) {
-    if (!have || g >= s_g1) {
-      if (!next_segment()) return false;
-      have = true;
-      g = s_g0;
-    }
-    int n = first ? kFirstChunk : CG;
-    first = false;
-    if (s_g1 - g < n) n = s_g1 - g;
-    c.tile = s_tile; c.g = g; c.n = n; c.seg_g0 = s_g0; c.seg_g1 = s_g1;
-    g += n;
-    c.seg_last = (g == s_g1);
-    return true;
+  // number of steps of the whole walk
+  __device__ int steps() const {
+    int n = 0;
+    if (tail_partial) n += (tail_g1 + 1) >> 1;
+    if (head_partial) n += ((single ? tail_g1 : G) - head_g0 + 1) >> 1;
+    int whole = t_last - t_first + 1 - (head_partial ? 1 : 0) - (tail_partial ? 1 : 0);
+    n += whole * ((G + 1) >> 1);
+    return n;
   }
 };
+
+// Step table entry, written by the producer, read by the MMA issuers and the fix-up warps:
+//   x = slot0 | slot1 << 8 | (groups - 1) << 16 | last step of its segment << 17 | whole tile << 18
+//   y = row tile
+__device__ __forceinline__ uint32_t step_word(int slot0, int slot1, int ng, bool seg_last, bool whole) {
+  return static_cast<uint32_t>(slot0) | (static_cast<uint32_t>(slot1) << 8) | (static_cast<uint32_t>(ng - 1) << 16) |
+         (seg_last ? 1u << 17 : 0u) | (whole ? 1u << 18 : 0u);
+}
 
 // ---- PTX used only here ------------------------------------------------------------------
 // One lane of the (converged) warp; unlike a test of the lane index this keeps the code around it
@@ -235,9 +213,6 @@ __device__ __forceinline__ bool wait_h(uint32_t bar, uint32_t parity, uint32_t h
   for (uint32_t i = 0; i < limit; ++i)
     if (mbar_try_wait(bar, parity, hint_ns)) return true;
   return false;
-}
-__device__ __forceinline__ void l2_prefetch(const void* src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
 // Instruction descriptor for kind::i8: signed 8-bit A and B (both K-major), int32 accumulate.
 __host__ __device__ constexpr uint32_t umma_idesc_s8(int M, int N) {
@@ -273,41 +248,25 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* d) {
       : "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ uint2 lds64(uint32_t addr) {
-  uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-  uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
-  asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
-}
 // exact int -> float for |v| < 2^22 without the conversion pipe
 __device__ __forceinline__ float small_int_to_float(uint32_t v) {
   return __uint_as_float(0x4B400000u + v) - 12582912.0f;
 }
 
 // dynamic shared memory:
-//   [weight ring: depth x 17152][B region: b_bytes][raw x: kXBufs x xbuf_bytes][(scale,zp) ring: kSide x 128 x 4]
-//   [(sum, 2^-p) region: xs_bytes][mbarriers][tmem base, flag]
-// The B operand of one k group is eight 16-k chunks, `b_lbo` bytes apart, each holding the token digit
-// rows as consecutive 16-byte rows (row n at 16 n; an 8-row core matrix every 128 bytes).
-//   ring mode : a chunk holds all N rows (b_lbo = 16 N); rows without a token stay zero.
-//   cache mode: a chunk holds only the 3 M rows in use (b_lbo = 48 M), so the rows the tensor core reads
-//               beyond them are the next chunk's bytes. They only produce accumulator columns nobody
-//               reads, and the whole K range of a token fits: 384 bytes per group for M = 1.
+//   [weight ring: depth x 17152][B region: b_bytes][(scale,zp) ring: kSide x 128 x 4][(sum, 2^-p): xs_bytes]
+//   [step table: kTable x 8][mbarriers][tmem base, flag]
+// The B operand of one k group is eight 16-k chunks, 48 M bytes apart, each holding the 3 M digit rows in
+// use as consecutive 16-byte rows (an 8-row core matrix every 128 bytes). The rows the tensor core reads
+// beyond them are the next chunk's bytes: they only produce accumulator columns nobody reads, and the
+// whole K range of a token fits: 384 bytes per group for M = 1.
 template <int MT>
 __host__ __device__ constexpr int bar_count(int depth) {
-  return 2 * depth + 2 * Geo<MT>::AD2 + 2 * Geo<MT>::DD2 + kXBufs + 2;
+  return 2 * depth + Geo<MT>::AD2 + 2 * Geo<MT>::DD2 + 2;
 }
 template <int MT>
-__host__ __device__ inline int total_smem(int depth, int b_bytes, int xbuf_bytes, int xs_bytes) {
-  return depth * kStageBytes + b_bytes + kXBufs * xbuf_bytes + kSide * kTileRows * 4 + xs_bytes +
-         bar_count<MT>(depth) * 8 + 16;
+__host__ __device__ inline int total_smem(int depth, int b_bytes, int xs_bytes) {
+  return depth * kStageBytes + b_bytes + kSide * kTileRows * 4 + xs_bytes + kTable * 8 + bar_count<MT>(depth) * 8 + 16;
 }
 
 // One token's 128 values of one k group (this lane: k = 4 lane .. 4 lane + 3, `rv`) -> three int8 digit
@@ -361,13 +320,12 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
   const int DS = p.depth;
   uint8_t* ring = smem;
   uint8_t* bq = ring + DS * kStageBytes;
-  uint8_t* xraw = bq + p.b_bytes;
-  uint8_t* side = xraw + kXBufs * p.xbuf_bytes;
+  uint8_t* side = bq + p.b_bytes;
   uint8_t* xsinv = side + kSide * kTileRows * 4;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(xsinv + p.xs_bytes);
+  uint2* table = reinterpret_cast<uint2*>(xsinv + p.xs_bytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(table + kTable);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + bar_count<MT>(DS));
   int* sflag = reinterpret_cast<int*>(tmem_slot + 1);
-  const bool cache = p.cache != 0;
 
   const int tid = threadIdx.x, lane = tid & 31;
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // the same value, but provably warp-uniform
@@ -376,55 +334,47 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
   if (tid == 0) TL(0);
   const int u0 = static_cast<int>(static_cast<long long>(U) * blockIdx.x / gridDim.x);
   const int u1 = static_cast<int>(static_cast<long long>(U) * (blockIdx.x + 1) / gridDim.x);
-
-  // cache mode keeps the digit rows of the groups this CTA multiplies, (g_first + j) % G for j < min(G, u1 - u0),
-  // in slot j
+  // the digit rows of the groups this CTA multiplies, (g_first + j) % G for j < min(G, u1 - u0), live in slot j
   const int g_first = u0 % G;
   auto cache_slot = [&](int g) { return g - g_first + (g < g_first ? G : 0); };
+  const int b_slot = 384 * M, b_lbo = 48 * M;
+  int T;  // steps of this CTA
+  {
+    SegIter si;
+    si.init(u0, u1, G);
+    T = si.steps();
+  }
 
   const uint32_t ring_a = smem_u32(ring);
   const uint32_t bq_a = smem_u32(bq);
-  const uint32_t xraw_a = smem_u32(xraw);
   const uint32_t side_a = smem_u32(side);
   const uint32_t xsinv_a = smem_u32(xsinv);
   const uint32_t wfull_a = smem_u32(bars);          // [DS]  weights of a step landed (tx bytes)
   const uint32_t wempty_a = wfull_a + DS * 8;       // [DS]  stage free again (4 unpack warps)
   const uint32_t afull_a = wempty_a + DS * 8;       // [AD2] A slot written (4 unpack warps)
-  const uint32_t bfull_a = afull_a + AD2 * 8;       // [AD2] ring mode: B slot written (activation warp)
-  const uint32_t done_a = bfull_a + AD2 * 8;        // [DD2] step t's MMAs have completed (tcgen05.commit): its sums are
-                                                    //       in D slot t % DD2, its A and B slots t % AD2 are free again
+  const uint32_t done_a = afull_a + AD2 * 8;        // [DD2] step t's MMAs have completed (tcgen05.commit): its sums are
+                                                    //       in D slot t % DD2, its A slot t % AD2 is free again
   const uint32_t dempty_a = done_a + DD2 * 8;       // [DD2] D slot read out (4 fix-up warps)
-  const uint32_t xfull_a = dempty_a + DD2 * 8;      // [kXBufs] ring mode: raw activation chunk landed
-  const uint32_t bready_a = xfull_a + kXBufs * 8;   // cache mode: every needed group's digit rows are written
+  const uint32_t bready_a = dempty_a + DD2 * 8;     // every needed group's digit rows are written
   const uint32_t tmemrdy_a = bready_a + 8;          // tensor memory allocated, base address published
 
-  // rows of B that carry no token stay zero for the whole kernel
-  for (int i = tid; i < p.b_bytes / 16; i += kThreads) reinterpret_cast<uint4*>(bq)[i] = make_uint4(0, 0, 0, 0);
   if (tid == 0) {
     for (int i = 0; i < DS; ++i) {
       mbar_init(wfull_a + i * 8, 1);
       mbar_init(wempty_a + i * 8, 4);
     }
-    for (int i = 0; i < AD2; ++i) {
-      mbar_init(afull_a + i * 8, 4);
-      mbar_init(bfull_a + i * 8, 1);
-    }
+    for (int i = 0; i < AD2; ++i) mbar_init(afull_a + i * 8, 4);
     for (int i = 0; i < DD2; ++i) {
       mbar_init(done_a + i * 8, 1);
       mbar_init(dempty_a + i * 8, CW);
     }
-    for (int i = 0; i < kXBufs; ++i) mbar_init(xfull_a + i * 8, 1);
     mbar_init(bready_a, kTeam);
     mbar_init(tmemrdy_a, 1);
     fence_mbar_init();
   }
-  fence_proxy_async();  // the zeroed B region is read by the tensor core (async proxy)
   __syncthreads();
   pdl_launch_dependents();
   if (tid == 0) TL(1);
-#ifdef W4A16_TRACE
-  const long long tr_kernel0 = clock64();
-#endif
 
   // The previous launch's CTA on this SM may still hold tensor memory: only this warp waits for it.
   if (warp == kWMma) {
@@ -435,8 +385,8 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
   }
 
   bool team_ok = true;
-  if (cache && warp != kWProducer && warp != kWMma) {
-    // ================================================================ cache mode: convert the k groups this CTA needs
+  if (warp != kWProducer && warp != kWMma) {
+    // ================================================================ activations -> digit rows, once per CTA
     // All warps but the producer and the allocating warp take part (their own work cannot start before
     // the activations exist anyway). x comes straight from global memory (L2); a round's loads are all in
     // flight before its first conversion.
@@ -463,9 +413,7 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
         const int i = i0 + j * kTeam;
         if (i < total) {
           const int gj = i / M, m = i - gj * M;
-          int g = g_first + gj;
-          if (g >= G) g -= G;
-          convert_group(rv[j], bq + gj * p.b_slot, p.b_lbo, m, reinterpret_cast<float2*>(xsinv) + gj * MT + m, lane);
+          convert_group(rv[j], bq + gj * b_slot, b_lbo, m, reinterpret_cast<float2*>(xsinv) + gj * MT + m, lane);
         }
       }
     }
@@ -473,11 +421,9 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
     __syncwarp();
     if (lane == 0) mbar_arrive(bready_a);
     if (tid == 0) TL(3);
-#ifdef W4A16_TRACE
-    if (tid == 0) g_trace[blockIdx.x * 24 + 20] = clock64() - tr_kernel0;  // conversion done
-#endif
     // the fix-up warps read the (sum, 2^-p) entries other warps wrote
     if (warp < CW && !wait_h(bready_a, 0, p.hint, kSpinLimit)) {
+      GAVE_UP(1, -1);
       atomicExch(p.status, W4A16_ETIMEOUT);
       team_ok = false;
     }
@@ -489,6 +435,7 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
   const bool uses_tmem = warp < kWProducer || warp == kWMma || warp == kWMma2;
   if (uses_tmem) {
     if (!wait_h(tmemrdy_a, 0, p.hint, kSpinLimit) || *reinterpret_cast<volatile uint32_t*>(tmem_slot) != 0u) {
+      GAVE_UP(2, -1);
       atomicExch(p.status, W4A16_ETIMEOUT);
       team_ok = false;
     }
@@ -498,271 +445,163 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
   if (warp == kWProducer) {
     // ================================================================ weight producer
     // One thread streams this CTA's share of the weight stream, one step (two consecutive (tile, group)
-    // blocks, 17 KB) per bulk copy. It does not wait for the previous kernel: weights never depend on it.
-    // A second cursor runs `l2ahead` blocks further and only pulls them into L2, so HBM stays busy while
-    // this kernel waits for its activations, and the ring refills at L2 speed afterwards.
+    // blocks, 17 KB) per bulk copy, and writes the step's table entry. It does not wait for the previous
+    // kernel: weights never depend on it.
     if (lane == 0) {
-      WorkIter it, pf;
-      it.init(u0, u1, G, p.chunk_groups);
-      pf.init(u0, u1, G, p.chunk_groups);
-      Chunk c, pc;
-      int ahead = 0;
-      bool pf_more = p.l2ahead > 0;
-      auto prefetch = [&]() {
-        while (pf_more && ahead < p.l2ahead) {
-          if (!pf.next(pc)) {
-            pf_more = false;
-            break;
-          }
-          l2_prefetch(p.stream + (static_cast<size_t>(pc.tile) * G + pc.g) * kTileGroupBytes, pc.n * kTileGroupBytes);
-          ahead += pc.n;
-        }
-      };
-      prefetch();
-      int st = 0, issued = 0;
+      SegIter it;
+      it.init(u0, u1, G);
+      Seg sg;
+      int st = 0, t = 0;
       uint32_t ph = 1;  // a fresh "empty" barrier reads as already released
       bool ok = true;
-      TR_DECL;
-      while (ok && it.next(c)) {
-        for (int gl = 0; gl < c.n; gl += kStepGroups) {
-          const int ng = (c.n - gl < kStepGroups) ? c.n - gl : kStepGroups;
-          TR_LAP(1);
+      while (ok && it.next(sg)) {
+        const uint8_t* src = p.stream + (static_cast<size_t>(sg.tile) * G + sg.g0) * kTileGroupBytes;
+        for (int gl = 0; gl < sg.L; gl += kStepGroups, ++t) {
+          const int ng = (sg.L - gl < kStepGroups) ? sg.L - gl : kStepGroups;
           if (!mbar_wait_bounded_relaxed(wempty_a + st * 8, ph, kSpinLimit)) {
+            GAVE_UP(3, t);
             atomicExch(p.status, W4A16_ETIMEOUT);
             ok = false;
             break;
           }
-          TR_LAP(0);
+          const int s0 = cache_slot(sg.g0 + gl);
+          const int s1 = ng == 2 ? cache_slot(sg.g0 + gl + 1) : s0;
+          table[t & (kTable - 1)] =
+              make_uint2(step_word(s0, s1, ng, gl + kStepGroups >= sg.L, sg.whole), static_cast<uint32_t>(sg.tile));
           mbar_expect_tx(wfull_a + st * 8, ng * kTileGroupBytes);
-          bulk_g2s(ring_a + st * kStageBytes, p.stream + (static_cast<size_t>(c.tile) * G + c.g + gl) * kTileGroupBytes,
-                   ng * kTileGroupBytes, wfull_a + st * 8);
-          ++issued;
-          ahead -= ng;
+          bulk_g2s(ring_a + st * kStageBytes, src + static_cast<size_t>(gl) * kTileGroupBytes, ng * kTileGroupBytes,
+                   wfull_a + st * 8);
           if (++st == DS) {
             st = 0;
             ph ^= 1;
           }
         }
-        prefetch();
       }
-      TR_OUT(0, 2);  // producer: [0] waiting for a free stage, [1] everything else
       // every copy this thread started has to land before the CTA may exit
-      for (int i = 0; i < DS && i < issued; ++i) {
-        const int k = issued - 1 - i;  // the last copy into stage k % DS
+      for (int i = 0; i < DS && i < t; ++i) {
+        const int k = t - 1 - i;  // the last copy into stage k % DS
         mbar_wait_bounded_relaxed(wfull_a + (k % DS) * 8, static_cast<uint32_t>(k / DS) & 1u, 1u << 14);
       }
     }
   } else if (warp == kWMma || warp == kWMma2) {
     // ================================================================ MMA issuers
-    // Two threads, even and odd steps. Issuing a step's eight small MMAs and its commit costs one thread
-    // more than the step's share of the HBM time; two issuers run side by side.
+    // Two warps, even and odd steps; one elected lane issues. Issuing a step's eight small MMAs and its
+    // commit costs one thread more than the step's share of the HBM time; two issuers run side by side.
+    // A step with a single group still issues both groups' MMAs: the second reads stale operands and
+    // fills accumulator columns nobody reads.
     if (team_ok) {
       constexpr uint32_t idesc = umma_idesc_s8(128, N);
       const int mine = (warp == kWMma) ? 0 : 1;
       bool ok = true;
-      if (cache && !wait_h(bready_a, 0, p.hint, kSpinLimit)) {
+      if (!wait_h(bready_a, 0, p.hint, kSpinLimit)) {
+        GAVE_UP(4, -1);
         atomicExch(p.status, W4A16_ETIMEOUT);
         ok = false;
       }
-      WorkIter it;
-      it.init(u0, u1, G, p.chunk_groups);
-      Chunk c;
-      const uint32_t lbo = p.b_lbo;
       // descriptor of the B region's first block, first 32-k step; other blocks and steps only move the address field
-      const uint64_t desc0 = umma_desc_kmajor(bq_a, lbo, 128);
-      const uint32_t step16 = (2 * lbo) >> 4, slot16 = static_cast<uint32_t>(p.b_slot) >> 4;
-      int t = 0;
-      TR_DECL;
-      while (ok && it.next(c)) {
-        for (int gl = 0; gl < c.n; gl += kStepGroups, ++t) {
-          if ((t & 1) != mine) continue;
-          const int ng = (c.n - gl < kStepGroups) ? c.n - gl : kStepGroups;
-          const int a = t & (AD2 - 1), d = t & (DD2 - 1);
-          const uint32_t aph = static_cast<uint32_t>(t / AD2) & 1u;
-          TR_LAP(3);
-          // A written (its writers also saw the D slot drained), and in ring mode B written
-          bool w_ok = wait_h(afull_a + a * 8, aph, p.hint, kSpinLimit);
-          TR_LAP(0);
-          w_ok = w_ok && (cache || wait_h(bfull_a + a * 8, aph, p.hint, kSpinLimit));
-          TR_LAP(1);
-          if (!w_ok) {
-            atomicExch(p.status, W4A16_ETIMEOUT);
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint32_t d_t = tmem + GE::kDCol0 + d * GE::kDColsS;
-          const uint32_t a_t = tmem + a * GE::kAColsS;
-          const uint64_t db0 = desc0 + static_cast<uint32_t>(cache ? cache_slot(c.g + gl) : a * kStepGroups) * slot16;
-          const uint64_t db1 = desc0 + static_cast<uint32_t>(cache ? cache_slot(c.g + gl + 1) : a * kStepGroups + 1) * slot16;
-          if (elect_one()) {
-            umma_s8_ts(d_t, a_t, db0, idesc, 0);
-            umma_s8_ts(d_t, a_t + 8, db0 + step16, idesc, 1);
-            umma_s8_ts(d_t, a_t + 16, db0 + 2 * step16, idesc, 1);
-            umma_s8_ts(d_t, a_t + 24, db0 + 3 * step16, idesc, 1);
-            if (ng == 2) {
-              umma_s8_ts(d_t + N, a_t + kAColsG, db1, idesc, 0);
-              umma_s8_ts(d_t + N, a_t + kAColsG + 8, db1 + step16, idesc, 1);
-              umma_s8_ts(d_t + N, a_t + kAColsG + 16, db1 + 2 * step16, idesc, 1);
-              umma_s8_ts(d_t + N, a_t + kAColsG + 24, db1 + 3 * step16, idesc, 1);
-            }
-            umma_commit(done_a + d * 8);
-          }
-          __syncwarp();
-        }
-      }
-      if (mine == 0 && lane == 0) TR_OUT(2, 4);  // mma: waiting for [2] A, [3] B; [5] issuing
-    }
-  } else if (warp == kWAct && !cache) {
-    // ================================================================ activation warp (ring mode)
-    // Waits for the previous kernel (it produced x), then per chunk bulk-copies the token rows and
-    // per step turns each token's 128 values per group into three int8 digit rows of the B slot.
-    pdl_wait();
-    WorkIter it;
-    it.init(u0, u1, G, p.chunk_groups);
-    Chunk c, cn;
-    const int rowb = p.chunk_groups * 256;
-    auto issue = [&](const Chunk& ch, int xb) {
-      if (lane == 0) {
-        fence_proxy_async();  // this warp's reads of the buffer come before the copy's writes
-        mbar_expect_tx(xfull_a + xb * 8, M * ch.n * 256);
-        for (int m = 0; m < M; ++m)
-          bulk_g2s(xraw_a + xb * p.xbuf_bytes + m * rowb, p.x + static_cast<size_t>(m) * p.K + ch.g * kGroup,
-                   ch.n * 256, xfull_a + xb * 8);
-      }
-    };
-    bool have = it.next(c);
-    if (have) issue(c, 0);
-    int xb = 0, n = 0, t = 0;
-    uint32_t xph0 = 0, xph1 = 0;
-    bool ok = true;
-    while (ok && have) {
-      const bool more = it.next(cn);
-      __syncwarp();
-      if (more) issue(cn, xb ^ 1);
-      if (!wait_h(xfull_a + xb * 8, xb ? xph1 : xph0, p.hint, kSpinLimit)) {
-        atomicExch(p.status, W4A16_ETIMEOUT);
-        ok = false;
-        break;
-      }
-      for (int gl = 0; gl < c.n && ok; gl += kStepGroups, ++t) {
-        const int ng = (c.n - gl < kStepGroups) ? c.n - gl : kStepGroups;
-        const int a = t & (AD2 - 1);
-        if (t >= AD2 && !wait_h(done_a + ((t - AD2) & (DD2 - 1)) * 8, static_cast<uint32_t>((t - AD2) / DD2) & 1u, p.hint,
-                                kSpinLimit)) {
+      const uint64_t desc0 = umma_desc_kmajor(bq_a, b_lbo, 128);
+      const uint32_t step16 = (2 * b_lbo) >> 4, slot16 = static_cast<uint32_t>(b_slot) >> 4;
+      for (int t = mine; ok && t < T; t += 2) {
+        const int a = t & (AD2 - 1), d = t & (DD2 - 1);
+        // A written; its writers also saw the D slot drained and the step's weights (and table entry) landed
+        if (!wait_h(afull_a + a * 8, static_cast<uint32_t>(t / AD2) & 1u, p.hint, kSpinLimit)) {
+          GAVE_UP(5, t);
           atomicExch(p.status, W4A16_ETIMEOUT);
-          ok = false;
           break;
         }
-        for (int j = 0; j < ng; ++j, ++n)
-          for (int m = 0; m < M; ++m) {
-            const uint2 rv =
-                *reinterpret_cast<const uint2*>(xraw + xb * p.xbuf_bytes + m * rowb + (gl + j) * 256 + lane * 8);
-            convert_group(rv, bq + (a * kStepGroups + j) * p.b_slot, p.b_lbo, m,
-                          reinterpret_cast<float2*>(xsinv) + (n & (kXsRing - 1)) * 16 + m, lane);
-          }
-        fence_proxy_async();  // B was written through the generic proxy, the tensor core reads it through the async one
+        tc_fence_after();
+        const uint32_t e = table[t & (kTable - 1)].x;
+        const uint32_t d_t = tmem + GE::kDCol0 + d * GE::kDColsS;
+        const uint32_t a_t = tmem + a * GE::kAColsS;
+        const uint64_t db0 = desc0 + (e & 0xFFu) * slot16;
+        const uint64_t db1 = desc0 + ((e >> 8) & 0xFFu) * slot16;
+        if (elect_one()) {
+          umma_s8_ts(d_t, a_t, db0, idesc, 0);
+          umma_s8_ts(d_t, a_t + 8, db0 + step16, idesc, 1);
+          umma_s8_ts(d_t, a_t + 16, db0 + 2 * step16, idesc, 1);
+          umma_s8_ts(d_t, a_t + 24, db0 + 3 * step16, idesc, 1);
+          umma_s8_ts(d_t + N, a_t + kAColsG, db1, idesc, 0);
+          umma_s8_ts(d_t + N, a_t + kAColsG + 8, db1 + step16, idesc, 1);
+          umma_s8_ts(d_t + N, a_t + kAColsG + 16, db1 + 2 * step16, idesc, 1);
+          umma_s8_ts(d_t + N, a_t + kAColsG + 24, db1 + 3 * step16, idesc, 1);
+          umma_commit(done_a + d * 8);
+        }
         __syncwarp();
-        if (lane == 0) mbar_arrive(bfull_a + a * 8);
       }
-      if (xb) xph1 ^= 1; else xph0 ^= 1;
-      xb ^= 1;
-      c = cn;
-      have = more;
-    }
-    if (!ok && lane == 0) {  // a copy into the other buffer may still be in flight
-      mbar_wait_bounded_relaxed(xfull_a + (xb ^ 1) * 8, (xb ^ 1) ? xph1 : xph0, 1u << 14);
     }
   } else if (warp >= kWUnpack0 && warp < kWUnpack0 + 8) {
     // ================================================================ unpack warps
     // Thread = one row of the tile = one TMEM lane. Per group: the row's 64 bytes (four 16-byte slots)
-    // -> 32 registers of int8 -> 32 TMEM columns of the A slot. Two warps per lane quarter, alternating steps.
+    // -> 32 registers of int8 -> 32 TMEM columns of the A slot. Two warps per lane quarter, alternating
+    // steps. Both groups of a step are always unpacked (a missing second group is stale bytes that feed
+    // only unread accumulator columns), so this role needs nothing but the step number.
     const int q = warp & 3, pair = (warp - kWUnpack0) >> 2, r = q * 32 + lane;
     const uint32_t lane_t = tmem + (static_cast<uint32_t>(q * 32) << 16);
-    uint32_t woff[4];
-#pragma unroll
-    for (int c4 = 0; c4 < 4; ++c4) woff[c4] = c4 * kChunkBytes + weight_slot(r, c4) * 16;
-    WorkIter it;
-    it.init(u0, u1, G, p.chunk_groups);
-    Chunk c;
-    int st = 0, t = 0, n = 0;
-    uint32_t wph = 0;
+    // the row's slot in even and odd 32-k chunks (rotated by four slots in odd chunks)
+    const uint32_t off_e = static_cast<uint32_t>(r) * 16, off_o = static_cast<uint32_t>((r + 4) & 127) * 16 + kChunkBytes;
+    int st = pair % DS;
+    uint32_t wph = static_cast<uint32_t>(pair / DS) & 1u;
     bool ok = team_ok;
-    TR_DECL;
-    while (ok && it.next(c)) {
-      for (int gl = 0; gl < c.n; gl += kStepGroups, ++t) {
-        const int ng = (c.n - gl < kStepGroups) ? c.n - gl : kStepGroups;
-        if ((t & 1) == pair) {
-          const int a = t & (AD2 - 1);
-          TR_LAP(5);
-          if (!wait_h(wfull_a + st * 8, wph, p.hint, kSpinLimit)) {
-            atomicExch(p.status, W4A16_ETIMEOUT);
-            ok = false;
-            break;
-          }
-          TR_LAP(0);
-          const uint32_t base = ring_a + st * kStageBytes;
-          uint4 w[4];
+    for (int t = pair; ok && t < T; t += 2) {
+      const int a = t & (AD2 - 1);
+      if (!wait_h(wfull_a + st * 8, wph, p.hint, kSpinLimit)) {
+        GAVE_UP(6, t);
+        atomicExch(p.status, W4A16_ETIMEOUT);
+        break;
+      }
+      const uint8_t* base = ring + st * kStageBytes;
+      uint4 w0 = *reinterpret_cast<const uint4*>(base + off_e);
+      uint4 w1 = *reinterpret_cast<const uint4*>(base + off_o);
+      uint4 w2 = *reinterpret_cast<const uint4*>(base + off_e + 2 * kChunkBytes);
+      uint4 w3 = *reinterpret_cast<const uint4*>(base + off_o + 2 * kChunkBytes);
+      // the A slot's previous step has been multiplied, and the D slot this step will fill has been read out
+      if ((t >= AD2 && !wait_h(done_a + ((t - AD2) & (DD2 - 1)) * 8, static_cast<uint32_t>((t - AD2) / DD2) & 1u, p.hint,
+                               kSpinLimit)) ||
+          (t >= DD2 &&
+           !wait_h(dempty_a + (t & (DD2 - 1)) * 8, static_cast<uint32_t>(t / DD2 - 1) & 1u, p.hint, kSpinLimit))) {
+        GAVE_UP(7, t);
+        atomicExch(p.status, W4A16_ETIMEOUT);
+        break;
+      }
+      tc_fence_after();
+      uint32_t* side_w = reinterpret_cast<uint32_t*>(side) + ((t & 7) * kStepGroups) * kTileRows + r;
 #pragma unroll
-          for (int c4 = 0; c4 < 4; ++c4) w[c4] = lds128(base + woff[c4]);
-          TR_LAP(2);
-          // the A slot's previous step has been multiplied, and the D slot this step will fill has been read out
-          if ((t >= AD2 && !wait_h(done_a + ((t - AD2) & (DD2 - 1)) * 8, static_cast<uint32_t>((t - AD2) / DD2) & 1u,
-                                   p.hint, kSpinLimit)) ||
-              (t >= DD2 && !wait_h(dempty_a + (t & (DD2 - 1)) * 8, static_cast<uint32_t>(t / DD2 - 1) & 1u, p.hint,
-                                   kSpinLimit))) {
-            atomicExch(p.status, W4A16_ETIMEOUT);
-            ok = false;
-            break;
-          }
-          TR_LAP(1);
-          tc_fence_after();
-#pragma unroll
-          for (int j = 0; j < kStepGroups; ++j) {
-            if (j < ng) {
-              const uint32_t gb = base + j * kTileGroupBytes;
-              if (j > 0) {
-#pragma unroll
-                for (int c4 = 0; c4 < 4; ++c4) w[c4] = lds128(gb + woff[c4]);
-              }
-              uint32_t sc, zp;
-              asm volatile("ld.shared.u16 %0, [%1];" : "=r"(sc) : "r"(gb + kTgScaleOff + 2 * r));
-              asm volatile("ld.shared.u8 %0, [%1];" : "=r"(zp) : "r"(gb + kTgZpOff + r));
-              uint32_t v[32];
-#pragma unroll
-              for (int c4 = 0; c4 < 4; ++c4) {
-                const uint32_t ww[4] = {w[c4].x, w[c4].y, w[c4].z, w[c4].w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  v[c4 * 8 + 2 * i] = ww[i] & 0x0F0F0F0Fu;
-                  v[c4 * 8 + 2 * i + 1] = (ww[i] >> 4) & 0x0F0F0F0Fu;
-                }
-              }
-              const uint32_t a_t = lane_t + a * GE::kAColsS + j * kAColsG;
-              tmem_st16(a_t, reinterpret_cast<const uint32_t(&)[16]>(v[0]));
-              tmem_st16(a_t + 16, reinterpret_cast<const uint32_t(&)[16]>(v[16]));
-              sts32(side_a + (((n + j) & (kSide - 1)) * kTileRows + r) * 4, (sc << 16) | zp);
-            }
-          }
-          TR_LAP(3);
-          tmem_wait_st();
-          TR_LAP(4);
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) {
-            mbar_arrive(afull_a + a * 8);
-            mbar_arrive(wempty_a + st * 8);
-          }
-          TR_LAP(5);
+      for (int j = 0; j < kStepGroups; ++j) {
+        const uint8_t* gb = base + j * kTileGroupBytes;
+        if (j > 0) {
+          w0 = *reinterpret_cast<const uint4*>(gb + off_e);
+          w1 = *reinterpret_cast<const uint4*>(gb + off_o);
+          w2 = *reinterpret_cast<const uint4*>(gb + off_e + 2 * kChunkBytes);
+          w3 = *reinterpret_cast<const uint4*>(gb + off_o + 2 * kChunkBytes);
         }
-        n += ng;
-        if (++st == DS) {
-          st = 0;
-          wph ^= 1;
+        const uint32_t sc = *reinterpret_cast<const uint16_t*>(gb + kTgScaleOff + 2 * r);
+        const uint32_t zp = *(gb + kTgZpOff + r);
+        const uint32_t ww[16] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w,
+                                 w2.x, w2.y, w2.z, w2.w, w3.x, w3.y, w3.z, w3.w};
+        uint32_t v[32];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          v[2 * i] = ww[i] & 0x0F0F0F0Fu;
+          v[2 * i + 1] = (ww[i] >> 4) & 0x0F0F0F0Fu;
         }
+        const uint32_t a_t = lane_t + a * GE::kAColsS + j * kAColsG;
+        tmem_st16(a_t, reinterpret_cast<const uint32_t(&)[16]>(v[0]));
+        tmem_st16(a_t + 16, reinterpret_cast<const uint32_t(&)[16]>(v[16]));
+        side_w[j * kTileRows] = (sc << 16) | zp;
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(afull_a + a * 8);
+        mbar_arrive(wempty_a + st * 8);
+      }
+      st += 2;
+      if (st >= DS) {
+        st -= DS;
+        wph ^= 1;
       }
     }
-    if (warp == kWUnpack0 && lane == 0) TR_OUT(14, 6);  // unpack: waiting for [6] weights, [7] a free A slot; [8] loads, [9] unpack + store
   } else if (warp < CW) {
     // ================================================================ fix-up warps
     const int q = warp, r = q * 32 + lane;
@@ -805,106 +644,93 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
     // (tile, first/last contributing CTA, arrival ticket) of up to two split tiles, in lane 0
     int sp_n = 0, sp_tile0 = 0, sp_cf0 = 0, sp_cl0 = 0, sp_tile1 = 0, sp_cf1 = 0, sp_cl1 = 0;
     unsigned sp_old0 = 0, sp_old1 = 0;
-    bool waited_pdl = cache;  // the cache-mode conversion above already waited
-    auto before_global_write = [&]() {
-      if (!waited_pdl) {
-        pdl_wait();  // outputs and the shared scratch belong to the previous kernel until now
-        waited_pdl = true;
-      }
-    };
 
-    WorkIter it;
-    it.init(u0, u1, G, p.chunk_groups);
-    Chunk c;
-    int n = 0, t = 0;
     bool ok = team_ok;
-    constexpr int RG = GE::RG, GB = GE::GB;
+    constexpr int GB = GE::GB;
     constexpr int NLD = MT == 1 ? 4 : (MT == 2 ? 8 : N);
-    TR_DECL;
-    while (ok && it.next(c)) {
-      // RG groups (RG/2 steps) per round: one wait per issuer (a commit covers everything its thread issued
-      // before), GB groups' tensor-memory loads in flight together.
-      for (int gl = 0; gl < c.n; gl += RG) {
-        const int rg = (c.n - gl < RG) ? c.n - gl : RG;
-        const int ns = (rg + kStepGroups - 1) / kStepGroups;
-        TR_LAP(1);
-        {
-          const int l1 = t + ns - 1, l2 = t + ns - 2;
-          bool w_ok = wait_h(done_a + (l1 & (DD2 - 1)) * 8, static_cast<uint32_t>(l1 / DD2) & 1u, p.hint, kSpinLimit);
-          if (ns > 1)
-            w_ok = w_ok && wait_h(done_a + (l2 & (DD2 - 1)) * 8, static_cast<uint32_t>(l2 / DD2) & 1u, p.hint, kSpinLimit);
-          if (!w_ok) {
-            atomicExch(p.status, W4A16_ETIMEOUT);
-            ok = false;
-            break;
-          }
-        }
-        TR_LAP(0);
-#ifdef W4A16_TRACE
-        if (tid == 0 && n == 0) TL(4);
-#endif
-        tc_fence_after();
-#pragma unroll
-        for (int k0 = 0; k0 < RG; k0 += GB) {
-          if (k0 < rg) {
-            uint32_t dv[GB][NLD];
-            uint32_t sz[GB];
-#pragma unroll
-            for (int j = 0; j < GB; ++j) {
-              const int k = k0 + j;
-              if (k < rg) {
-                const uint32_t d_t = lane_t + ((t + (k >> 1)) & (DD2 - 1)) * GE::kDColsS + (k & 1) * N;
-                if constexpr (MT == 1) tmem_ld4(d_t, dv[j]);
-                else if constexpr (MT == 2) tmem_ld8(d_t, dv[j]);
-                else {
-#pragma unroll
-                  for (int i = 0; i < N / 16; ++i) tmem_ld16(d_t + 16 * i, dv[j] + 16 * i);
-                }
-                sz[j] = lds32(side_a + (((n + k) & (kSide - 1)) * kTileRows + r) * 4);
-              }
-            }
-            TR_LAP(2);
-            tmem_wait_ld();
-            TR_LAP(3);
-            if (k0 + GB >= rg) {  // the round's last loads are in registers: release its D slots
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) {
-#pragma unroll
-                for (int sidx = 0; sidx < RG / kStepGroups; ++sidx)
-                  if (sidx < ns) mbar_arrive(dempty_a + ((t + sidx) & (DD2 - 1)) * 8);
-              }
-            }
-#pragma unroll
-            for (int j = 0; j < GB; ++j) {
-              const int k = k0 + j;
-              if (k < rg) {
-                const uint32_t xs_a = xsinv_a + (cache ? cache_slot(c.g + gl + k) * MT : ((n + k) & (kXsRing - 1)) * 16) * 8;
-                const float s = __uint_as_float(sz[j] & 0xFFFF0000u);
-                const float z = static_cast<float>(sz[j] & 0xFFu);
-#pragma unroll
-                for (int m = 0; m < MT; ++m)
-                  if (m < M) {
-                    const uint2 tt = lds64(xs_a + m * 8);  // (sum of X, 2^-p)
-                    const float d0 = small_int_to_float(dv[j][3 * m]), d1 = small_int_to_float(dv[j][3 * m + 1]);
-                    const float d2 = small_int_to_float(dv[j][3 * m + 2]);
-                    const float dot = fmaf(d2, 65536.f, fmaf(d1, 256.f, d0));
-                    fin[m] = fmaf(s * __uint_as_float(tt.y), fmaf(-z, __uint_as_float(tt.x), dot), fin[m]);
-                  }
-              }
-            }
-          }
-        }
-        TR_LAP(4);
-        n += rg;
-        t += ns;
+    const uint32_t* side_r = reinterpret_cast<const uint32_t*>(side) + r;
+    const float2* xs_tab = reinterpret_cast<const float2*>(xsinv);
+    for (int t = 0; ok && t < T;) {
+      // A round is one or two steps (two unless the first ends its segment): one wait per issuer (a commit
+      // covers everything its thread issued before), GB groups' tensor-memory loads in flight together.
+      if (!wait_h(done_a + (t & (DD2 - 1)) * 8, static_cast<uint32_t>(t / DD2) & 1u, p.hint, kSpinLimit)) {
+        GAVE_UP(8, t);
+        atomicExch(p.status, W4A16_ETIMEOUT);
+        ok = false;
+        break;
       }
-      if (!ok) break;
-      if (c.seg_last) {
-        // ---- end of this CTA's segment of row tile c.tile: groups [seg_g0, seg_g1) ----
-        before_global_write();
-        const int tile = c.tile;
-        if (c.seg_g0 == 0 && c.seg_g1 == G) {
+      const uint2 e0 = table[t & (kTable - 1)];  // written before the step's weights were requested
+      const bool two = !((e0.x >> 17) & 1u) && t + 1 < T;
+      if (two && !wait_h(done_a + ((t + 1) & (DD2 - 1)) * 8, static_cast<uint32_t>((t + 1) / DD2) & 1u, p.hint, kSpinLimit)) {
+        GAVE_UP(9, t);
+        atomicExch(p.status, W4A16_ETIMEOUT);
+        ok = false;
+        break;
+      }
+#ifdef W4A16_TRACE
+      if (tid == 0 && t == 0) TL(4);
+#endif
+      tc_fence_after();
+      const uint2 e1 = two ? table[(t + 1) & (kTable - 1)] : e0;
+      const int ng0 = static_cast<int>((e0.x >> 16) & 1u) + 1;
+      const int rg = two ? ng0 + static_cast<int>((e1.x >> 16) & 1u) + 1 : ng0;  // groups of the round (ng0 == 2 if two)
+      // group k of the round: step t + (k >> 1), position k & 1
+#pragma unroll
+      for (int k0 = 0; k0 < 4; k0 += GB) {
+        if (k0 < rg) {
+          uint32_t dv[GB][NLD];
+          uint32_t sz[GB];
+#pragma unroll
+          for (int j = 0; j < GB; ++j) {
+            const int k = k0 + j;
+            if (k < rg) {
+              const int ts = t + (k >> 1);
+              const uint32_t d_t = lane_t + (ts & (DD2 - 1)) * GE::kDColsS + (k & 1) * N;
+              if constexpr (MT == 1) tmem_ld4(d_t, dv[j]);
+              else if constexpr (MT == 2) tmem_ld8(d_t, dv[j]);
+              else {
+#pragma unroll
+                for (int i = 0; i < N / 16; ++i) tmem_ld16(d_t + 16 * i, dv[j] + 16 * i);
+              }
+              sz[j] = side_r[((ts & 7) * kStepGroups + (k & 1)) * kTileRows];
+            }
+          }
+          tmem_wait_ld();
+          if (k0 + GB >= rg) {  // the round's last loads are in registers: release its D slots
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              mbar_arrive(dempty_a + (t & (DD2 - 1)) * 8);
+              if (two) mbar_arrive(dempty_a + ((t + 1) & (DD2 - 1)) * 8);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < GB; ++j) {
+            const int k = k0 + j;
+            if (k < rg) {
+              const uint32_t ew = (k >> 1) ? e1.x : e0.x;
+              const uint32_t slot = (k & 1) ? (ew >> 8) & 0xFFu : ew & 0xFFu;
+              const float s = __uint_as_float(sz[j] & 0xFFFF0000u);
+              const float z = __uint_as_float(0x4B000000u | (sz[j] & 0xFFu)) - 8388608.0f;
+#pragma unroll
+              for (int m = 0; m < MT; ++m)
+                if (m < M) {
+                  const float2 xv = xs_tab[slot * MT + m];  // (sum of X, 2^-p)
+                  const float d0 = small_int_to_float(dv[j][3 * m]), d1 = small_int_to_float(dv[j][3 * m + 1]);
+                  const float d2 = small_int_to_float(dv[j][3 * m + 2]);
+                  const float dot = fmaf(d2, 65536.f, fmaf(d1, 256.f, d0));
+                  fin[m] = fmaf(s * xv.y, fmaf(-z, xv.x, dot), fin[m]);
+                }
+            }
+          }
+        }
+      }
+      const uint2 el = two ? e1 : e0;  // the round's last step
+      t += two ? 2 : 1;
+      if ((el.x >> 17) & 1u) {
+        // ---- end of this CTA's segment of row tile el.y ----
+        const int tile = static_cast<int>(el.y);
+        if ((el.x >> 18) & 1u) {
           finalize(tile, fin);
         } else {
           // split tile: this warp publishes its 32 rows and moves on; no CTA-wide barrier
@@ -912,10 +738,10 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
           const int c_first = static_cast<int>(((X0 + 1) * gridDim.x - 1) / U);
           const int c_last = static_cast<int>(((X0 + G) * gridDim.x - 1) / U);
           const int which = (u0 / G == tile) ? 0 : 1;
-          float* slot = p.partial + (static_cast<size_t>(blockIdx.x) * 2 + which) * SLOT;
+          float* slotp = p.partial + (static_cast<size_t>(blockIdx.x) * 2 + which) * SLOT;
 #pragma unroll
           for (int m = 0; m < MT; ++m)
-            if (m < M) slot[m * kTileRows + r] = fin[m];
+            if (m < M) slotp[m * kTileRows + r] = fin[m];
           __syncwarp();
           if (lane == 0) {
             __threadfence();  // release: this warp's partial rows (ordered by the __syncwarp) before the ticket
@@ -932,10 +758,7 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
         for (int m = 0; m < MT; ++m) fin[m] = 0.f;
       }
     }
-
-    TR_LAP(1);
     if (tid == 0) TL(5);
-    if (warp == 0 && lane == 0) TR_OUT(8, 5);  // fix-up: [10] waiting for D, [11] everything else in the main loop
     // ---- split tiles: the warp that drew the last ticket for its rows adds the pieces up ----
     if (ok) {
       const int ns = __shfl_sync(0xffffffffu, sp_n, 0);
@@ -966,7 +789,6 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
     }
 
     if (p.argmax) {
-      before_global_write();
       // ---- fused argmax: thread -> warp -> CTA -> grid, larger value then lower index ----
 #pragma unroll
       for (int m = 0; m < MT; ++m)
@@ -1027,13 +849,7 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
   // every role ends here: tensor memory goes back only after all its readers and writers are done
   tc_fence_before();
   __syncthreads();
-#ifdef W4A16_TRACE
-  if (tid == 0) {
-    TL(6);
-    g_trace[blockIdx.x * 24 + 21] = clock64() - tr_kernel0;  // whole CTA
-    g_trace[blockIdx.x * 24 + 22] = u1 - u0;
-  }
-#endif
+  if (tid == 0) TL(6);
   if (warp == kWMma) {
     tc_fence_after();
     tmem_dealloc(*reinterpret_cast<volatile uint32_t*>(tmem_slot), kTmemCols);
@@ -1053,29 +869,23 @@ __global__ void k_pairs_reduce(int32_t* ids, const Pair* pairs, int nranks, int 
 
 // ------------------------------------------------------------------ host side
 struct Config {
-  int depth;     // weight ring stages (two blocks, 17152 B, each)
-  int l2ahead;   // blocks of L2 prefetch ahead of the ring
+  int depth;     // weight ring stages (two blocks, 17152 B, each); even
   int pdl;
-  int cache_kb;  // largest B region (KB) for which all k groups are kept converted in shared memory
   int smem_kb;   // shared-memory target per CTA that still lets the next launch's CTA fit beside it
   int hint;      // suspend-time hint of the in-kernel mbarrier waits, ns
 };
 
 const Config& config() {
   static Config c = [] {
-    Config k{5, 0, 1, 56, 112, 2000};
+    Config k{4, 1, 112, 2000};
     if (const char* e = getenv("W4A16_DEPTH")) k.depth = atoi(e);
-    if (const char* e = getenv("W4A16_L2AHEAD")) k.l2ahead = atoi(e);
     if (const char* e = getenv("W4A16_PDL")) k.pdl = atoi(e) != 0;
-    if (const char* e = getenv("W4A16_BCACHE_KB")) k.cache_kb = atoi(e);
     if (const char* e = getenv("W4A16_SMEM_KB")) k.smem_kb = atoi(e);
     if (const char* e = getenv("W4A16_HINT")) k.hint = atoi(e);
     if (k.hint < 0) k.hint = 0;
     if (k.depth < 2) k.depth = 2;
-    if (k.depth > 20) k.depth = 20;
-    if (k.l2ahead < 0) k.l2ahead = 0;
-    if (k.l2ahead > 256) k.l2ahead = 256;
-    if (k.cache_kb < 0) k.cache_kb = 0;
+    if (k.depth > 12) k.depth = 12;
+    k.depth &= ~1;  // even: see the ring-depth note in launch_cfg
     return k;
   }();
   return c;
@@ -1083,36 +893,42 @@ const Config& config() {
 
 constexpr int kMaxCtasPerSm = 2;  // what the scratch is sized for (the grid itself is one CTA per SM)
 
+int tile_rows() { return kTileRows; }
+
+int grid_for_shape(int out_f, int G, int sms) {
+  const int tiles = (out_f + tile_rows() - 1) / tile_rows();
+  const long long U = static_cast<long long>(tiles) * G;
+  return static_cast<int>(U < sms ? U : sms);
+}
+
+// groups whose digit rows one CTA keeps: the most (tile, group) units any CTA gets, at most all of K
+int cache_groups_for(int tiles, int G, int grid) {
+  const long long U = static_cast<long long>(tiles) * G;
+  const int per_cta = static_cast<int>((U + grid - 1) / grid);
+  return per_cta < G ? per_cta : G;
+}
+
 template <int MT>
 int launch_cfg(SkinnyParams& p, int grid, cudaStream_t st, int smem_optin) {
-  using GE = Geo<MT>;
-  const int M = p.M, G = p.G;
-  const long long U = static_cast<long long>(p.tiles) * G;
-  const int per_cta = static_cast<int>((U + grid - 1) / grid);  // most (tile, group) units any CTA gets
-  const int cache_groups = per_cta < G ? per_cta : G;
-  const int cache_bytes = cache_groups * 384 * M + 256;
-  p.cache = cache_bytes <= config().cache_kb * 1024;
-  if (p.cache) {
-    p.b_slot = 384 * M;
-    p.b_lbo = 48 * M;
-    p.b_bytes = cache_bytes;
-    p.xs_bytes = cache_groups * MT * 8;
-    p.xbuf_bytes = 0;
-  } else {
-    p.b_slot = GE::kBGroup;
-    p.b_lbo = GE::kLbo;
-    p.b_bytes = GE::AD2 * kStepGroups * GE::kBGroup;
-    p.xs_bytes = kXsRing * 16 * 8;
-  }
-  // ring depth: as configured, but inside the per-CTA target (two launches side by side) when possible
-  int limit = config().smem_kb * 1024;
+  const int groups = cache_groups_for(p.tiles, p.G, grid);
+  p.b_bytes = groups * 384 * p.M + 256;
+  p.xs_bytes = groups * MT * 8;
+  // ring depth: as configured; M <= 2 stays inside the per-CTA target (two launches side by side)
+  int limit = Geo<MT>::kMinCtas == 2 ? config().smem_kb * 1024 : smem_optin;
   if (limit > smem_optin) limit = smem_optin;
-  int smem = total_smem<MT>(p.depth, p.b_bytes, p.xbuf_bytes, p.xs_bytes);
+  // The depth stays EVEN. The two unpack warps of a lane quarter take alternate steps, and a parity wait on
+  // an mbarrier only tells the current phase from the previous one: with an odd depth a stage's consecutive
+  // uses would belong to different warps, and a warp that runs ahead could take "the other warp's copy has
+  // not landed yet" for "my copy has landed".
+  p.depth = config().depth;
+  int smem = total_smem<MT>(p.depth, p.b_bytes, p.xs_bytes);
   while (smem > limit && p.depth > 2) {
-    --p.depth;
-    smem = total_smem<MT>(p.depth, p.b_bytes, p.xbuf_bytes, p.xs_bytes);
+    p.depth -= 2;
+    smem = total_smem<MT>(p.depth, p.b_bytes, p.xs_bytes);
   }
-  if (smem > smem_optin) return fail(W4A16_EINVAL, "decode kernel needs %d bytes of shared memory, device offers %d", smem, smem_optin);
+  if (smem > smem_optin)
+    return fail(W4A16_EINVAL, "decode kernel needs %d bytes of shared memory for in_f = %d, M = %d; the device offers %d",
+                smem, p.K, p.M, smem_optin);
   static int attr_set[64] = {};
   int dev = 0;
   W4_CUDA(cudaGetDevice(&dev));
@@ -1134,12 +950,13 @@ int launch_cfg(SkinnyParams& p, int grid, cudaStream_t st, int smem_optin) {
   return W4A16_OK;
 }
 
-int tile_rows() { return kTileRows; }
-
-int grid_for_shape(int out_f, int G, int sms) {
-  const int tiles = (out_f + tile_rows() - 1) / tile_rows();
-  const long long U = static_cast<long long>(tiles) * G;
-  return static_cast<int>(U < sms ? U : sms);
+// Most tokens one launch can take: the digit rows of `groups` k groups (384 B per group and token) must
+// fit beside a two-stage weight ring.
+int max_batch(int groups, int smem_optin) {
+  const int fixed = 2 * kStageBytes + kSide * kTileRows * 4 + kTable * 8 + 64 * 8 + 16 + 256;
+  int mb = (smem_optin - fixed) / (groups * (384 + 8));
+  if (mb > kMaxBatch) mb = kMaxBatch;
+  return mb;
 }
 
 int launch_skinny(SkinnyParams& p, const w4a16_weights_t* w, const uint16_t* x, int M, w4a16_scratch_t* s,
@@ -1152,8 +969,6 @@ int launch_skinny(SkinnyParams& p, const w4a16_weights_t* w, const uint16_t* x, 
   if (!di) return W4A16_ECUDA;
   const int TR = tile_rows();
   p.stream = reinterpret_cast<const uint8_t*>(w->qweight);
-  p.x = x;
-  p.M = M;
   p.N = w->out_f;
   p.K = w->in_f;
   p.G = w->num_groups;
@@ -1162,24 +977,37 @@ int launch_skinny(SkinnyParams& p, const w4a16_weights_t* w, const uint16_t* x, 
   p.counters = reinterpret_cast<unsigned*>(s->xgsum);
   p.cta_pairs = s->xf;
   p.status = di->status;
-  static int launch_counter = 0;
-  p.trace_id = launch_counter++;
-  p.depth = config().depth;
   p.hint = static_cast<uint32_t>(config().hint);
-  p.l2ahead = config().l2ahead;
-  // groups per raw activation chunk: about 2 KB per buffer (256 B per token per group)
-  int cg = (2048 / (256 * M)) & ~1;
-  if (cg > kMaxChunkGroups) cg = kMaxChunkGroups;
-  if (cg < 2) cg = 2;
-  p.chunk_groups = cg;
-  p.xbuf_bytes = M * cg * 256;
   const int grid = grid_for_shape(w->out_f, w->num_groups, di->sms);
   if (int rc = w4a16_scratch_check(s, w->out_f, M)) return rc;
-  if (M == 1) return launch_cfg<1>(p, grid, st, di->smem_optin);
-  if (M == 2) return launch_cfg<2>(p, grid, st, di->smem_optin);
-  if (M <= 5) return launch_cfg<5>(p, grid, st, di->smem_optin);
-  if (M <= 10) return launch_cfg<10>(p, grid, st, di->smem_optin);
-  return launch_cfg<16>(p, grid, st, di->smem_optin);
+  const int mb = max_batch(cache_groups_for(p.tiles, p.G, grid), di->smem_optin);
+  if (mb < 1)
+    return fail(W4A16_EINVAL, "in_f = %d is too wide for the decode kernel's activation cache", w->in_f);
+  // token batches: one launch for M <= mb, else equal halves (each launch streams the weights once)
+  const int nb = (M + mb - 1) / mb;
+  static int launch_counter = 0;
+  const SkinnyParams base = p;
+  for (int b = 0, m0 = 0; b < nb; ++b) {
+    const int m1 = static_cast<int>(static_cast<long long>(M) * (b + 1) / nb);
+    SkinnyParams q = base;
+    q.M = m1 - m0;
+    q.x = x + static_cast<size_t>(m0) * w->in_f;
+    if (base.y)
+      q.y = base.y_f32 ? static_cast<void*>(static_cast<float*>(base.y) + static_cast<size_t>(m0) * base.ldy)
+                       : static_cast<void*>(static_cast<uint16_t*>(base.y) + static_cast<size_t>(m0) * base.ldy);
+    for (int r = 0; r < base.npeers; ++r) q.y_peers[r] = base.y_peers[r] + static_cast<size_t>(m0) * base.ldy;
+    if (base.ids) q.ids = base.ids + m0;
+    if (base.pairs_out) q.pairs_out = static_cast<Pair*>(base.pairs_out) + m0;
+    q.trace_id = launch_counter++;
+    int rc;
+    if (q.M == 1) rc = launch_cfg<1>(q, grid, st, di->smem_optin);
+    else if (q.M == 2) rc = launch_cfg<2>(q, grid, st, di->smem_optin);
+    else if (q.M <= 5) rc = launch_cfg<5>(q, grid, st, di->smem_optin);
+    else rc = launch_cfg<10>(q, grid, st, di->smem_optin);
+    if (rc) return rc;
+    m0 = m1;
+  }
+  return W4A16_OK;
 }
 
 }  // namespace
@@ -1190,9 +1018,9 @@ using namespace w4a16;
 extern "C" {
 
 #ifdef W4A16_TRACE
-__attribute__((visibility("default"))) int w4a16_debug_trace(long long* dst, int n) {
+__attribute__((visibility("default"))) int w4a16_debug_where(int* dst) {
   W4_CUDA(cudaDeviceSynchronize());
-  W4_CUDA(cudaMemcpyFromSymbol(dst, g_trace, sizeof(long long) * n));
+  W4_CUDA(cudaMemcpyFromSymbol(dst, g_where, sizeof(int) * 8));
   return 0;
 }
 __attribute__((visibility("default"))) int w4a16_debug_timeline(long long* dst, int n) {
