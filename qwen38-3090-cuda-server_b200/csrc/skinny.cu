@@ -49,13 +49,14 @@ namespace w4a16 {
 namespace {
 
 constexpr int CW = 4;                      // fix-up warps per CTA: 32 rows of the 128-row tile each
-constexpr int kWarps = 16;
+constexpr int kWarps = 24;
 constexpr int kThreads = kWarps * 32;
 constexpr int kWUnpack0 = 4;               // warps 4..11 unpack
 constexpr int kWProducer = 12;
 constexpr int kWMma = 13;                  // MMA issuer of the even steps; owns the tensor-memory allocation
 constexpr int kWMma2 = 15;                 // MMA issuer of the odd steps
-constexpr int kTeam = kWarps - 2;          // warps that convert activations (all but producer, kWMma)
+constexpr int kWConv0 = 16;                // warps 16..23 (and the otherwise idle warp 14) only convert activations
+constexpr int kTeam = 4 + 1 + 8;           // converting warps: the fix-up warps, warp 14, warps 16..23
 constexpr int kStepGroups = 2;             // k groups per step: every hand-off between roles moves two groups
 constexpr int kStageBytes = kStepGroups * kTileGroupBytes;  // 17152
 constexpr int kSide = 16;                  // (scale, zp) side ring: 8 steps x 2 groups
@@ -90,7 +91,6 @@ struct Geo {
   static constexpr int kDColsS = kStepGroups * N;        // D columns per step
   static constexpr int kDCol0 = AD2 * kAColsS;           // first D column
   static constexpr int GB = MT == 1 ? 4 : (MT == 2 ? 2 : 1);  // groups whose tensor-memory loads are in flight together
-  static constexpr int kMinCtas = MT <= 2 ? 2 : 1;       // M <= 2 leaves room for the next launch's CTA
   static_assert(kDCol0 + DD2 * kDColsS <= kTmemCols, "tensor memory budget");
   static_assert(AD2 <= DD2 && 2 <= DD2 / 2, "ring depths");
   static_assert(kStepGroups * DD2 <= kSide, "a (scale, zp) slot is read before the D slot of its step is released");
@@ -310,7 +310,7 @@ __device__ __forceinline__ void convert_group(uint2 rv, uint8_t* bslot, int lbo,
 }
 
 template <int MT>
-__global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const SkinnyParams p) {
+__global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   using GE = Geo<MT>;
   constexpr int N = GE::N, AD2 = GE::AD2, DD2 = GE::DD2;
   constexpr int SLOT = kTileRows * MT;  // floats per partial tile
@@ -358,18 +358,16 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
   const uint32_t bready_a = dempty_a + DD2 * 8;     // every needed group's digit rows are written
   const uint32_t tmemrdy_a = bready_a + 8;          // tensor memory allocated, base address published
 
-  if (tid == 0) {
-    for (int i = 0; i < DS; ++i) {
-      mbar_init(wfull_a + i * 8, 1);
-      mbar_init(wempty_a + i * 8, 4);
+  {
+    // barrier i of the block [wfull | wempty | afull | done | dempty | bready | tmemrdy]: arrival counts
+    const int nb = bar_count<MT>(DS);
+    if (tid < nb) {
+      uint32_t cnt = 1;                                                    // wfull, done, tmemrdy
+      if (tid >= DS && tid < 2 * DS + AD2) cnt = 4;                        // wempty, afull: 4 unpack warps
+      else if (tid >= 2 * DS + AD2 + DD2 && tid < 2 * DS + AD2 + 2 * DD2) cnt = CW;  // dempty
+      else if (tid == nb - 2) cnt = kTeam;                                 // bready
+      mbar_init(wfull_a + tid * 8, cnt);
     }
-    for (int i = 0; i < AD2; ++i) mbar_init(afull_a + i * 8, 4);
-    for (int i = 0; i < DD2; ++i) {
-      mbar_init(done_a + i * 8, 1);
-      mbar_init(dempty_a + i * 8, CW);
-    }
-    mbar_init(bready_a, kTeam);
-    mbar_init(tmemrdy_a, 1);
     fence_mbar_init();
   }
   __syncthreads();
@@ -385,14 +383,15 @@ __global__ void __launch_bounds__(kThreads, Geo<MT>::kMinCtas) k_skinny(const Sk
   }
 
   bool team_ok = true;
-  if (warp != kWProducer && warp != kWMma) {
+  const bool converts = warp < CW || warp == 14 || warp >= kWConv0;
+  if (converts) {
     // ================================================================ activations -> digit rows, once per CTA
-    // All warps but the producer and the allocating warp take part (their own work cannot start before
-    // the activations exist anyway). x comes straight from global memory (L2); a round's loads are all in
+    // The fix-up warps (idle until the first sums exist) and nine warps that do nothing else. The unpack
+    // warps and the issuers do not take part: they fill the A ring from the weights meanwhile. x comes straight from global memory (L2); a round's loads are all in
     // flight before its first conversion.
     pdl_wait();  // the previous kernel produced x
     if (tid == 0) TL(2);
-    const int ti = warp < kWProducer ? warp : warp - 2;
+    const int ti = warp < CW ? warp : (warp == 14 ? CW : warp - kWConv0 + CW + 1);
     const int cnt = (u1 - u0 < G) ? u1 - u0 : G;
     const int total = cnt * M;  // (group, token) items; item i belongs to warp i % kTeam
     constexpr int kBatch = 4;
@@ -871,16 +870,14 @@ __global__ void k_pairs_reduce(int32_t* ids, const Pair* pairs, int nranks, int 
 struct Config {
   int depth;     // weight ring stages (two blocks, 17152 B, each); even
   int pdl;
-  int smem_kb;   // shared-memory target per CTA that still lets the next launch's CTA fit beside it
   int hint;      // suspend-time hint of the in-kernel mbarrier waits, ns
 };
 
 const Config& config() {
   static Config c = [] {
-    Config k{4, 1, 112, 2000};
+    Config k{8, 1, 2000};
     if (const char* e = getenv("W4A16_DEPTH")) k.depth = atoi(e);
     if (const char* e = getenv("W4A16_PDL")) k.pdl = atoi(e) != 0;
-    if (const char* e = getenv("W4A16_SMEM_KB")) k.smem_kb = atoi(e);
     if (const char* e = getenv("W4A16_HINT")) k.hint = atoi(e);
     if (k.hint < 0) k.hint = 0;
     if (k.depth < 2) k.depth = 2;
@@ -913,9 +910,7 @@ int launch_cfg(SkinnyParams& p, int grid, cudaStream_t st, int smem_optin) {
   const int groups = cache_groups_for(p.tiles, p.G, grid);
   p.b_bytes = groups * 384 * p.M + 256;
   p.xs_bytes = groups * MT * 8;
-  // ring depth: as configured; M <= 2 stays inside the per-CTA target (two launches side by side)
-  int limit = Geo<MT>::kMinCtas == 2 ? config().smem_kb * 1024 : smem_optin;
-  if (limit > smem_optin) limit = smem_optin;
+  const int limit = smem_optin;
   // The depth stays EVEN. The two unpack warps of a lane quarter take alternate steps, and a parity wait on
   // an mbarrier only tells the current phase from the previous one: with an odd depth a stage's consecutive
   // uses would belong to different warps, and a warp that runs ahead could take "the other warp's copy has
