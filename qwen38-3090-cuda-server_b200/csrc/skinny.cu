@@ -132,7 +132,7 @@ __device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
 
 // ---- the order in which a CTA walks its unit range [u0,u1) -------------------------------
 // A segment is a run of consecutive k groups of one row tile. Row tiles that this CTA shares with a
-// neighbour come first (the piece at the end of the range, then the piece at its start), whole tiles
+// neighbour come first (the piece at the start of the range, then the piece at its end), whole tiles
 // after, so the cross-CTA reduction of the shared tiles overlaps everybody's main loop instead of
 // sitting at the end of the kernel. A segment of L groups is ceil(L/2) steps.
 struct Seg {
@@ -160,15 +160,15 @@ struct SegIter {
   __device__ bool next(Seg& s) {
     if (phase == 0) {
       phase = 1;
-      if (tail_partial) {
-        s.tile = t_last; s.g0 = 0; s.L = tail_g1; s.whole = false;
+      if (head_partial) {
+        s.tile = t_first; s.g0 = head_g0; s.L = (single ? tail_g1 : G) - head_g0; s.whole = false;
         return true;
       }
     }
     if (phase == 1) {
       phase = 2;
-      if (head_partial) {
-        s.tile = t_first; s.g0 = head_g0; s.L = (single ? tail_g1 : G) - head_g0; s.whole = false;
+      if (tail_partial) {
+        s.tile = t_last; s.g0 = 0; s.L = tail_g1; s.whole = false;
         return true;
       }
     }
@@ -255,7 +255,7 @@ __device__ __forceinline__ float small_int_to_float(uint32_t v) {
 
 // dynamic shared memory:
 //   [weight ring: depth x 17152][B region: b_bytes][(scale,zp) ring: kSide x 128 x 4][(sum, 2^-p): xs_bytes]
-//   [step table: kTable x 8][mbarriers][tmem base, flag]
+//   [step table: kTable x 8][ready counters: 256 x 4][mbarriers][tmem base, flag]
 // The B operand of one k group is eight 16-k chunks, 48 M bytes apart, each holding the 3 M digit rows in
 // use as consecutive 16-byte rows (an 8-row core matrix every 128 bytes). The rows the tensor core reads
 // beyond them are the next chunk's bytes: they only produce accumulator columns nobody reads, and the
@@ -266,7 +266,8 @@ __host__ __device__ constexpr int bar_count(int depth) {
 }
 template <int MT>
 __host__ __device__ inline int total_smem(int depth, int b_bytes, int xs_bytes) {
-  return depth * kStageBytes + b_bytes + kSide * kTileRows * 4 + xs_bytes + kTable * 8 + bar_count<MT>(depth) * 8 + 16;
+  return depth * kStageBytes + b_bytes + kSide * kTileRows * 4 + xs_bytes + kTable * 8 + 256 * 4 +
+         bar_count<MT>(depth) * 8 + 16;
 }
 
 // One token's 128 values of one k group (this lane: k = 4 lane .. 4 lane + 3, `rv`) -> three int8 digit
@@ -323,7 +324,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   uint8_t* side = bq + p.b_bytes;
   uint8_t* xsinv = side + kSide * kTileRows * 4;
   uint2* table = reinterpret_cast<uint2*>(xsinv + p.xs_bytes);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(table + kTable);
+  uint32_t* ready = reinterpret_cast<uint32_t*>(table + kTable);  // [slot]: tokens whose digit rows are written
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ready + 256);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + bar_count<MT>(DS));
   int* sflag = reinterpret_cast<int*>(tmem_slot + 1);
 
@@ -332,8 +334,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   const int G = p.G, M = p.M;
   const int U = p.tiles * G;
   if (tid == 0) TL(0);
-  const int u0 = static_cast<int>(static_cast<long long>(U) * blockIdx.x / gridDim.x);
-  const int u1 = static_cast<int>(static_cast<long long>(U) * (blockIdx.x + 1) / gridDim.x);
+  // (U * gridDim.x fits 32 bits: checked on the host; a 64-bit division here costs a visible part of the start-up)
+  const int u0 = static_cast<int>(static_cast<uint32_t>(U) * blockIdx.x / gridDim.x);
+  const int u1 = static_cast<int>(static_cast<uint32_t>(U) * (blockIdx.x + 1) / gridDim.x);
   // the digit rows of the groups this CTA multiplies, (g_first + j) % G for j < min(G, u1 - u0), live in slot j
   const int g_first = u0 % G;
   auto cache_slot = [&](int g) { return g - g_first + (g < g_first ? G : 0); };
@@ -358,6 +361,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   const uint32_t bready_a = dempty_a + DD2 * 8;     // every needed group's digit rows are written
   const uint32_t tmemrdy_a = bready_a + 8;          // tensor memory allocated, base address published
 
+  if (tid < 256) ready[tid] = 0u;
   {
     // barrier i of the block [wfull | wempty | afull | done | dempty | bready | tmemrdy]: arrival counts
     const int nb = bar_count<MT>(DS);
@@ -413,19 +417,22 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
         if (i < total) {
           const int gj = i / M, m = i - gj * M;
           convert_group(rv[j], bq + gj * b_slot, b_lbo, m, reinterpret_cast<float2*>(xsinv) + gj * MT + m, lane);
+          // publish the item: B was written through the generic proxy, the tensor core reads it through the
+          // async one; the slot counts as ready once all M tokens are in. Slots are numbered in the order the
+          // CTA walks its groups, and items are taken in slot order, so the first steps can start after the
+          // first round.
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            __threadfence_block();
+            atomicAdd(ready + gj, 1u);
+          }
         }
       }
     }
-    fence_proxy_async();  // B was written through the generic proxy, the tensor core reads it through the async one
     __syncwarp();
     if (lane == 0) mbar_arrive(bready_a);
     if (tid == 0) TL(3);
-    // the fix-up warps read the (sum, 2^-p) entries other warps wrote
-    if (warp < CW && !wait_h(bready_a, 0, p.hint, kSpinLimit)) {
-      GAVE_UP(1, -1);
-      atomicExch(p.status, W4A16_ETIMEOUT);
-      team_ok = false;
-    }
   }
 
   // This CTA owns all 512 columns, so its tensor-memory addresses start at 0: a compile-time constant
@@ -492,11 +499,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
       constexpr uint32_t idesc = umma_idesc_s8(128, N);
       const int mine = (warp == kWMma) ? 0 : 1;
       bool ok = true;
-      if (!wait_h(bready_a, 0, p.hint, kSpinLimit)) {
-        GAVE_UP(4, -1);
-        atomicExch(p.status, W4A16_ETIMEOUT);
-        ok = false;
-      }
+      bool all_ready = false;  // true once every slot is known to be written: no more polling
       // descriptor of the B region's first block, first 32-k step; other blocks and steps only move the address field
       const uint64_t desc0 = umma_desc_kmajor(bq_a, b_lbo, 128);
       const uint32_t step16 = (2 * b_lbo) >> 4, slot16 = static_cast<uint32_t>(b_slot) >> 4;
@@ -508,8 +511,25 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
           atomicExch(p.status, W4A16_ETIMEOUT);
           break;
         }
-        tc_fence_after();
         const uint32_t e = table[t & (kTable - 1)].x;
+        if (!all_ready) {
+          // the digit rows of this step's two slots (all M tokens each) must be in shared memory
+          const volatile uint32_t* rdy = ready;
+          const uint32_t s0 = e & 0xFFu, s1 = (e >> 8) & 0xFFu, need = static_cast<uint32_t>(M);
+          uint32_t spins = 0;
+          while (rdy[s0] < need || rdy[s1] < need) {
+            if (++spins > kSpinLimit) break;
+            __nanosleep(40);
+          }
+          if (spins > kSpinLimit) {
+            GAVE_UP(4, t);
+            atomicExch(p.status, W4A16_ETIMEOUT);
+            break;
+          }
+          __threadfence_block();
+          all_ready = mbar_try_wait(bready_a, 0, 0);
+        }
+        tc_fence_after();
         const uint32_t d_t = tmem + GE::kDCol0 + d * GE::kDColsS;
         const uint32_t a_t = tmem + a * GE::kAColsS;
         const uint64_t db0 = desc0 + (e & 0xFFu) * slot16;
@@ -975,6 +995,7 @@ int launch_skinny(SkinnyParams& p, const w4a16_weights_t* w, const uint16_t* x, 
   p.status = di->status;
   p.hint = static_cast<uint32_t>(config().hint);
   const int grid = grid_for_shape(w->out_f, w->num_groups, di->sms);
+  W4_REQUIRE(static_cast<long long>(p.tiles) * p.G * grid < (1LL << 32), "out_f x in_f too large for the decode kernel");
   if (int rc = w4a16_scratch_check(s, w->out_f, M)) return rc;
   const int mb = max_batch(cache_groups_for(p.tiles, p.G, grid), di->smem_optin);
   if (mb < 1)
