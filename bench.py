@@ -266,6 +266,8 @@ def run_ours(args):
             torch.cuda.synchronize()
 
         alg_bytes = sum(synth.algorithmic_bytes(L["N"], L["K"]) for L in layers)
+        # what THIS GPU streams per pass (its shards of the sharded layers, the replicated layers in full)
+        alg_local = sum(synth.algorithmic_bytes(L["n_local"], L["K"]) for L in layers)
         n_launch = len(layers)
 
         # ---- device-resident timing ----
@@ -316,7 +318,7 @@ def run_ours(args):
         peaks, which = measured_peaks()
         peak = float(peaks.get("hbm_gbs", FALLBACK_HBM_GBS))
         # dominant kernel: the persistent W4A16 GEMV kernel, all 256 launches of a step.
-        per_launch_bytes = alg_bytes / n_launch
+        per_launch_bytes = alg_local / n_launch  # roofline of one GPU's kernel: that GPU's bytes
         per_launch_s = ms_step * 1e-3 / n_launch
         achieved = per_launch_bytes / per_launch_s / 1e9
         # DRAM bytes per launch of the dominant kernel: ncu measured 97.79 MB (read + write) for the
