@@ -42,6 +42,7 @@
 #include <climits>
 #include <cstdlib>
 #include <cstring>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -91,6 +92,8 @@ struct Geo {
   static constexpr int kDColsS = kStepGroups * N;        // D columns per step
   static constexpr int kDCol0 = AD2 * kAColsS;           // first D column
   static constexpr int GB = MT == 1 ? 4 : (MT == 2 ? 2 : 1);  // groups whose tensor-memory loads are in flight together
+  static constexpr int FW = MT <= 2 ? 1 : 2;  // fix-up warps per lane quarter: they split the tokens (three were slower)
+  static constexpr int TM = (MT + FW - 1) / FW;               // tokens per fix-up warp
   static_assert(kDCol0 + DD2 * kDColsS <= kTmemCols, "tensor memory budget");
   static_assert(AD2 <= DD2 && 2 <= DD2 / 2, "ring depths");
   static_assert(kStepGroups * DD2 <= kSide, "a (scale, zp) slot is read before the D slot of its step is released");
@@ -315,7 +318,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   using GE = Geo<MT>;
   constexpr int N = GE::N, AD2 = GE::AD2, DD2 = GE::DD2;
   constexpr int SLOT = kTileRows * MT;  // floats per partial tile
-  constexpr int NFT = CW * 32;          // fix-up threads
   extern __shared__ __align__(128) uint8_t smem[];
 
   const int DS = p.depth;
@@ -368,7 +370,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
     if (tid < nb) {
       uint32_t cnt = 1;                                                    // wfull, done, tmemrdy
       if (tid >= DS && tid < 2 * DS + AD2) cnt = 4;                        // wempty, afull: 4 unpack warps
-      else if (tid >= 2 * DS + AD2 + DD2 && tid < 2 * DS + AD2 + 2 * DD2) cnt = CW;  // dempty
+      else if (tid >= 2 * DS + AD2 + DD2 && tid < 2 * DS + AD2 + 2 * DD2) cnt = CW * ((M + GE::TM - 1) / GE::TM);  // dempty: every active fix-up warp
       else if (tid == nb - 2) cnt = kTeam;                                 // bready
       mbar_init(wfull_a + tid * 8, cnt);
     }
@@ -438,7 +440,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   // This CTA owns all 512 columns, so its tensor-memory addresses start at 0: a compile-time constant
   // keeps every tcgen05 address warp-uniform. (Checked once; anything else is reported, not used.)
   constexpr uint32_t tmem = 0;
-  const bool uses_tmem = warp < kWProducer || warp == kWMma || warp == kWMma2;
+  const bool uses_tmem = warp < kWProducer || warp == kWMma || warp == kWMma2 || warp >= kWConv0;
   if (uses_tmem) {
     if (!wait_h(tmemrdy_a, 0, p.hint, kSpinLimit) || *reinterpret_cast<volatile uint32_t*>(tmem_slot) != 0u) {
       GAVE_UP(2, -1);
@@ -621,40 +623,49 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
         wph ^= 1;
       }
     }
-  } else if (warp < CW) {
+  } else if (warp < CW || warp >= kWConv0) {
     // ================================================================ fix-up warps
-    const int q = warp, r = q * 32 + lane;
+    // One warp per TMEM lane quarter and token set: warps 0..3 take the first TM tokens, warps 16..19 and
+    // 20..23 (idle after converting) the next ones when M is larger. Each keeps its own running sums, so
+    // the sets never have to be combined; a D slot is released when every active warp has loaded from it.
+    auto fixup = [&](auto ftag) {
+    constexpr int F = decltype(ftag)::value;  // this warp's token set
+    constexpr int TM = GE::TM, m0 = F * TM;   // its tokens: m0 .. m0 + TM - 1 (those below M)
+    const int q = warp & 3, r = q * 32 + lane;
+    const int fslot = F * CW + q;             // this warp's index among the fix-up warps
     const uint32_t lane_t = tmem + (static_cast<uint32_t>(q * 32) << 16) + GE::kDCol0;
+    unsigned* tickets = p.counters + static_cast<size_t>(F) * p.tiles * CW;  // [tile][quarter] of this token set
 
-    float fin[MT];
-    float best_v[MT];
-    int best_i[MT];
+    float fin[TM];
+    float best_v[TM];
+    int best_i[TM];
 #pragma unroll
-    for (int m = 0; m < MT; ++m) {
-      fin[m] = 0.f;
-      best_v[m] = -FLT_MAX;
-      best_i[m] = INT_MAX;
+    for (int i = 0; i < TM; ++i) {
+      fin[i] = 0.f;
+      best_v[i] = -FLT_MAX;
+      best_i[i] = INT_MAX;
     }
 
     // Final values of one row tile are in registers: write them out / fold into the argmax.
-    auto finalize = [&](int tile, const float(&v)[MT]) {
+    auto finalize = [&](int tile, const float(&v)[TM]) {
       const int row = tile * kTileRows + r;
       if (row >= p.N) return;  // zero-padded rows of the last tile
 #pragma unroll
-      for (int m = 0; m < MT; ++m) {
+      for (int i = 0; i < TM; ++i) {
+        const int m = m0 + i;
         if (m >= M) continue;
-        const uint16_t hb = float_to_bf16_bits(v[m]);
+        const uint16_t hb = float_to_bf16_bits(v[i]);
         if (p.y) {
           const size_t o = static_cast<size_t>(m) * p.ldy + p.y_col0 + row;
-          if (p.y_f32) static_cast<float*>(p.y)[o] = v[m];
+          if (p.y_f32) static_cast<float*>(p.y)[o] = v[i];
           else static_cast<uint16_t*>(p.y)[o] = hb;
           for (int pq = 0; pq < p.npeers; ++pq) p.y_peers[pq][o] = hb;
         }
         if (p.argmax) {
           const float lv = bf16_bits_to_float(hb);
-          if (better(lv, row, best_v[m], best_i[m])) {
-            best_v[m] = lv;
-            best_i[m] = row;
+          if (better(lv, row, best_v[i], best_i[i])) {
+            best_v[i] = lv;
+            best_i[i] = row;
           }
         }
       }
@@ -666,7 +677,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
 
     bool ok = team_ok;
     constexpr int GB = GE::GB;
-    constexpr int NLD = MT == 1 ? 4 : (MT == 2 ? 8 : N);
+    constexpr int kB0 = (3 * m0) / 16;                                       // first 16-column block of this set
+    constexpr int kB1 = (3 * (m0 + TM) - 1) / 16 < N / 16 ? (3 * (m0 + TM) - 1) / 16 : N / 16 - 1;  // last one
+    constexpr int NLD = MT == 1 ? 4 : (MT == 2 ? 8 : 16 * (kB1 - kB0 + 1));
+    constexpr int kC0 = MT <= 2 ? 0 : 16 * kB0;                              // column of dv[.][0]
     const uint32_t* side_r = reinterpret_cast<const uint32_t*>(side) + r;
     const float2* xs_tab = reinterpret_cast<const float2*>(xsinv);
     for (int t = 0; ok && t < T;) {
@@ -709,7 +723,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
               else if constexpr (MT == 2) tmem_ld8(d_t, dv[j]);
               else {
 #pragma unroll
-                for (int i = 0; i < N / 16; ++i) tmem_ld16(d_t + 16 * i, dv[j] + 16 * i);
+                for (int i = 0; i <= kB1 - kB0; ++i) tmem_ld16(d_t + 16 * (kB0 + i), dv[j] + 16 * i);
               }
               sz[j] = side_r[((ts & 7) * kStepGroups + (k & 1)) * kTileRows];
             }
@@ -732,13 +746,16 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
               const float s = __uint_as_float(sz[j] & 0xFFFF0000u);
               const float z = __uint_as_float(0x4B000000u | (sz[j] & 0xFFu)) - 8388608.0f;
 #pragma unroll
-              for (int m = 0; m < MT; ++m)
-                if (m < M) {
-                  const float2 xv = xs_tab[slot * MT + m];  // (sum of X, 2^-p)
-                  const float d0 = small_int_to_float(dv[j][3 * m]), d1 = small_int_to_float(dv[j][3 * m + 1]);
-                  const float d2 = small_int_to_float(dv[j][3 * m + 2]);
+              for (int i = 0; i < TM; ++i)
+                if (m0 + i < M) {
+                  // (tokens past MT never pass the test above; the clamp only keeps their dead indices in range)
+                  const int c = 3 * (m0 + i) - kC0 + 2 < NLD ? 3 * (m0 + i) - kC0 : NLD - 3;
+                  const float2 xv = xs_tab[slot * MT + m0 + i];  // (sum of X, 2^-p)
+                  const float d0 = small_int_to_float(dv[j][c]);
+                  const float d1 = small_int_to_float(dv[j][c + 1]);
+                  const float d2 = small_int_to_float(dv[j][c + 2]);
                   const float dot = fmaf(d2, 65536.f, fmaf(d1, 256.f, d0));
-                  fin[m] = fmaf(s * xv.y, fmaf(-z, xv.x, dot), fin[m]);
+                  fin[i] = fmaf(s * xv.y, fmaf(-z, xv.x, dot), fin[i]);
                 }
             }
           }
@@ -759,12 +776,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
           const int which = (u0 / G == tile) ? 0 : 1;
           float* slotp = p.partial + (static_cast<size_t>(blockIdx.x) * 2 + which) * SLOT;
 #pragma unroll
-          for (int m = 0; m < MT; ++m)
-            if (m < M) slotp[m * kTileRows + r] = fin[m];
+          for (int i = 0; i < TM; ++i)
+            if (m0 + i < M) slotp[(m0 + i) * kTileRows + r] = fin[i];
           __syncwarp();
           if (lane == 0) {
             __threadfence();  // release: this warp's partial rows (ordered by the __syncwarp) before the ticket
-            const unsigned old = atomicAdd(p.counters + tile * CW + warp, 1u);
+            const unsigned old = atomicAdd(tickets + tile * CW + q, 1u);
             if (sp_n == 0) {
               sp_tile0 = tile; sp_cf0 = c_first; sp_cl0 = c_last; sp_old0 = old;
             } else {
@@ -774,7 +791,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
           }
         }
 #pragma unroll
-        for (int m = 0; m < MT; ++m) fin[m] = 0.f;
+        for (int i = 0; i < TM; ++i) fin[i] = 0.f;
       }
     }
     if (tid == 0) TL(5);
@@ -788,20 +805,20 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
         const unsigned old = __shfl_sync(0xffffffffu, i ? sp_old1 : sp_old0, 0);
         if (old != static_cast<unsigned>(c_last - c_first)) continue;  // another warp finishes these rows
         if (lane == 0) {
-          p.counters[tile * CW + warp] = 0;  // every contributor has arrived: leave it clean
+          tickets[tile * CW + q] = 0;  // every contributor has arrived: leave it clean
           __threadfence();                   // acquire side for the reads below
         }
         __syncwarp();
-        float v[MT];
+        float v[TM];
 #pragma unroll
-        for (int m = 0; m < MT; ++m) v[m] = 0.f;
+        for (int i = 0; i < TM; ++i) v[i] = 0.f;
         for (int cc = c_first; cc <= c_last; ++cc) {  // fixed order: bitwise reproducible
           const int cu0 = static_cast<int>(static_cast<long long>(U) * cc / gridDim.x);
           const int wc = (cu0 / G == tile) ? 0 : 1;
           const float* sl = p.partial + (static_cast<size_t>(cc) * 2 + wc) * SLOT;
 #pragma unroll
-          for (int m = 0; m < MT; ++m)
-            if (m < M) v[m] += __ldcg(sl + m * kTileRows + r);
+          for (int i = 0; i < TM; ++i)
+            if (m0 + i < M) v[i] += __ldcg(sl + (m0 + i) * kTileRows + r);
         }
         finalize(tile, v);
       }
@@ -809,46 +826,47 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
 
     if (p.argmax) {
       // ---- fused argmax: thread -> warp -> CTA -> grid, larger value then lower index ----
+      const int nfix = 32 * CW * ((M + TM - 1) / TM);  // threads of all active fix-up warps
 #pragma unroll
-      for (int m = 0; m < MT; ++m)
+      for (int i = 0; i < TM; ++i)
 #pragma unroll
         for (int off = 1; off < 32; off <<= 1) {
-          const float ov = __shfl_xor_sync(0xffffffffu, best_v[m], off);
-          const int oi = __shfl_xor_sync(0xffffffffu, best_i[m], off);
-          if (better(ov, oi, best_v[m], best_i[m])) {
-            best_v[m] = ov;
-            best_i[m] = oi;
+          const float ov = __shfl_xor_sync(0xffffffffu, best_v[i], off);
+          const int oi = __shfl_xor_sync(0xffffffffu, best_i[i], off);
+          if (better(ov, oi, best_v[i], best_i[i])) {
+            best_v[i] = ov;
+            best_i[i] = oi;
           }
         }
-      named_bar_sync(kFixBar, NFT);
+      named_bar_sync(kFixBar, nfix);
       // per-warp candidates go through the (now idle) side ring: every unit has been read
-      Pair* cand = reinterpret_cast<Pair*>(side);  // [CW][16]
+      Pair* cand = reinterpret_cast<Pair*>(side);  // [fix-up warp][16 tokens]
       if (lane == 0) {
 #pragma unroll
-        for (int m = 0; m < MT; ++m) cand[warp * 16 + m] = Pair{best_v[m], best_i[m]};
+        for (int i = 0; i < TM; ++i) cand[fslot * 16 + m0 + i] = Pair{best_v[i], best_i[i]};
       }
-      named_bar_sync(kFixBar, NFT);
+      named_bar_sync(kFixBar, nfix);
       Pair* cta_pairs = static_cast<Pair*>(p.cta_pairs);
       if (tid < M) {
         Pair b{-FLT_MAX, INT_MAX};
         for (int w = 0; w < CW; ++w) {
-          const Pair qv = cand[w * 16 + tid];
+          const Pair qv = cand[((tid / TM) * CW + w) * 16 + tid];  // the set that owns token `tid`, its four quarters
           if (better(qv.v, qv.i, b.v, b.i)) b = qv;
         }
         cta_pairs[blockIdx.x * 16 + tid] = b;
       }
-      named_bar_sync(kFixBar, NFT);
+      named_bar_sync(kFixBar, nfix);
       if (tid == 0) {
         __threadfence();
-        const unsigned old = atomicAdd(p.counters + p.tiles * CW, 1u);
+        const unsigned old = atomicAdd(p.counters + 3 * p.tiles * CW, 1u);
         const int last = (old == gridDim.x - 1);
         if (last) {
-          p.counters[p.tiles * CW] = 0;
+          p.counters[3 * p.tiles * CW] = 0;
           __threadfence();
         }
         *sflag = last;
       }
-      named_bar_sync(kFixBar, NFT);
+      named_bar_sync(kFixBar, nfix);
       if (*sflag && tid < M) {
         Pair b{-FLT_MAX, INT_MAX};
         for (unsigned cc = 0; cc < gridDim.x; ++cc) {
@@ -862,6 +880,15 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
         if (p.pairs_out)
           static_cast<Pair*>(p.pairs_out)[tid] = Pair{b.v, (b.i == INT_MAX) ? INT_MAX : b.i + p.row_offset};
       }
+    }
+    };
+    const int fset = warp < CW ? 0 : (warp - kWConv0) / CW + 1;
+    if (fset == 0) fixup(std::integral_constant<int, 0>{});
+    if constexpr (GE::FW >= 2) {
+      if (fset == 1 && GE::TM < M) fixup(std::integral_constant<int, 1>{});
+    }
+    if constexpr (GE::FW >= 3) {
+      if (fset == 2 && 2 * GE::TM < M) fixup(std::integral_constant<int, 2>{});
     }
   }
 
@@ -1060,7 +1087,8 @@ int w4a16_scratch_alloc(w4a16_scratch_t* s, int max_in, int max_out, int min_gro
   s->max_splits = di->sms * kMaxCtasPerSm;  // CTAs of the persistent grid
   // two partial tiles per CTA (head and tail of its unit range), widest tile, 16 tokens
   s->partial_elems = static_cast<size_t>(s->max_splits) * 2 * kTileRows * 16;
-  const size_t counters = ((static_cast<size_t>(max_out) / kTileRows + 2) * CW + 8) * sizeof(unsigned);
+  // arrival tickets per (token set, tile, lane quarter) + the argmax ticket
+  const size_t counters = (3 * (static_cast<size_t>(max_out) / kTileRows + 2) * CW + 8) * sizeof(unsigned);
   const size_t pairs = static_cast<size_t>(s->max_splits) * 16 * sizeof(Pair);
   void *xf = nullptr, *cn = nullptr, *pa = nullptr;
   cudaError_t e = cudaMalloc(&xf, pairs);
