@@ -671,9 +671,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
       }
     };
 
-    // (tile, first/last contributing CTA, arrival ticket) of up to two split tiles, in lane 0
-    int sp_n = 0, sp_tile0 = 0, sp_cf0 = 0, sp_cl0 = 0, sp_tile1 = 0, sp_cf1 = 0, sp_cl1 = 0;
-    unsigned sp_old0 = 0, sp_old1 = 0;
 
     bool ok = team_ok;
     constexpr int GB = GE::GB;
@@ -779,15 +776,32 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
           for (int i = 0; i < TM; ++i)
             if (m0 + i < M) slotp[(m0 + i) * kTileRows + r] = fin[i];
           __syncwarp();
+          unsigned old = 0;
           if (lane == 0) {
             __threadfence();  // release: this warp's partial rows (ordered by the __syncwarp) before the ticket
-            const unsigned old = atomicAdd(tickets + tile * CW + q, 1u);
-            if (sp_n == 0) {
-              sp_tile0 = tile; sp_cf0 = c_first; sp_cl0 = c_last; sp_old0 = old;
-            } else {
-              sp_tile1 = tile; sp_cf1 = c_first; sp_cl1 = c_last; sp_old1 = old;
+            old = atomicAdd(tickets + tile * CW + q, 1u);
+          }
+          old = __shfl_sync(0xffffffffu, old, 0);
+          if (old == static_cast<unsigned>(c_last - c_first)) {
+            // The last ticket for these rows: every other piece is already in memory, so this warp adds
+            // them up right away (the D ring is deep enough to absorb the pause), in a fixed order.
+            if (lane == 0) {
+              tickets[tile * CW + q] = 0;  // leave it clean for the next launch
+              __threadfence();             // acquire side for the reads below
             }
-            ++sp_n;
+            __syncwarp();
+            float v[TM];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) v[i] = 0.f;
+            for (int cc = c_first; cc <= c_last; ++cc) {  // fixed order: bitwise reproducible
+              const int cu0 = static_cast<int>(static_cast<long long>(U) * cc / gridDim.x);
+              const int wc = (cu0 / G == tile) ? 0 : 1;
+              const float* sl = p.partial + (static_cast<size_t>(cc) * 2 + wc) * SLOT;
+#pragma unroll
+              for (int i = 0; i < TM; ++i)
+                if (m0 + i < M) v[i] += __ldcg(sl + (m0 + i) * kTileRows + r);
+            }
+            finalize(tile, v);
           }
         }
 #pragma unroll
@@ -795,35 +809,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
       }
     }
     if (tid == 0) TL(5);
-    // ---- split tiles: the warp that drew the last ticket for its rows adds the pieces up ----
-    if (ok) {
-      const int ns = __shfl_sync(0xffffffffu, sp_n, 0);
-      for (int i = 0; i < ns; ++i) {
-        const int tile = __shfl_sync(0xffffffffu, i ? sp_tile1 : sp_tile0, 0);
-        const int c_first = __shfl_sync(0xffffffffu, i ? sp_cf1 : sp_cf0, 0);
-        const int c_last = __shfl_sync(0xffffffffu, i ? sp_cl1 : sp_cl0, 0);
-        const unsigned old = __shfl_sync(0xffffffffu, i ? sp_old1 : sp_old0, 0);
-        if (old != static_cast<unsigned>(c_last - c_first)) continue;  // another warp finishes these rows
-        if (lane == 0) {
-          tickets[tile * CW + q] = 0;  // every contributor has arrived: leave it clean
-          __threadfence();                   // acquire side for the reads below
-        }
-        __syncwarp();
-        float v[TM];
-#pragma unroll
-        for (int i = 0; i < TM; ++i) v[i] = 0.f;
-        for (int cc = c_first; cc <= c_last; ++cc) {  // fixed order: bitwise reproducible
-          const int cu0 = static_cast<int>(static_cast<long long>(U) * cc / gridDim.x);
-          const int wc = (cu0 / G == tile) ? 0 : 1;
-          const float* sl = p.partial + (static_cast<size_t>(cc) * 2 + wc) * SLOT;
-#pragma unroll
-          for (int i = 0; i < TM; ++i)
-            if (m0 + i < M) v[i] += __ldcg(sl + (m0 + i) * kTileRows + r);
-        }
-        finalize(tile, v);
-      }
-    }
-
     if (p.argmax) {
       // ---- fused argmax: thread -> warp -> CTA -> grid, larger value then lower index ----
       const int nfix = 32 * CW * ((M + TM - 1) / TM);  // threads of all active fix-up warps
