@@ -251,6 +251,14 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* d) {
       : "r"(taddr)
       : "memory");
 }
+// Ticket counter with release + acquire in one operation: the partial rows written before it (by the whole
+// warp, ordered by __syncwarp) are visible to whoever draws a later ticket, and whoever draws the last one
+// sees every earlier contributor's rows. Saves the two full memory fences of the fence-atomic-fence form.
+__device__ __forceinline__ unsigned ticket_acq_rel(unsigned* addr) {
+  unsigned old;
+  asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(addr) : "memory");
+  return old;
+}
 // exact int -> float for |v| < 2^22 without the conversion pipe
 __device__ __forceinline__ float small_int_to_float(uint32_t v) {
   return __uint_as_float(0x4B400000u + v) - 12582912.0f;
@@ -777,18 +785,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
             if (m0 + i < M) slotp[(m0 + i) * kTileRows + r] = fin[i];
           __syncwarp();
           unsigned old = 0;
-          if (lane == 0) {
-            __threadfence();  // release: this warp's partial rows (ordered by the __syncwarp) before the ticket
-            old = atomicAdd(tickets + tile * CW + q, 1u);
-          }
+          if (lane == 0) old = ticket_acq_rel(tickets + tile * CW + q);
           old = __shfl_sync(0xffffffffu, old, 0);
           if (old == static_cast<unsigned>(c_last - c_first)) {
             // The last ticket for these rows: every other piece is already in memory, so this warp adds
             // them up right away (the D ring is deep enough to absorb the pause), in a fixed order.
-            if (lane == 0) {
-              tickets[tile * CW + q] = 0;  // leave it clean for the next launch
-              __threadfence();             // acquire side for the reads below
-            }
+            if (lane == 0) tickets[tile * CW + q] = 0;  // leave it clean for the next launch
             __syncwarp();
             float v[TM];
 #pragma unroll
