@@ -38,12 +38,12 @@ struct W4A16Weights {
 
 struct GemvScratch {
   float* xf      = nullptr;   // per-CTA (max, index) pairs of the fused argmax
-  float* xgsum   = nullptr;   // split-tile arrival counters (kept zero between calls)
+  float* xgsum   = nullptr;   // split-tile arrival tickets (zero between calls)
   float* partial = nullptr;   // split-K partial tiles
   int    max_in = 0, max_groups = 0, max_out = 0, max_splits = 0, max_m = 1;
   size_t partial_elems = 0;
   size_t bytes() const {
-    return size_t(max_splits) * 16 * 8 + (size_t(max_out) / 128 + 2) * 16 + 32 + partial_elems * 4;
+    return size_t(max_splits) * 16 * 8 + (size_t(max_out) / 128 + 2) * 48 + 32 + partial_elems * 4;
   }
 };
 
