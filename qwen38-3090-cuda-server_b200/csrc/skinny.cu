@@ -7,11 +7,9 @@
 // for lm_head, the separate argmax kernels (src/kernels/elementwise.cu:96-194).
 //
 // Shape of the computation (HBM-bound: every weight byte is read exactly once):
-//   * persistent grid, one CTA per SM, small enough (shared memory, registers, 256 of the 512
-//     tensor-memory columns) that the NEXT launch's CTA fits beside it: with programmatic
-//     dependent launch the next layer's weights are already streaming while this layer drains.
-//     The (128-row tile, k group) units of the matrix are dealt out as equal contiguous ranges,
-//     so every CTA streams the same number of bytes whatever N and K are. A row tile whose K
+//   * persistent grid, one CTA per SM (24 warps, all 512 tensor-memory columns, about 160 KB of shared
+//     memory). The (128-row tile, k group) units of the matrix are dealt out as equal contiguous
+//     ranges, so every CTA streams the same number of bytes whatever N and K are. A row tile whose K
 //     range is shared by several CTAs is finished by the last warp to arrive for its rows, which
 //     adds the partial tiles in a fixed order (bitwise reproducible, no float atomics). Shared
 //     tiles are processed FIRST, so that reduction overlaps everybody's main loop.
@@ -27,17 +25,20 @@
 //       - per group:  y += s * 2^-p * ((D0 + 2^8 D1 + 2^16 D2) - zp * sum(X)),  Dj = sum(q * digit_j),
 //         with the integer dot products exact and only this last step in fp32.
 //     This keeps the per-byte instruction count low enough for the ALU pipe (LOP3/SHF issue at
-//     half rate on this part) to keep up with HBM, which the bf16 formulation could not.
-//   * warp roles, all decoupled by mbarrier rings so that no role waits for a round trip:
-//       producer   1 thread  streams this CTA's share of the weight stream with 1-D bulk async
-//                            copies (8576-byte blocks) into a shared-memory ring, and runs an L2
-//                            prefetch a few blocks further ahead
-//       unpack     8 warps   nibbles -> int8 -> tensor memory (two warps per TMEM lane quarter,
-//                            alternating units), and the row's (scale, zero point) into a side ring
-//       activation 1 warp    bf16 x -> digit rows of the B operand in shared memory
-//       mma        1 thread  four tcgen05.mma per unit, tcgen05.commit to release A/B and publish D
-//       fix-up     4 warps   tcgen05.ld of the unit's int32 sums, the fp32 step above, the
-//                            split-tile reduction, output / fused argmax
+//     half rate on this part) to keep up with HBM, which the bf16 formulations could not.
+//   * every hand-off moves a STEP of two k groups; the roles are decoupled by mbarrier rings so that
+//     none waits for a round trip:
+//       producer    1 thread   one 17 KB bulk async copy per step into a shared-memory ring and the
+//                              step's table entry; it never waits for the previous kernel
+//       unpack      8 warps    nibbles -> int8 -> tensor memory (two warps per TMEM lane quarter,
+//                              alternating steps), and the row's (scale, zero point) into a side ring
+//       issuers     2 warps    even / odd steps: eight tcgen05.mma and one tcgen05.commit per step
+//       fix-up      4 warps    tcgen05.ld of the int32 sums, the fp32 step above, the split-tile
+//                  (+4)        reduction, output / fused argmax; for M >= 3 a second warp per lane
+//                              quarter takes half of the tokens
+//       converters  9 warps    after griddepcontrol.wait: bf16 x -> digit rows of the B operand, once per
+//                  (+fix-up)   CTA, for exactly the k groups it multiplies; issuers start on a group as
+//                              soon as its rows are in
 #include <cfloat>
 #include <climits>
 #include <cstdlib>
