@@ -776,9 +776,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
           finalize(tile, fin);
         } else {
           // split tile: this warp publishes its 32 rows and moves on; no CTA-wide barrier
-          const long long X0 = static_cast<long long>(tile) * G;
-          const int c_first = static_cast<int>(((X0 + 1) * gridDim.x - 1) / U);
-          const int c_last = static_cast<int>(((X0 + G) * gridDim.x - 1) / U);
+          // first and last CTA whose unit range touches this tile (32-bit: U * gridDim.x < 2^32, host-checked)
+          const uint32_t X0 = static_cast<uint32_t>(tile) * G, Uu = static_cast<uint32_t>(U);
+          const int c_first = static_cast<int>(((X0 + 1) * gridDim.x - 1) / Uu);
+          const int c_last = static_cast<int>(((X0 + G) * gridDim.x - 1) / Uu);
           const int which = (u0 / G == tile) ? 0 : 1;
           float* slotp = p.partial + (static_cast<size_t>(blockIdx.x) * 2 + which) * SLOT;
 #pragma unroll
@@ -796,13 +797,28 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
             float v[TM];
 #pragma unroll
             for (int i = 0; i < TM; ++i) v[i] = 0.f;
-            for (int cc = c_first; cc <= c_last; ++cc) {  // fixed order: bitwise reproducible
-              const int cu0 = static_cast<int>(static_cast<long long>(U) * cc / gridDim.x);
-              const int wc = (cu0 / G == tile) ? 0 : 1;
-              const float* sl = p.partial + (static_cast<size_t>(cc) * 2 + wc) * SLOT;
+            // four pieces' loads in flight at a time, added in CTA order: bitwise reproducible
+            for (int cb = c_first; cb <= c_last; cb += 4) {
+              float piece[4][TM];
 #pragma unroll
-              for (int i = 0; i < TM; ++i)
-                if (m0 + i < M) v[i] += __ldcg(sl + (m0 + i) * kTileRows + r);
+              for (int k = 0; k < 4; ++k) {
+                const int cc = cb + k;
+                if (cc <= c_last) {
+                  const int cu0 = static_cast<int>(Uu * static_cast<uint32_t>(cc) / gridDim.x);
+                  const int wc = (cu0 / G == tile) ? 0 : 1;
+                  const float* sl = p.partial + (static_cast<size_t>(cc) * 2 + wc) * SLOT;
+#pragma unroll
+                  for (int i = 0; i < TM; ++i)
+                    if (m0 + i < M) piece[k][i] = __ldcg(sl + (m0 + i) * kTileRows + r);
+                }
+              }
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                if (cb + k <= c_last) {
+#pragma unroll
+                  for (int i = 0; i < TM; ++i)
+                    if (m0 + i < M) v[i] += piece[k][i];
+                }
             }
             finalize(tile, v);
           }
