@@ -110,6 +110,7 @@ struct SkinnyParams {
   int M, N, K, G, tiles;
   int b_bytes;       // bytes of the B region (digit rows of the groups this CTA multiplies)
   int xs_bytes;      // bytes of the (sum, 2^-p) region
+  unsigned long long mg_grid, mg_G;  // ceil(2^40 / d) for d = gridDim.x and G: exact division by multiply
   int trace_id;      // launch counter (development trace only)
   uint32_t hint;     // suspend-time hint of the mbarrier waits, ns
   int depth;         // weight ring stages
@@ -149,10 +150,10 @@ struct SegIter {
   bool single, head_partial, tail_partial;
   int phase, t;
 
-  __device__ void init(int u0, int u1, int G_) {
+  __device__ void init(int u0, int u1, int G_, unsigned long long mg_G) {
     G = G_;
-    t_first = u0 / G;
-    t_last = (u1 - 1) / G;
+    t_first = static_cast<int>(static_cast<uint32_t>((static_cast<unsigned long long>(u0) * mg_G) >> 40));
+    t_last = static_cast<int>(static_cast<uint32_t>((static_cast<unsigned long long>(u1 - 1) * mg_G) >> 40));
     head_g0 = u0 - t_first * G;
     tail_g1 = u1 - t_last * G;
     single = (t_first == t_last);
@@ -260,6 +261,11 @@ __device__ __forceinline__ unsigned ticket_acq_rel(unsigned* addr) {
   asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(addr) : "memory");
   return old;
 }
+// u / d for u * d < 2^40, with m = ceil(2^40 / d) from the host: a multiply and a shift instead of the
+// division loop (three of them sat in the start-up path of every launch).
+__device__ __forceinline__ uint32_t fdiv(uint32_t u, unsigned long long m) {
+  return static_cast<uint32_t>((static_cast<unsigned long long>(u) * m) >> 40);
+}
 // exact int -> float for |v| < 2^22 without the conversion pipe
 __device__ __forceinline__ float small_int_to_float(uint32_t v) {
   return __uint_as_float(0x4B400000u + v) - 12582912.0f;
@@ -346,16 +352,16 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   const int U = p.tiles * G;
   if (tid == 0) TL(0);
   // (U * gridDim.x fits 32 bits: checked on the host; a 64-bit division here costs a visible part of the start-up)
-  const int u0 = static_cast<int>(static_cast<uint32_t>(U) * blockIdx.x / gridDim.x);
-  const int u1 = static_cast<int>(static_cast<uint32_t>(U) * (blockIdx.x + 1) / gridDim.x);
+  const int u0 = static_cast<int>(fdiv(static_cast<uint32_t>(U) * blockIdx.x, p.mg_grid));
+  const int u1 = static_cast<int>(fdiv(static_cast<uint32_t>(U) * (blockIdx.x + 1), p.mg_grid));
   // the digit rows of the groups this CTA multiplies, (g_first + j) % G for j < min(G, u1 - u0), live in slot j
-  const int g_first = u0 % G;
+  const int g_first = u0 - static_cast<int>(fdiv(static_cast<uint32_t>(u0), p.mg_G)) * G;
   auto cache_slot = [&](int g) { return g - g_first + (g < g_first ? G : 0); };
   const int b_slot = 384 * M, b_lbo = 48 * M;
   int T;  // steps of this CTA
   {
     SegIter si;
-    si.init(u0, u1, G);
+    si.init(u0, u1, G, p.mg_G);
     T = si.steps();
   }
 
@@ -466,7 +472,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
     // kernel: weights never depend on it.
     if (lane == 0) {
       SegIter it;
-      it.init(u0, u1, G);
+      it.init(u0, u1, G, p.mg_G);
       Seg sg;
       int st = 0, t = 0;
       uint32_t ph = 1;  // a fresh "empty" barrier reads as already released
@@ -780,7 +786,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
           const uint32_t X0 = static_cast<uint32_t>(tile) * G, Uu = static_cast<uint32_t>(U);
           const int c_first = static_cast<int>(((X0 + 1) * gridDim.x - 1) / Uu);
           const int c_last = static_cast<int>(((X0 + G) * gridDim.x - 1) / Uu);
-          const int which = (u0 / G == tile) ? 0 : 1;
+          const int which = (static_cast<int>(fdiv(static_cast<uint32_t>(u0), p.mg_G)) == tile) ? 0 : 1;
           float* slotp = p.partial + (static_cast<size_t>(blockIdx.x) * 2 + which) * SLOT;
 #pragma unroll
           for (int i = 0; i < TM; ++i)
@@ -804,8 +810,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
               for (int k = 0; k < 4; ++k) {
                 const int cc = cb + k;
                 if (cc <= c_last) {
-                  const int cu0 = static_cast<int>(Uu * static_cast<uint32_t>(cc) / gridDim.x);
-                  const int wc = (cu0 / G == tile) ? 0 : 1;
+                  const uint32_t cu0 = fdiv(Uu * static_cast<uint32_t>(cc), p.mg_grid);
+                  const int wc = (static_cast<int>(fdiv(cu0, p.mg_G)) == tile) ? 0 : 1;
                   const float* sl = p.partial + (static_cast<size_t>(cc) * 2 + wc) * SLOT;
 #pragma unroll
                   for (int i = 0; i < TM; ++i)
@@ -1026,7 +1032,10 @@ int launch_skinny(SkinnyParams& p, const w4a16_weights_t* w, const uint16_t* x, 
   p.status = di->status;
   p.hint = static_cast<uint32_t>(config().hint);
   const int grid = grid_for_shape(w->out_f, w->num_groups, di->sms);
-  W4_REQUIRE(static_cast<long long>(p.tiles) * p.G * grid < (1LL << 32), "out_f x in_f too large for the decode kernel");
+  W4_REQUIRE(static_cast<long long>(p.tiles) * p.G * (grid + 1) < (1LL << 32), "out_f x in_f too large for the decode kernel");
+  auto magic = [](long long d) { return static_cast<unsigned long long>(((1LL << 40) + d - 1) / d); };
+  p.mg_grid = magic(grid);
+  p.mg_G = magic(p.G);
   if (int rc = w4a16_scratch_check(s, w->out_f, M)) return rc;
   const int mb = max_batch(cache_groups_for(p.tiles, p.G, grid), di->smem_optin);
   if (mb < 1)
