@@ -422,7 +422,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
       for (int j = 0; j < kBatch; ++j) {
         const int i = i0 + j * kTeam;
         if (i < total) {
-          const int gj = i / M, m = i - gj * M;
+          const int gj = MT == 1 ? i : i / M, m = i - gj * M;  // (no division on the M = 1 path)
           int g = g_first + gj;
           if (g >= G) g -= G;
           rv[j] = __ldcg(reinterpret_cast<const uint2*>(p.x + static_cast<size_t>(m) * p.K + g * kGroup) + lane);
@@ -432,7 +432,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
       for (int j = 0; j < kBatch; ++j) {
         const int i = i0 + j * kTeam;
         if (i < total) {
-          const int gj = i / M, m = i - gj * M;
+          const int gj = MT == 1 ? i : i / M, m = i - gj * M;
           convert_group(rv[j], bq + gj * b_slot, b_lbo, m, reinterpret_cast<float2*>(xsinv) + gj * MT + m, lane);
           // publish the item: B was written through the generic proxy, the tensor core reads it through the
           // async one; the slot counts as ready once all M tokens are in. Slots are numbered in the order the
