@@ -164,7 +164,14 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     shapes = synth.decode_pass_shapes()
-    sharded = {"gate_up", "down"} if world > 1 else set()
+    # With more than one GPU every linear layer is column-sharded (all BASELINE widths are multiples of
+    # 16 x 8); W4A16_BENCH_SHARD=mlp shards only the two MLP layers and keeps the rest as replicas.
+    if world == 1:
+        sharded = set()
+    elif os.environ.get("W4A16_BENCH_SHARD", "all") == "mlp":
+        sharded = {"gate_up", "down"}
+    else:
+        sharded = {"gate_up", "down", "gdn_in", "gdn_out", "attn_qkv", "attn_o"}
     gen = torch.Generator(device="cuda")
 
     # ---- build the 256 weight containers (distinct buffers: 12.6 GB at N=1) ----
@@ -338,8 +345,8 @@ def run_ours(args):
                        "cache": "inputs larger than L2 (12.6 GB of distinct weights per step)",
                        "launch": "cuda_graph" if graphed else "eager",
                        "parallelism": "single" if world == 1 else
-                       (f"mlp_column_shard_x{world}+fused_peer_store_all_gather" if comm == "fused"
-                        else f"mlp_column_shard_x{world}+nccl_all_gather")},
+                       (f"column_shard_x{world}({len(sharded)}_of_6_layer_kinds)+fused_peer_store_all_gather"
+                        if comm == "fused" else f"column_shard_x{world}+nccl_all_gather")},
             "us_per_weight_pass": ms_step * 1e3,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": traffic, "peak_source": which,
