@@ -328,10 +328,10 @@ def run_ours(args):
         per_launch_bytes = alg_local / n_launch  # roofline of one GPU's kernel: that GPU's bytes
         per_launch_s = ms_step * 1e-3 / n_launch
         achieved = per_launch_bytes / per_launch_s / 1e9
-        # DRAM bytes per launch of the dominant kernel: ncu measured 97.79 MB (read + write) for the
+        # DRAM bytes per launch of the dominant kernel: ncu measured 97.39 MB (read + write) for the
         # 93.68 MB (algorithmic) launch on out 34816 x in 5120 (ncu summary under profiles/);
         # the weight stream is read exactly once for every shape, so traffic scales with the bytes.
-        traffic = per_launch_bytes * (97.79 / 93.68)
+        traffic = per_launch_bytes * (97.39 / 93.68)
         cpu = None
         if world == 1 and not args.no_cpu:
             tb, dt, desc, threads = cpu_sample(n_layers=2, repeats=3)
