@@ -93,7 +93,9 @@ struct Geo {
   static constexpr int kDColsS = kStepGroups * N;        // D columns per step
   static constexpr int kDCol0 = AD2 * kAColsS;           // first D column
   static constexpr int GB = MT == 1 ? 4 : (MT == 2 ? 2 : 1);  // groups whose tensor-memory loads are in flight together
-  static constexpr int FW = MT <= 2 ? 1 : 2;  // fix-up warps per lane quarter: they split the tokens (three were slower)
+  // fix-up warps per lane quarter: two token sets for M >= 3 (three were slower). The launcher picks MT so
+  // that the sets are balanced: TM = ceil(M / 2).
+  static constexpr int FW = MT <= 2 ? 1 : 2;
   static constexpr int TM = (MT + FW - 1) / FW;               // tokens per fix-up warp
   static_assert(kDCol0 + DD2 * kDColsS <= kTmemCols, "tensor memory budget");
   static_assert(AD2 <= DD2 && 2 <= DD2 / 2, "ring depths");
@@ -1059,8 +1061,11 @@ int launch_skinny(SkinnyParams& p, const w4a16_weights_t* w, const uint16_t* x, 
     int rc;
     if (q.M == 1) rc = launch_cfg<1>(q, grid, st, di->smem_optin);
     else if (q.M == 2) rc = launch_cfg<2>(q, grid, st, di->smem_optin);
-    else if (q.M <= 5) rc = launch_cfg<5>(q, grid, st, di->smem_optin);
-    else rc = launch_cfg<10>(q, grid, st, di->smem_optin);
+    else if (q.M <= 4) rc = launch_cfg<4>(q, grid, st, di->smem_optin);   // token sets (2, M - 2)
+    else if (q.M == 5) rc = launch_cfg<5>(q, grid, st, di->smem_optin);   // (3, 2)
+    else if (q.M == 6) rc = launch_cfg<6>(q, grid, st, di->smem_optin);   // (3, 3)
+    else if (q.M <= 8) rc = launch_cfg<8>(q, grid, st, di->smem_optin);   // (4, M - 4)
+    else rc = launch_cfg<10>(q, grid, st, di->smem_optin);                // (5, M - 5)
     if (rc) return rc;
     m0 = m1;
   }
