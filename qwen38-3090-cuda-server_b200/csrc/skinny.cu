@@ -95,7 +95,7 @@ struct Geo {
   static constexpr int GB = MT == 1 ? 4 : (MT == 2 ? 2 : 1);  // groups whose tensor-memory loads are in flight together
   // fix-up warps per lane quarter: two token sets for M >= 3 (three were slower). The launcher picks MT so
   // that the sets are balanced: TM = ceil(M / 2).
-  static constexpr int FW = MT <= 2 ? 1 : 2;
+  static constexpr int FW = MT <= 1 ? 1 : 2;
   static constexpr int TM = (MT + FW - 1) / FW;               // tokens per fix-up warp
   static_assert(kDCol0 + DD2 * kDColsS <= kTmemCols, "tensor memory budget");
   static_assert(AD2 <= DD2 && 2 <= DD2 / 2, "ring depths");
