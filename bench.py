@@ -1,23 +1,29 @@
 #!/usr/bin/env python3
-"""Benchmark of the W4A16 decode weight pass on B200.
+"""Benchmark of the W4A16 matmul path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-A "step" is one full decode token's weight pass: the 256 W4A16 GEMVs (M=1) of the
-64-layer model, each on its own weight buffer (12.6 GB of packed int4 weights in
-total, far larger than L2, so every step streams from HBM). Inputs are seeded
-synthetic tensors with the checkpoint's shapes and the value distributions the
-benchmark configuration states; the real checkpoint is not available here.
+The headline "step" is one full decode token's weight pass: the 256 W4A16 GEMVs (M=1) of the
+64-layer model, each on its own weight buffer (12.6 GB of packed int4 weights in total, far
+larger than L2, so every step streams from HBM), replayed as one CUDA graph. Inputs are seeded
+synthetic tensors with the checkpoint's shapes and the value distributions the benchmark
+configuration states; the real checkpoint is not available here.
 
-Prints ONE JSON line (rank 0). `value` is algorithmic TB/s over the whole job with
-everything resident in HBM; `e2e` is the same metric through the public C-ABI
-launchers with the step's activations copied from pinned host memory and the result
-copied back inside the timed region. `roofline` compares the GEMV kernel with the
-measured HBM copy bandwidth; `cpu_baseline` times the CPU oracle on a bounded sample.
+Prints ONE JSON line (rank 0). `value` is algorithmic TB/s over the whole job with everything
+resident in HBM (median of several timed regions of exactly --steps steps; the spread is in
+`regions_ms_per_step`); `e2e` is the same metric through the public C-ABI launchers with the
+step's activations copied from pinned host memory and the result copied back inside the timed
+region. `roofline` compares the GEMV kernel with the measured HBM copy bandwidth; `cpu_baseline`
+times the CPU oracle on a bounded sample. `configs` carries the other benchmark configurations,
+measured in the same run: the single GEMV (config 0), the 64-layer verify pass at M=9 and M=16
+(config 2), the lm_head with fused argmax in int4 and int8 (config 3) and the prefill GEMM
+(config 4).
 
-With --gpus N > 1 (launched under torchrun) the gate/up and down projections are
-column-sharded over the ranks and their outputs all-gathered (NCCL); the other layers
-are replicated. The job is still one decode pass, so scaling is "strong".
+With --gpus N > 1 (launched under torchrun, one rank per GPU) the layers are column-sharded over
+the ranks; every sharded kernel stores its slice of the output straight into every rank's copy
+over NVLink peer mappings and then raises a per-rank flag; the next layer's kernel waits for all
+ranks' flags before it reads activations, so the timed pass carries one cross-rank
+synchronisation per layer. The job is still one decode pass, so scaling is "strong".
 """
 from __future__ import annotations
 
@@ -38,6 +44,9 @@ PKG = "qwen38-3090-cuda-server_b200"
 METRIC = "w4a16_gemv_hbm_tbps_full_decode_weight_pass"
 UNIT = "TB/s"
 FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
+WORKLOAD = "decode_weight_pass_256_gemv_M1"
+REGIONS = 5            # timed regions of --steps steps each; the median is reported
 
 
 def measured_peaks():
@@ -45,7 +54,15 @@ def measured_peaks():
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
             return json.load(f), "measured"
     except Exception:
-        return {"hbm_gbs": FALLBACK_HBM_GBS}, "fallback"
+        return {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": FALLBACK_BF16_TFLOPS}, "fallback"
+
+
+def base_config(synth):
+    """The `config` object both arms print: the workload the metric is quoted on."""
+    shapes = synth.decode_pass_shapes()
+    return {"workload": WORKLOAD, "layers": 64, "hidden": 5120, "gemvs_per_step": len(shapes),
+            "algorithmic_bytes_per_step": sum(synth.algorithmic_bytes(N, K) for _, N, K in shapes),
+            "cache": "inputs larger than L2 (12.6 GB of distinct weights per step)"}
 
 
 class ClockSampler:
@@ -96,16 +113,23 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------ reference arm
-def cpu_sample(n_layers: int = 2, repeats: int = 1):
-    """Times the CPU oracle (dequant-then-fp32-matmul, all host threads) on the GEMVs of the
-    first `n_layers` layers of the pass. Returns (TB/s, seconds, description, threads)."""
+SAMPLE_LAYERS = 2
+_CPU_CASES = None
+
+
+def cpu_sample(repeats: int = 1):
+    """Times the CPU oracle (dequant-then-fp32-matmul, all host threads) on the GEMVs of the first
+    SAMPLE_LAYERS layers of the pass. Returns (TB/s, seconds per sample, description, threads)."""
     from oracle import oracle
     synth = importlib.import_module(PKG + ".synth")
     oracle.build()
-    shapes = synth.decode_pass_shapes()[: 4 * n_layers]
-    cases = []
-    for i, (_, N, K) in enumerate(shapes):
-        cases.append((synth.make_weights(N, K, seed=i), synth.make_activations(1, K, seed=i), N, K))
+    # every host core, whatever the launcher exported (torchrun sets OMP_NUM_THREADS=1 for its children)
+    oracle.set_num_threads(os.cpu_count() or 1)
+    global _CPU_CASES
+    if _CPU_CASES is None:  # generated once; only the matmuls are timed
+        _CPU_CASES = [(synth.make_weights(N, K, seed=i), synth.make_activations(1, K, seed=i), N, K)
+                      for i, (_, N, K) in enumerate(synth.decode_pass_shapes()[: 4 * SAMPLE_LAYERS])]
+    cases = _CPU_CASES
     nbytes = sum(synth.algorithmic_bytes(N, K) for _, _, N, K in cases)
     oracle.gemm_f32(*cases[0][0], cases[0][1])  # warm the thread pool
     t0 = time.perf_counter()
@@ -113,38 +137,119 @@ def cpu_sample(n_layers: int = 2, repeats: int = 1):
         for (w, x, N, K) in cases:
             oracle.gemm_f32(w[0], w[1], w[2], x)
     dt = (time.perf_counter() - t0) / repeats
-    desc = (f"first {n_layers} of 64 layers ({len(cases)} of 256 GEMVs, {nbytes / 1e6:.0f} MB algorithmic), "
+    desc = (f"first {SAMPLE_LAYERS} of 64 layers ({len(cases)} of 256 GEMVs, {nbytes / 1e6:.0f} MB algorithmic), "
             f"oracle dequant-then-fp32-matmul, {repeats} repeat(s)")
-    return nbytes / dt / 1e12, dt, desc, oracle.num_threads()
+    return nbytes / dt / 1e12, dt, desc, oracle.num_threads(), nbytes
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    # The reference project has no CPU matmul of its own outside two test-embedded check loops, so
-    # its CPU arm is the oracle port of that arithmetic, threaded over output rows.
+    # The reference project has no CPU matmul of its own outside two test-embedded check loops, so its CPU
+    # arm is the oracle port of that arithmetic, threaded over output rows. Each step times a bounded sample
+    # of the pass (the first layers); ms_per_step is scaled to a whole pass by bytes.
+    synth = importlib.import_module(PKG + ".synth")
+    cfg = base_config(synth)
     times = []
-    tb = None
     for i in range(args.warmup + args.steps):
-        tb, dt, desc, threads = cpu_sample(n_layers=2, repeats=1)
+        tb, dt, desc, threads, nbytes = cpu_sample(repeats=1)
         if i >= args.warmup:
             times.append(dt)
-    synth = importlib.import_module(PKG + ".synth")
-    nbytes = sum(synth.algorithmic_bytes(N, K) for _, N, K in synth.decode_pass_shapes()[:8])
     dt = sum(times) / len(times)
     value = nbytes / dt / 1e12
+    pass_ms = dt * 1e3 * cfg["algorithmic_bytes_per_step"] / nbytes
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": pass_ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16 x int4 -> fp32", "data": "synthetic",
-            "config": {"workload": "decode_weight_pass_256_gemv_M1", "sample": desc},
-            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
+            "config": cfg,
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc,
+                             "sample_ms": dt * 1e3},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
 
 # ------------------------------------------------------------------------ our arm
+def make_layer_weights(pkg, torch, gen, n_rows, K, seed):
+    """Seeded on-device tensors in the on-disk layout, repacked into a weight container."""
+    gen.manual_seed(seed)
+    G = K // 128
+    packed = torch.randint(-2 ** 31, 2 ** 31 - 1, (n_rows, K // 8), dtype=torch.int32, device="cuda", generator=gen)
+    scale = (torch.randn((n_rows, G), device="cuda", generator=gen).abs() * 0.02 + 1e-4).to(torch.bfloat16)
+    zp = torch.randint(-2 ** 31, 2 ** 31 - 1, (n_rows // 8, G), dtype=torch.int32, device="cuda", generator=gen)
+    return pkg.awq_repack(packed, scale, zp)
+
+
+def time_regions(torch, stream, step, steps, regions, barrier):
+    """`regions` timed regions of exactly `steps` steps each, CUDA events on the launching stream."""
+    out = []
+    for _ in range(regions):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(stream)
+        for _ in range(steps):
+            step()
+        e1.record(stream)
+        barrier()
+        out.append(e0.elapsed_time(e1) / steps)
+    return out
+
+
+def other_configs(pkg, synth, torch, layers, scratch, stream, peak_hbm, peak_tf, m1_ms):
+    """Configs 0, 2, 3 and 4 of the benchmark on one GPU, after the headline measurement."""
+    import shape_bench
+    out = {}
+
+    def shape(kind, N, K, M, iters):
+        r = shape_bench.run_case(pkg, synth, torch, kind, N, K, M, iters, 768)
+        d = {"us": round(r["us"], 2), "tbps": round(r["tbps"], 3), "frac_of_measured_hbm": round(r["tbps"] * 1e3 / peak_hbm, 3),
+             "algorithmic_bytes": r["algorithmic_bytes"], "ring_copies": r["ring_copies"]}
+        if kind == "prefill":
+            d = {"us": round(r["us"], 1), "tflops": round(r["tflops"], 1), "frac_of_measured_bf16": round(r["tflops"] / peak_tf, 3)}
+        return d
+
+    out["config0_gemv_17408x5120_M1"] = shape("gemv", 17408, 5120, 1, 48)
+    out["config3_lm_head_argmax_int4"] = {f"M{M}": shape("lmhead", 248320, 5120, M, 12) for M in (1, 9)}
+    out["config3_lm_head_argmax_int8"] = {f"M{M}": shape("lmhead8", 248320, 5120, M, 12) for M in (1, 9)}
+
+    # config 2: the 64-layer verify pass (skinny GEMM on every linear layer), same weight buffers as the M=1 pass
+    verify = {}
+    for M in (9, 16):
+        xs = {L["K"]: None for L in layers}
+        for K in xs:
+            xs[K] = torch.randn((M, K), device="cuda").to(torch.bfloat16)
+        ys = {}
+        for L in layers:
+            ys.setdefault(L["N"], torch.empty((M, L["N"]), dtype=torch.bfloat16, device="cuda"))
+
+        def one():
+            for L in layers:
+                pkg.gemm_mma_w4a16(ys[L["N"]], L["w"], xs[L["K"]], M, scratch)
+
+        with torch.cuda.stream(stream):
+            one()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                one()
+            for _ in range(3):
+                g.replay()
+            torch.cuda.synchronize()
+            ms = time_regions(torch, stream, g.replay, 5, 3, torch.cuda.synchronize)
+        med = statistics.median(ms)
+        alg = sum(synth.algorithmic_bytes(L["N"], L["K"], M) for L in layers)
+        verify[f"M{M}"] = {"ms_per_pass": round(med, 4), "x_cost_vs_M1_pass": round(med / m1_ms, 3),
+                           "tbps": round(alg / med / 1e9, 3), "frac_of_measured_hbm": round(alg / med / 1e6 / peak_hbm, 3),
+                           "algorithmic_bytes": alg, "regions_ms": [round(v, 4) for v in ms]}
+        del g, xs, ys
+    out["config2_verify_pass_256_skinny_gemm"] = verify
+
+    out["config4_prefill_M4096"] = {"gate_up_34816x5120": shape("prefill", 34816, 5120, 4096, 6),
+                                    "down_5120x17408": shape("prefill", 5120, 17408, 4096, 6)}
+    return out
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -164,8 +269,8 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     shapes = synth.decode_pass_shapes()
-    # With more than one GPU every linear layer is column-sharded (all BASELINE widths are multiples of
-    # 16 x 8); W4A16_BENCH_SHARD=mlp shards only the two MLP layers and keeps the rest as replicas.
+    # With more than one GPU every linear layer is column-sharded (all widths are multiples of 16 x 8);
+    # W4A16_BENCH_SHARD=mlp shards only the two MLP layers and keeps the rest as replicas.
     if world == 1:
         sharded = set()
     elif os.environ.get("W4A16_BENCH_SHARD", "all") == "mlp":
@@ -182,16 +287,8 @@ def run_ours(args):
         if kind in sharded:
             row0, row1 = pkg.shard_rows(N, world, rank)
             n_local = row1 - row0
-        gen.manual_seed(1000 * i + (rank if kind in sharded else 0))
-        G = K // 128
-        packed = torch.randint(-2 ** 31, 2 ** 31 - 1, (n_local, K // 8), dtype=torch.int32, device="cuda",
-                               generator=gen)
-        scale = (torch.randn((n_local, G), device="cuda", generator=gen).abs() * 0.02 + 1e-4).to(torch.bfloat16)
-        zp = torch.randint(-2 ** 31, 2 ** 31 - 1, (n_local // 8, G), dtype=torch.int32, device="cuda",
-                           generator=gen)
-        w = pkg.awq_repack(packed, scale, zp)
-        layers.append({"kind": kind, "N": N, "K": K, "n_local": n_local, "row0": row0, "w": w})
-        del packed, scale, zp
+        w = make_layer_weights(pkg, torch, gen, n_local, K, 1000 * i + (rank if kind in sharded else 0))
+        layers.append({"kind": kind, "N": N, "K": K, "n_local": n_local, "row0": row0, "w": w, "index": i})
     torch.cuda.synchronize()
 
     scratch = pkg.gemv_scratch_alloc(17408, 34816, 128, 16)
@@ -203,7 +300,6 @@ def run_ours(args):
         y_off.append(yo)
         xo += L["K"]
         yo += L["N"]
-    gen.manual_seed(7)
     x_host = torch.randn(xo, generator=torch.Generator().manual_seed(7)).to(torch.bfloat16).pin_memory()
     x_dev = torch.empty(xo, dtype=torch.bfloat16, device="cuda")
     x_dev.copy_(x_host)
@@ -247,8 +343,7 @@ def run_ours(args):
     with torch.cuda.stream(stream):
         one_pass()  # eager warm-up: one-time function attributes, NCCL channels
         torch.cuda.synchronize()
-        # The pass is replayed as a CUDA graph, as the reference replays its decode step. Only the NCCL baseline
-        # is launched eagerly (a graph of 128 collectives per rank did not replay reliably on this pool).
+        # Only the NCCL baseline is launched eagerly (its collectives are kept out of the graph).
         if comm != "nccl" and os.environ.get("W4A16_BENCH_GRAPH", "1") != "0":
             try:
                 graph = torch.cuda.CUDAGraph()
@@ -277,53 +372,71 @@ def run_ours(args):
         alg_local = sum(synth.algorithmic_bytes(L["n_local"], L["K"]) for L in layers)
         n_launch = len(layers)
 
-        # ---- device-resident timing ----
-        for _ in range(max(args.warmup, 3)):
+        # ---- device-resident timing: REGIONS regions of exactly --steps steps ----
+        warm = max(args.warmup, 3)
+        for _ in range(warm):
             step()
         barrier()
         sampler = ClockSampler(local)
         if rank == 0:
             sampler.start()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
         torch.cuda.profiler.start()  # a profiler started with --profile-from-start off sees only the timed steps
-        e0.record(stream)
-        for _ in range(args.steps):
-            step()
-        e1.record(stream)
-        barrier()
+        regions = time_regions(torch, stream, step, args.steps, REGIONS, barrier)
         torch.cuda.profiler.stop()
-        ms_total = e0.elapsed_time(e1)
 
         # ---- end to end: inputs from pinned host memory, result back to the host, every step ----
+        def e2e_step():
+            x_dev.copy_(x_host, non_blocking=True)
+            step()
+            y_host.copy_(y_dev[y_off[-1]:], non_blocking=True)
+
         for _ in range(2):
-            x_dev.copy_(x_host, non_blocking=True)
-            step()
-            y_host.copy_(y_dev[y_off[-1]:], non_blocking=True)
-        barrier()
-        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        f0.record(stream)
-        for _ in range(args.steps):
-            x_dev.copy_(x_host, non_blocking=True)
-            step()
-            y_host.copy_(y_dev[y_off[-1]:], non_blocking=True)
-        f1.record(stream)
-        barrier()
-        ms_e2e = f0.elapsed_time(f1)
+            e2e_step()
+        e2e_regions = time_regions(torch, stream, e2e_step, args.steps, 3, barrier)
         clocks = sampler.stop() if rank == 0 else None
 
     if world > 1:
-        t = torch.tensor([ms_total, ms_e2e], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total, ms_e2e = float(t[0]), float(t[1])
+        t = torch.tensor(regions + e2e_regions, device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)  # every region: the slowest rank's time
+        regions, e2e_regions = [float(v) for v in t[:REGIONS]], [float(v) for v in t[REGIONS:]]
+    ms_step = statistics.median(regions)
+    ms_e2e = statistics.median(e2e_regions)
     status = pkg.device_status()
 
+    # ---- multi-GPU: is the gathered arena what the unsharded kernels give? (after the timed regions) ----
+    parity_ok = None
+    if world > 1:
+        ok = True
+        seen = set()
+        for i, L in enumerate(layers):
+            if L["kind"] not in sharded or L["kind"] in seen:
+                continue
+            seen.add(L["kind"])
+            x = x_dev[x_off[i]: x_off[i] + L["K"]]
+            per = L["N"] // world
+            for r in range(world):  # every rank's shard, recomputed here from its seed, against the arena
+                w_r = make_layer_weights(pkg, torch, gen, per, L["K"], 1000 * i + r)
+                y_r = torch.empty(per, dtype=torch.bfloat16, device="cuda")
+                pkg.gemv_w4a16(y_r, w_r, x, scratch)
+                torch.cuda.synchronize()
+                got = y_dev[y_off[i] + r * per: y_off[i] + (r + 1) * per]
+                ok = ok and bool(torch.equal(got.view(torch.int16), y_r.view(torch.int16)))
+                pkg.awq_free(w_r)
+        t = torch.tensor([1 if ok else 0], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        parity_ok = bool(int(t[0]))
+
+    peaks, which = measured_peaks()
+    peak = float(peaks.get("hbm_gbs", FALLBACK_HBM_GBS))
+    peak_tf = float(peaks.get("bf16_tflops", FALLBACK_BF16_TFLOPS))
+    extras = None
+    if rank == 0 and world == 1 and os.environ.get("W4A16_BENCH_EXTRAS", "1") != "0":
+        extras = other_configs(pkg, synth, torch, layers, scratch, stream, peak, peak_tf, ms_step)
+        status = status or pkg.device_status()
+
     if rank == 0:
-        ms_step = ms_total / args.steps
         value = alg_bytes / (ms_step * 1e-3) / 1e12
-        e2e_value = alg_bytes / (ms_e2e / args.steps * 1e-3) / 1e12
-        peaks, which = measured_peaks()
-        peak = float(peaks.get("hbm_gbs", FALLBACK_HBM_GBS))
+        e2e_value = alg_bytes / (ms_e2e * 1e-3) / 1e12
         # dominant kernel: the persistent W4A16 GEMV kernel, all 256 launches of a step.
         per_launch_bytes = alg_local / n_launch  # roofline of one GPU's kernel: that GPU's bytes
         per_launch_s = ms_step * 1e-3 / n_launch
@@ -334,31 +447,37 @@ def run_ours(args):
         traffic = per_launch_bytes * (97.39 / 93.68)
         cpu = None
         if world == 1 and not args.no_cpu:
-            tb, dt, desc, threads = cpu_sample(n_layers=2, repeats=3)
-            cpu = {"value": tb, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc}
+            tb, dt, desc, threads, _ = cpu_sample(repeats=3)
+            cpu = {"value": tb, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc, "sample_ms": dt * 1e3}
+        cfg = base_config(synth)
+        run = {"launch": "cuda_graph" if graphed else "eager",
+               "parallelism": "single" if world == 1 else
+               (f"column_shard_x{world}({len(sharded)}_of_6_layer_kinds)+fused_peer_store_all_gather"
+                if comm == "fused" else f"column_shard_x{world}+nccl_all_gather")}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "warmup": warm, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16 x int4 -> fp32", "data": "synthetic",
-            "config": {"workload": "decode_weight_pass_256_gemv_M1", "layers": 64, "hidden": 5120,
-                       "gemvs_per_step": n_launch, "algorithmic_bytes_per_step": alg_bytes,
-                       "cache": "inputs larger than L2 (12.6 GB of distinct weights per step)",
-                       "launch": "cuda_graph" if graphed else "eager",
-                       "parallelism": "single" if world == 1 else
-                       (f"column_shard_x{world}({len(sharded)}_of_6_layer_kinds)+fused_peer_store_all_gather"
-                        if comm == "fused" else f"column_shard_x{world}+nccl_all_gather")},
+            "config": cfg,
+            "run": run,
             "us_per_weight_pass": ms_step * 1e3,
+            "regions_ms_per_step": [round(v, 4) for v in regions],
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": traffic, "peak_source": which,
                          "kernel": "k_skinny<MT=1> (persistent W4A16 GEMV, tcgen05 kind::i8)",
                          "frac_of_nominal_8TBps": achieved / 8000.0},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(x_host.numel() * 2),
-                    "d2h_bytes_per_step": int(y_host.numel() * 2), "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": n_launch * args.steps,
+                    "d2h_bytes_per_step": int(y_host.numel() * 2), "ms_per_step": ms_e2e,
+                    "regions_ms_per_step": [round(v, 4) for v in e2e_regions]},
+            "gpu_launches": n_launch * args.steps * REGIONS,
             "clocks": clocks,
             "device_status": status,
         }
+        if parity_ok is not None:
+            line["parity_ok"] = parity_ok
+        if extras is not None:
+            line["configs"] = extras
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

@@ -70,8 +70,9 @@ typedef struct w4a16_scratch {
 } w4a16_scratch_t;
 
 /* Prefill workspace; mirrors qwen::GemmWorkspace (src/kernels/gemm_w4a16.cuh:30-38).
- * The fused prefill GEMM needs no dequantised tile, so `wbuf` only holds the
- * tensor-map descriptors and is small; `cublas` stays NULL (no cuBLAS). */
+ * The fused prefill GEMM needs no dequantised tile and no library handle: `wbuf` is a
+ * small placeholder allocation (the reference's callers free it themselves) and
+ * `cublas` stays NULL. The activation tensor map travels as a kernel parameter. */
 typedef struct w4a16_workspace {
   uint16_t* wbuf;
   size_t bytes;
@@ -79,10 +80,31 @@ typedef struct w4a16_workspace {
   void* cublas;
 } w4a16_workspace_t;
 
+/* INT8 weight container of the lm_head variant; field-for-field qwen::W8A16Weights
+ * (src/kernels/gemv_w4a16.cuh:148-155). Symmetric int8 codes in [-127,127], one bf16 scale
+ * per (row, group of 128). Both buffers are independent allocations (the reference's
+ * caller frees them one by one, src/model/model.cu:384-385); the whole stream - blocks of
+ * 16640 B per (128-row tile, group): [8 chunks of 16 k][128 rows] 16 B of int8, then 128
+ * bf16 scales - lives behind `qweight`, `scale` is a placeholder. */
+typedef struct w4a16_w8_weights {
+  int8_t* qweight;
+  uint16_t* scale; /* bf16 bits */
+  int out_f, in_f, group_size, num_groups;
+} w4a16_w8_weights_t;
+
 const char* w4a16_last_error(void);
 /* Sticky device-side status of the last kernels on the current device (0 = ok,
  * W4A16_ETIMEOUT if a bounded wait expired). Synchronises the device. */
 int w4a16_device_status(void);
+/* Clears the status word of the current device (synchronises it first). After a
+ * W4A16_ETIMEOUT: w4a16_device_status_clear(), then w4a16_scratch_reset() on every scratch
+ * that was in use (and w4a16_gemv_static_reset() if that entry point was), then carry on. */
+int w4a16_device_status_clear(void);
+/* Launches one tiny kernel whose only wait is on a barrier nobody arrives at, with a limit
+ * of `polls` tests: the wait gives up, the kernel sets W4A16_ETIMEOUT in the status word and
+ * returns normally. Lets a caller (or a test) exercise the detection path end to end without
+ * any fault or hang. polls in [1, 4096]. */
+int w4a16_selftest_wait_timeout(int polls, void* stream);
 
 /* awq_alloc_fused (gemv_w4a16.cuh:85, gemv_w4a16.cu:308-315): allocate the three buffers. */
 int w4a16_weights_alloc(w4a16_weights_t* w, int out_f, int in_f, int group_size, void* stream);
@@ -97,6 +119,10 @@ int w4a16_weights_free(w4a16_weights_t* w);
 /* gemv_scratch_alloc / gemv_scratch_free (gemv_w4a16.cuh:106-107, gemv_w4a16.cu:344-371). */
 int w4a16_scratch_alloc(w4a16_scratch_t* s, int max_in, int max_out, int min_group, int max_m);
 int w4a16_scratch_free(w4a16_scratch_t* s);
+/* Zeroes the arrival tickets of a scratch on `stream`. Only needed after a bounded wait
+ * expired (a launch that gave up may leave tickets behind); launches that complete leave
+ * them at zero themselves. */
+int w4a16_scratch_reset(w4a16_scratch_t* s, void* stream);
 /* gemv_partial_check (gemv_w4a16.cuh:109): W4A16_ESCRATCH instead of abort. */
 int w4a16_scratch_check(const w4a16_scratch_t* s, int out_f, int M);
 /* gemv_choose_splits (gemv_w4a16.cuh:135): the number of CTAs that share one
@@ -116,6 +142,9 @@ int w4a16_gemv(void* y, int y_is_f32, const w4a16_weights_t* w, const uint16_t* 
  * and clears its counters, so make that call before capturing a stream. All calls share the
  * array: calls that overlap on the GPU race; calls in stream order are fine. */
 int w4a16_gemv_static(void* y, int y_is_f32, const w4a16_weights_t* w, const uint16_t* x, void* stream);
+/* Zeroes the arrival tickets inside the built-in array of w4a16_gemv_static on `stream`
+ * (recovery after W4A16_ETIMEOUT; allocates nothing). */
+int w4a16_gemv_static_reset(void* stream);
 /* gemm_small_w4a16 and gemm_mma_w4a16 (gemv_w4a16.cuh:124-125,187-188):
  * Y[M][out_f] = X[M][in_f] W^T, 1 <= M <= 16, row-major bf16, weights read once. */
 int w4a16_gemm_skinny(uint16_t* y, const w4a16_weights_t* w, const uint16_t* x, int M,
@@ -132,6 +161,31 @@ int w4a16_lm_head_argmax(int32_t* ids, uint16_t* logits, void* pairs, int row_of
 /* Reduce nranks x M gathered {float,int32} pairs (rank-major) to ids[M]:
  * larger value wins, then lower index. The cross-rank step of the sharded lm_head. */
 int w4a16_argmax_pairs_reduce(int32_t* ids, const void* pairs, int nranks, int M, void* stream);
+
+/* quantize_w8a16 (gemv_w4a16.cuh:157-158, gemv_w4a16.cu:479-499,610-617): allocate `dst` and
+ * quantise src bf16 [out_f][in_f] (device) per (row, group): s = max|v|/127 stored as bf16,
+ * q = clamp(rn(v * (127/max|v|)), -127, 127). group_size must be 128, out_f a multiple of 16. */
+int w4a16_w8_quantize(w4a16_w8_weights_t* dst, const uint16_t* src, int out_f, int in_f,
+                      int group_size, void* stream);
+/* w8a16_free (gemv_w4a16.cuh:166). */
+int w4a16_w8_free(w4a16_w8_weights_t* w);
+/* Rows [row0,row0+nrows) back as plain tensors: q int8 [nrows][in_f], scale bf16 [nrows][G]
+ * (either may be NULL). The check that anchors the INT8 path bit for bit; no reference
+ * counterpart (its layout is never read back). */
+int w4a16_w8_unpack_rows(int8_t* q, uint16_t* scale, const w4a16_w8_weights_t* w, int row0,
+                         int nrows, void* stream);
+/* gemv_w8a16 (gemv_w4a16.cuh:159-160, gemv_w4a16.cu:619-632): y bf16 [out_f] = W x. */
+int w4a16_w8_gemv(uint16_t* y, const w4a16_w8_weights_t* w, const uint16_t* x,
+                  w4a16_scratch_t* s, void* stream);
+/* gemm_small_w8a16 (gemv_w4a16.cuh:164-165, gemv_w4a16.cu:570-608): Y[M][out_f], 1 <= M <= 16. */
+int w4a16_w8_gemm_skinny(uint16_t* y, const w4a16_w8_weights_t* w, const uint16_t* x, int M,
+                         w4a16_scratch_t* s, void* stream);
+/* INT8 lm_head with the argmax fused; same contract as w4a16_lm_head_argmax. Replaces
+ * gemv_w8a16 / gemm_small_w8a16 followed by argmax / argmax_rows
+ * (src/model/model.cu:805-806,1049; src/kernels/elementwise.cu:96-194). */
+int w4a16_w8_lm_head_argmax(int32_t* ids, uint16_t* logits, void* pairs, int row_offset,
+                            const w4a16_w8_weights_t* w, const uint16_t* x, int M,
+                            w4a16_scratch_t* s, void* stream);
 
 /* w4a16_dequant_rows (gemm_w4a16.cuh:45-48, gemm_w4a16.cu:15-38,56-61): rows
  * [row0,row0+nrows) -> row-major bf16 [nrows][in_f], bf16(float(q-zp)*float(s)). */

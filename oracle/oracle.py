@@ -48,6 +48,8 @@ def lib():
             build()
         L = C.CDLL(_LIB_PATH)
         L.oracle_num_threads.restype = C.c_int
+        L.oracle_set_num_threads.argtypes = [C.c_int]
+        L.oracle_set_num_threads.restype = None
         L.oracle_f32_to_bf16.argtypes = [_f32p, _u16p, _i64]
         L.oracle_bf16_to_f32.argtypes = [_u16p, _f32p, _i64]
         L.oracle_unpack_q.argtypes = [_u32p, _i64, _i64, _i8p]
@@ -61,9 +63,12 @@ def lib():
         L.oracle_lm_head_argmax.argtypes = [_u32p, _u16p, _u32p, _i64, _i64, _i64, _u16p, _i64,
                                             _i32p, C.c_void_p, C.c_void_p]
         L.oracle_quant_i4.argtypes = [_u16p, _i64, _i64, _i64, _u32p, _u16p, _u32p]
+        L.oracle_quant_w8.argtypes = [_u16p, _i64, _i64, _i64, _i8p, _u16p]
+        L.oracle_gemm_w8_f64.argtypes = [_i8p, _u16p, _i64, _i64, _i64, _u16p, _i64, C.c_void_p, _i64, _f64p]
         for f in ("oracle_f32_to_bf16", "oracle_bf16_to_f32", "oracle_unpack_q", "oracle_unpack_zp",
                   "oracle_dequant_f32", "oracle_dequant_bf16", "oracle_gemm_f64", "oracle_gemm_f32",
-                  "oracle_argmax_bf16", "oracle_lm_head_argmax", "oracle_quant_i4"):
+                  "oracle_argmax_bf16", "oracle_lm_head_argmax", "oracle_quant_i4", "oracle_quant_w8",
+                  "oracle_gemm_w8_f64"):
             getattr(L, f).restype = None
         _lib = L
     return _lib
@@ -85,6 +90,11 @@ def ref_lib():
 
 def num_threads() -> int:
     return int(lib().oracle_num_threads())
+
+
+def set_num_threads(n: int) -> None:
+    """OpenMP thread count of the oracle (torchrun exports OMP_NUM_THREADS=1 to its children)."""
+    lib().oracle_set_num_threads(int(n))
 
 
 def _c(a, dt):
@@ -206,3 +216,47 @@ def quant_i4(src_bf16, group=128):
     zp = np.zeros((rows // 8, G), np.uint32)
     lib().oracle_quant_i4(src, rows, cols, group, packed, scale, zp)
     return packed, scale, zp
+
+
+# ------------------------------------------------------------------ INT8 g128 lm_head variant
+def quant_w8(src_bf16, group=128):
+    """bf16 [rows, cols] -> (q int8 [rows, cols], scale uint16 [rows, G]), symmetric per group."""
+    src = _c(src_bf16, np.uint16)
+    rows, cols = src.shape
+    q = np.zeros((rows, cols), np.int8)
+    scale = np.zeros((rows, cols // group), np.uint16)
+    lib().oracle_quant_w8(src, rows, cols, group, q, scale)
+    return q, scale
+
+
+def gemm_w8_f64(q, scale, x, rows=None):
+    """fp64 reference Y[M, N] (or Y[M, len(rows)]) of the int8 weights."""
+    q, scale = _c(q, np.int8), _c(scale, np.uint16)
+    N, K = q.shape
+    group = K // scale.shape[1]
+    x = _c(x, np.uint16).reshape(-1, K)
+    M = x.shape[0]
+    if rows is None:
+        out = np.empty((M, N), np.float64)
+        lib().oracle_gemm_w8_f64(q, scale, N, K, group, x, M, None, 0, out)
+    else:
+        rows = _c(rows, np.int64)
+        out = np.empty((M, rows.size), np.float64)
+        lib().oracle_gemm_w8_f64(q, scale, N, K, group, x, M, rows.ctypes.data_as(C.c_void_p), rows.size, out)
+    return out
+
+
+def argmax_with_gaps(y64):
+    """fp64 logits [M, N] -> (ids, top-2 gap in bf16 ulps of the best, bf16 logits): the tail of
+    oracle_lm_head_argmax for logits computed elsewhere (rounded fp64 -> fp32 -> bf16, as there)."""
+    logits = f32_to_bf16(np.asarray(y64, np.float64).astype(np.float32))
+    ids = argmax_bf16(logits)
+    lf = bf16_to_f32(logits)
+    gaps = np.empty(len(ids), np.float64)
+    for m, i in enumerate(ids):
+        best = float(lf[m, i])
+        rest = np.delete(lf[m], i)
+        second = float(rest.max()) if rest.size else -3.4e38
+        e = np.frexp(abs(best) if best != 0 else 1e-30)[1]
+        gaps[m] = (best - second) / 2.0 ** (e - 8)
+    return ids, gaps, logits

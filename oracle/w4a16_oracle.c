@@ -19,6 +19,8 @@
  *   bf16 round-to-nearest-even ....... tests/gate_gemv.cu:24-29
  *   argmax, ties to lowest index ..... src/spec/spec.cu:128-136, src/kernels/elementwise.cu:129-150
  *   min/max int4 quantiser ........... src/model/model.cu:140-172
+ *   symmetric int8 quantiser ......... src/kernels/gemv_w4a16.cu:479-499
+ *   int8 GEMV / GEMM (s * sum q x) ... src/kernels/gemv_w4a16.cu:501-523,525-568
  *
  * On-disk ("compressed-tensors pack-quantized") layout, all little endian:
  *   packed [N][K/8] u32 : element i of a row is bits [4(i%8), 4(i%8)+4) of word i/8
@@ -67,6 +69,15 @@ ORACLE_API int oracle_num_threads(void) {
   return omp_get_max_threads();
 #else
   return 1;
+#endif
+}
+
+/* Thread count of the timed baseline; a launcher may have exported OMP_NUM_THREADS=1. */
+ORACLE_API void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
 #endif
 }
 
@@ -266,6 +277,55 @@ ORACLE_API void oracle_quant_i4(const uint16_t* src, int64_t rows, int64_t cols,
         }
         packed[r * (cols / 8) + (g * group + i) / 8] = w;
       }
+    }
+  }
+}
+
+/* ---- INT8 g128 symmetric lm_head variant (W8A16) ----
+ * Quantiser: per (row, group) mx = max|v|, s = mx/127 stored as bf16, inv = mx>0 ? 127/mx : 0,
+ * q = clamp(rn(v*inv), -127, 127); fp32 throughout. q is plain row-major int8 [rows][cols],
+ * scale bf16 [rows][G] (the reference's 32-row interleave is a private layout, not part of
+ * the arithmetic). */
+ORACLE_API void oracle_quant_w8(const uint16_t* src, int64_t rows, int64_t cols, int64_t group,
+                                int8_t* q, uint16_t* scale) {
+  const int64_t G = cols / group;
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < rows; ++r) {
+    for (int64_t g = 0; g < G; ++g) {
+      const int64_t base = r * cols + g * group;
+      float mx = 0.f;
+      for (int64_t i = 0; i < group; ++i) mx = fmaxf(mx, fabsf(bf16_to_f32(src[base + i])));
+      const float s = mx / 127.0f;
+      const float inv = (mx > 0.f) ? 127.0f / mx : 0.f;
+      scale[r * G + g] = f32_to_bf16(s);
+      for (int64_t i = 0; i < group; ++i) {
+        int v = (int)nearbyintf(bf16_to_f32(src[base + i]) * inv);
+        v = v < -127 ? -127 : (v > 127 ? 127 : v);
+        q[base + i] = (int8_t)v;
+      }
+    }
+  }
+}
+
+/* Y[M][N] (fp64) = X[M][K] * W^T with W = double(q) * double(bf16 scale), ascending k.
+ * rows == NULL: all N rows; else only the listed rows, out is [M][nrows]. */
+ORACLE_API void oracle_gemm_w8_f64(const int8_t* q, const uint16_t* scale, int64_t N, int64_t K,
+                                   int64_t group, const uint16_t* x, int64_t M, const int64_t* rows,
+                                   int64_t nrows, double* out) {
+  const int64_t G = K / group;
+  const int64_t R = rows ? nrows : N;
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < R; ++r) {
+    const int64_t o = rows ? rows[r] : r;
+    for (int64_t m = 0; m < M; ++m) {
+      const uint16_t* xm = x + m * K;
+      double acc = 0.0;
+      for (int64_t g = 0; g < G; ++g) {
+        const double s = (double)bf16_to_f32(scale[o * G + g]);
+        for (int64_t i = g * group; i < (g + 1) * group; ++i)
+          acc += (double)q[o * K + i] * s * (double)bf16_to_f32(xm[i]);
+      }
+      out[m * R + r] = acc;
     }
   }
 }

@@ -43,6 +43,15 @@ class Weights(C.Structure):
         return self.qweight_bytes() + self.scale_bytes() + self.zp_bytes()
 
 
+class W8Weights(C.Structure):
+    """w4a16_w8_weights_t == qwen::W8A16Weights (src/kernels/gemv_w4a16.cuh:148-155)."""
+    _fields_ = [("qweight", C.c_void_p), ("scale", C.c_void_p),
+                ("out_f", C.c_int), ("in_f", C.c_int), ("group_size", C.c_int), ("num_groups", C.c_int)]
+
+    def total_bytes(self):
+        return self.out_f * self.in_f + self.out_f * self.num_groups * 2
+
+
 class Scratch(C.Structure):
     """w4a16_scratch_t == qwen::GemvScratch (src/kernels/gemv_w4a16.cuh:94-104)."""
     _fields_ = [("xf", C.c_void_p), ("xgsum", C.c_void_p), ("partial", C.c_void_p),
@@ -59,6 +68,18 @@ class Workspace(C.Structure):
 _SIGNATURES = {
     "w4a16_last_error": (C.c_char_p, []),
     "w4a16_device_status": (C.c_int, []),
+    "w4a16_device_status_clear": (C.c_int, []),
+    "w4a16_selftest_wait_timeout": (C.c_int, [C.c_int, C.c_void_p]),
+    "w4a16_scratch_reset": (C.c_int, [C.POINTER(Scratch), C.c_void_p]),
+    "w4a16_gemv_static_reset": (C.c_int, [C.c_void_p]),
+    "w4a16_w8_quantize": (C.c_int, [C.POINTER(W8Weights), C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "w4a16_w8_free": (C.c_int, [C.POINTER(W8Weights)]),
+    "w4a16_w8_unpack_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(W8Weights), C.c_int, C.c_int, C.c_void_p]),
+    "w4a16_w8_gemv": (C.c_int, [C.c_void_p, C.POINTER(W8Weights), C.c_void_p, C.POINTER(Scratch), C.c_void_p]),
+    "w4a16_w8_gemm_skinny": (C.c_int, [C.c_void_p, C.POINTER(W8Weights), C.c_void_p, C.c_int,
+                                       C.POINTER(Scratch), C.c_void_p]),
+    "w4a16_w8_lm_head_argmax": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.POINTER(W8Weights),
+                                          C.c_void_p, C.c_int, C.POINTER(Scratch), C.c_void_p]),
     "w4a16_weights_alloc": (C.c_int, [C.POINTER(Weights), C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "w4a16_repack_into": (C.c_int, [C.POINTER(Weights), C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
                                     C.c_int, C.c_void_p]),
@@ -238,3 +259,50 @@ def gemm_skinny_sharded(y_peer_ptrs, rank: int, out_f_total: int, row_begin: int
 
 def device_status() -> int:
     return int(lib().w4a16_device_status())
+
+
+def device_status_clear():
+    check(lib().w4a16_device_status_clear())
+
+
+def selftest_wait_timeout(polls: int = 64, stream=None):
+    """One tiny kernel whose only wait can never be satisfied: it gives up and sets the status word."""
+    check(lib().w4a16_selftest_wait_timeout(polls, _stream(stream)))
+
+
+def gemv_scratch_reset(s: Scratch, stream=None):
+    check(lib().w4a16_scratch_reset(C.byref(s), _stream(stream)))
+
+
+def gemv_static_reset(stream=None):
+    check(lib().w4a16_gemv_static_reset(_stream(stream)))
+
+
+# --------------------------------------------------------------------- INT8 lm_head (W8A16)
+def quantize_w8a16(src, group_size: int = 128, stream=None) -> W8Weights:
+    """src: device bf16 [out_f, in_f] -> symmetric int8 g128 container."""
+    w = W8Weights()
+    check(lib().w4a16_w8_quantize(C.byref(w), _ptr(src), src.shape[0], src.shape[1], group_size, _stream(stream)))
+    return w
+
+
+def w8a16_free(w: W8Weights):
+    check(lib().w4a16_w8_free(C.byref(w)))
+
+
+def w8a16_unpack_rows(q, scale, w: W8Weights, row0: int, nrows: int, stream=None):
+    check(lib().w4a16_w8_unpack_rows(_ptr(q), _ptr(scale), C.byref(w), row0, nrows, _stream(stream)))
+
+
+def gemv_w8a16(y, w: W8Weights, x, s: Scratch, stream=None):
+    check(lib().w4a16_w8_gemv(_ptr(y), C.byref(w), _ptr(x), C.byref(s), _stream(stream)))
+
+
+def gemm_small_w8a16(y, w: W8Weights, x, M: int, s: Scratch, stream=None):
+    check(lib().w4a16_w8_gemm_skinny(_ptr(y), C.byref(w), _ptr(x), M, C.byref(s), _stream(stream)))
+
+
+def lm_head_argmax_w8(ids, w: W8Weights, x, M: int, s: Scratch, logits=None, pairs=None, row_offset: int = 0,
+                      stream=None):
+    check(lib().w4a16_w8_lm_head_argmax(_ptr(ids), _ptr(logits), _ptr(pairs), row_offset, C.byref(w), _ptr(x),
+                                        M, C.byref(s), _stream(stream)))

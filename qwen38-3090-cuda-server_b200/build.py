@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libw4a16_b200.so")
-SOURCES = ["weights.cu", "skinny.cu", "prefill.cu"]
+SOURCES = ["weights.cu", "w8.cu", "skinny.cu", "prefill.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC,-fvisibility=hidden"] + os.environ.get("W4A16_NVCC_FLAGS", "").split()

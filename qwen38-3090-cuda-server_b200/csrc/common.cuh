@@ -1,6 +1,6 @@
 // Shared host/device helpers for the sm_100a W4A16 kernels: error reporting for
-// the C ABI, PTX wrappers (mbarrier, bulk async copy, cp.async, mma, programmatic
-// dependent launch) and the private weight layout's index arithmetic.
+// the C ABI, PTX wrappers (mbarrier, bulk async copy, tcgen05 / tensor memory,
+// programmatic dependent launch) and the private weight layout's index arithmetic.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -74,6 +74,24 @@ __host__ __device__ inline int weight_slot(int r, int c) { return (r + 4 * (c & 
 // nibble position inside a packed word for k-offset c (0..7)
 __host__ __device__ inline int nib_pos(int c) { return (c >> 1) + 4 * (c & 1); }
 
+// INT8 stream (W8A16: symmetric int8, group 128, the lm_head variant). Same tiling; a block is 16640 bytes:
+//     [8 chunks of 16 k-bytes][128 rows] 16 B   16384 B   byte j (0..127) of a row holds k = 8 (j/8) + w8_k_of(j%8)
+//     [128 rows] bf16 scale                       256 B
+// The k order inside every 8 is the order in which the int4 unpack (two nibble masks) delivers a packed
+// word's weights, so both formats multiply the same activation operand.
+constexpr int kW8ChunkBytes = kTileRows * 16;               // 2048
+constexpr int kW8ScaleOff = 8 * kW8ChunkBytes;              // 16384
+constexpr int kW8BlockBytes = kW8ScaleOff + kTileRows * 2;  // 16640
+__host__ __device__ inline size_t w8_stream_bytes(int out_f, int G) {
+  return static_cast<size_t>((out_f + kTileRows - 1) / kTileRows) * G * kW8BlockBytes;
+}
+// position (0..7) inside its 8-block of k-offset o, and back
+__host__ __device__ inline int w8_pos_of_k(int o) { return (o & 3) * 2 + (o >> 2); }
+__host__ __device__ inline int w8_k_of_pos(int j) { return (j >> 1) + 4 * (j & 1); }
+
+// Validates an INT8 weight container.
+int check_w8(const w4a16_w8_weights_t* w);
+
 #ifdef __CUDACC__
 // ------------------------------------------------------------------ device PTX
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -138,30 +156,6 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
       "l"(src), "r"(bytes), "r"(bar)
       : "memory");
 }
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
-
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "r"(addr));
-  return v;
-}
-
-// D(16x8, fp32) += A(16x16, bf16, row) * B(16x8, bf16, col)
-__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                               uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%0,%1,%2,%3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
 // ------------------------------------------------------------------ tcgen05 / tensor memory
 // Allocation is warp-collective; the base address lands in shared memory.
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
@@ -186,28 +180,6 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 }
 template <int N>
 __device__ __forceinline__ void tmem_ld(uint32_t taddr, float (&d)[N]);
-template <>
-__device__ __forceinline__ void tmem_ld<1>(uint32_t taddr, float (&d)[1]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=f"(d[0]) : "r"(taddr) : "memory");
-}
-template <>
-__device__ __forceinline__ void tmem_ld<2>(uint32_t taddr, float (&d)[2]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0,%1}, [%2];" : "=f"(d[0]), "=f"(d[1]) : "r"(taddr) : "memory");
-}
-template <>
-__device__ __forceinline__ void tmem_ld<4>(uint32_t taddr, float (&d)[4]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
-               : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-               : "r"(taddr)
-               : "memory");
-}
-template <>
-__device__ __forceinline__ void tmem_ld<8>(uint32_t taddr, float (&d)[8]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-               : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3]), "=f"(d[4]), "=f"(d[5]), "=f"(d[6]), "=f"(d[7])
-               : "r"(taddr)
-               : "memory");
-}
 template <>
 __device__ __forceinline__ void tmem_ld<16>(uint32_t taddr, float (&d)[16]) {
   asm volatile(
@@ -237,15 +209,6 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, u
       "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// D[tmem] (+)= A[smem desc] * B[smem desc]
-__device__ __forceinline__ void umma_bf16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                             uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
 // The mbarrier gets one arrival once every tcgen05.mma issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -259,15 +222,6 @@ __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
-// D = A * B with a zero accumulator (starts an accumulation chain without clearing registers)
-__device__ __forceinline__ void mma_bf16_16816_zero(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                                    uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%10,%10,%10,%10};"
-      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
-}
 // packed bf16 subtract: exact for the small integers used here
 __device__ __forceinline__ uint32_t sub_bf16x2(uint32_t a, uint32_t b) {
   uint32_t d;

@@ -43,6 +43,7 @@
 #include <climits>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <type_traits>
 
 #include "common.cuh"
@@ -60,7 +61,12 @@ constexpr int kWMma2 = 15;                 // MMA issuer of the odd steps
 constexpr int kWConv0 = 16;                // warps 16..23 (and the otherwise idle warp 14) only convert activations
 constexpr int kTeam = 4 + 1 + 8;           // converting warps: the fix-up warps, warp 14, warps 16..23
 constexpr int kStepGroups = 2;             // k groups per step: every hand-off between roles moves two groups
-constexpr int kStageBytes = kStepGroups * kTileGroupBytes;  // 17152
+// Weight formats: WB = 4 (AWQ int4 + zero points) or 8 (symmetric int8). A ring stage holds one step.
+template <int WB>
+struct Fmt {
+  static constexpr int kBlock = WB == 4 ? kTileGroupBytes : kW8BlockBytes;  // bytes per (row tile, group)
+  static constexpr int kStage = kStepGroups * kBlock;                        // 17152 / 33280
+};
 constexpr int kSide = 16;                  // (scale, zp) side ring: 8 steps x 2 groups
 constexpr int kTable = 64;                 // step table entries (ring)
 constexpr uint32_t kSpinLimit = 1u << 20;  // polls before a wait gives up
@@ -70,17 +76,6 @@ constexpr int kTmemCols = 512;             // all of tensor memory; the next lau
 constexpr int kAColsG = 32;                // 128 int8 along k = 32 columns of 32 bits per group
 constexpr int kMaxBatch = 10;              // tokens per launch; larger M runs as two launches
 
-#ifdef W4A16_TRACE
-// Development aid (compiled only with -DW4A16_TRACE): per-CTA timestamps of a launch's phases.
-__device__ long long g_tline[8 * 256 * 8];  // [launch % 8][CTA][event]
-__device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define TL(i) do { g_tline[((p.trace_id & 7) * 256 + blockIdx.x) * 8 + (i)] = gtime(); } while (0)
-__device__ int g_where[8];  // first bounded wait that gave up: site, step, CTA, warp
-#define GAVE_UP(site, step) do { if (atomicCAS(&g_where[0], 0, (site)) == 0) { g_where[1] = (step); g_where[2] = blockIdx.x; g_where[3] = threadIdx.x >> 5; g_where[4] = p.trace_id; } } while (0)
-#else
-#define TL(i)
-#define GAVE_UP(site, step)
-#endif
 
 // Per token-count geometry. N = rows of the B operand the tensor core reads (3 digit rows per token are
 // real). Ring depths are in steps: AD2 for A, DD2 for D and for the ring of "step done" barriers.
@@ -103,7 +98,7 @@ struct Geo {
 };
 
 struct SkinnyParams {
-  const uint8_t* stream;  // weight stream, kTileGroupBytes per (row tile, group)
+  const uint8_t* stream;  // weight stream, Fmt<WB>::kBlock bytes per (row tile, group)
   const uint16_t* x;      // [M][K] bf16
   void* y;                // bf16 or fp32 [M][ldy], may be null in argmax mode
   int y_f32;
@@ -113,7 +108,6 @@ struct SkinnyParams {
   int b_bytes;       // bytes of the B region (digit rows of the groups this CTA multiplies)
   int xs_bytes;      // bytes of the (sum, 2^-p) region
   unsigned long long mg_grid, mg_G;  // ceil(2^40 / d) for d = gridDim.x and G: exact division by multiply
-  int trace_id;      // launch counter (development trace only)
   uint32_t hint;     // suspend-time hint of the mbarrier waits, ns
   int depth;         // weight ring stages
   float* partial;
@@ -285,8 +279,8 @@ __host__ __device__ constexpr int bar_count(int depth) {
   return 2 * depth + Geo<MT>::AD2 + 2 * Geo<MT>::DD2 + 2;
 }
 template <int MT>
-__host__ __device__ inline int total_smem(int depth, int b_bytes, int xs_bytes) {
-  return depth * kStageBytes + b_bytes + kSide * kTileRows * 4 + xs_bytes + kTable * 8 + 256 * 4 +
+__host__ __device__ inline int total_smem(int depth, int stage_bytes, int b_bytes, int xs_bytes) {
+  return depth * stage_bytes + b_bytes + kSide * kTileRows * 4 + xs_bytes + kTable * 8 + 256 * 4 +
          bar_count<MT>(depth) * 8 + 16;
 }
 
@@ -330,9 +324,10 @@ __device__ __forceinline__ void convert_group(uint2 rv, uint8_t* bslot, int lbo,
   if (lane == 0) *xs = make_float2(static_cast<float>(tot), inv);
 }
 
-template <int MT>
+template <int MT, int WB>
 __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   using GE = Geo<MT>;
+  constexpr int kBlock = Fmt<WB>::kBlock, kStageBytes = Fmt<WB>::kStage;
   constexpr int N = GE::N, AD2 = GE::AD2, DD2 = GE::DD2;
   constexpr int SLOT = kTileRows * MT;  // floats per partial tile
   extern __shared__ __align__(128) uint8_t smem[];
@@ -352,7 +347,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // the same value, but provably warp-uniform
   const int G = p.G, M = p.M;
   const int U = p.tiles * G;
-  if (tid == 0) TL(0);
   // (U * gridDim.x fits 32 bits: checked on the host; a 64-bit division here costs a visible part of the start-up)
   const int u0 = static_cast<int>(fdiv(static_cast<uint32_t>(U) * blockIdx.x, p.mg_grid));
   const int u1 = static_cast<int>(fdiv(static_cast<uint32_t>(U) * (blockIdx.x + 1), p.mg_grid));
@@ -395,7 +389,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   }
   __syncthreads();
   pdl_launch_dependents();
-  if (tid == 0) TL(1);
 
   // The previous launch's CTA on this SM may still hold tensor memory: only this warp waits for it.
   if (warp == kWMma) {
@@ -413,7 +406,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
     // warps and the issuers do not take part: they fill the A ring from the weights meanwhile. x comes straight from global memory (L2); a round's loads are all in
     // flight before its first conversion.
     pdl_wait();  // the previous kernel produced x
-    if (tid == 0) TL(2);
     const int ti = warp < CW ? warp : (warp == 14 ? CW : warp - kWConv0 + CW + 1);
     const int cnt = (u1 - u0 < G) ? u1 - u0 : G;
     const int total = cnt * M;  // (group, token) items; item i belongs to warp i % kTeam
@@ -451,7 +443,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(bready_a);
-    if (tid == 0) TL(3);
   }
 
   // This CTA owns all 512 columns, so its tensor-memory addresses start at 0: a compile-time constant
@@ -460,7 +451,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   const bool uses_tmem = warp < kWProducer || warp == kWMma || warp == kWMma2 || warp >= kWConv0;
   if (uses_tmem) {
     if (!wait_h(tmemrdy_a, 0, p.hint, kSpinLimit) || *reinterpret_cast<volatile uint32_t*>(tmem_slot) != 0u) {
-      GAVE_UP(2, -1);
       atomicExch(p.status, W4A16_ETIMEOUT);
       team_ok = false;
     }
@@ -480,11 +470,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
       uint32_t ph = 1;  // a fresh "empty" barrier reads as already released
       bool ok = true;
       while (ok && it.next(sg)) {
-        const uint8_t* src = p.stream + (static_cast<size_t>(sg.tile) * G + sg.g0) * kTileGroupBytes;
+        const uint8_t* src = p.stream + (static_cast<size_t>(sg.tile) * G + sg.g0) * kBlock;
         for (int gl = 0; gl < sg.L; gl += kStepGroups, ++t) {
           const int ng = (sg.L - gl < kStepGroups) ? sg.L - gl : kStepGroups;
           if (!mbar_wait_bounded_relaxed(wempty_a + st * 8, ph, kSpinLimit)) {
-            GAVE_UP(3, t);
             atomicExch(p.status, W4A16_ETIMEOUT);
             ok = false;
             break;
@@ -493,9 +482,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
           const int s1 = ng == 2 ? cache_slot(sg.g0 + gl + 1) : s0;
           table[t & (kTable - 1)] =
               make_uint2(step_word(s0, s1, ng, gl + kStepGroups >= sg.L, sg.whole), static_cast<uint32_t>(sg.tile));
-          mbar_expect_tx(wfull_a + st * 8, ng * kTileGroupBytes);
-          bulk_g2s(ring_a + st * kStageBytes, src + static_cast<size_t>(gl) * kTileGroupBytes, ng * kTileGroupBytes,
-                   wfull_a + st * 8);
+          mbar_expect_tx(wfull_a + st * 8, ng * kBlock);
+          bulk_g2s(ring_a + st * kStageBytes, src + static_cast<size_t>(gl) * kBlock, ng * kBlock, wfull_a + st * 8);
           if (++st == DS) {
             st = 0;
             ph ^= 1;
@@ -526,7 +514,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
         const int a = t & (AD2 - 1), d = t & (DD2 - 1);
         // A written; its writers also saw the D slot drained and the step's weights (and table entry) landed
         if (!wait_h(afull_a + a * 8, static_cast<uint32_t>(t / AD2) & 1u, p.hint, kSpinLimit)) {
-          GAVE_UP(5, t);
           atomicExch(p.status, W4A16_ETIMEOUT);
           break;
         }
@@ -541,7 +528,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
             __nanosleep(40);
           }
           if (spins > kSpinLimit) {
-            GAVE_UP(4, t);
             atomicExch(p.status, W4A16_ETIMEOUT);
             break;
           }
@@ -569,8 +555,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
     }
   } else if (warp >= kWUnpack0 && warp < kWUnpack0 + 8) {
     // ================================================================ unpack warps
-    // Thread = one row of the tile = one TMEM lane. Per group: the row's 64 bytes (four 16-byte slots)
-    // -> 32 registers of int8 -> 32 TMEM columns of the A slot. Two warps per lane quarter, alternating
+    // Thread = one row of the tile = one TMEM lane. Per group: the row's 64 bytes of nibbles (four 16-byte
+    // slots; int8 weights: 128 bytes, eight slots) -> 32 registers of int8 -> 32 TMEM columns of the A slot. Two warps per lane quarter, alternating
     // steps. Both groups of a step are always unpacked (a missing second group is stale bytes that feed
     // only unread accumulator columns), so this role needs nothing but the step number.
     const int q = warp & 3, pair = (warp - kWUnpack0) >> 2, r = q * 32 + lane;
@@ -583,21 +569,30 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
     for (int t = pair; ok && t < T; t += 2) {
       const int a = t & (AD2 - 1);
       if (!wait_h(wfull_a + st * 8, wph, p.hint, kSpinLimit)) {
-        GAVE_UP(6, t);
         atomicExch(p.status, W4A16_ETIMEOUT);
         break;
       }
       const uint8_t* base = ring + st * kStageBytes;
-      uint4 w0 = *reinterpret_cast<const uint4*>(base + off_e);
-      uint4 w1 = *reinterpret_cast<const uint4*>(base + off_o);
-      uint4 w2 = *reinterpret_cast<const uint4*>(base + off_e + 2 * kChunkBytes);
-      uint4 w3 = *reinterpret_cast<const uint4*>(base + off_o + 2 * kChunkBytes);
+      // the first group's words are requested before the waits below
+      constexpr int NW = WB == 4 ? 4 : 8;  // 16-byte pieces of a row per group
+      uint4 wv[NW];
+      auto load_row = [&](const uint8_t* gb) {
+        if constexpr (WB == 4) {
+          wv[0] = *reinterpret_cast<const uint4*>(gb + off_e);
+          wv[1] = *reinterpret_cast<const uint4*>(gb + off_o);
+          wv[2] = *reinterpret_cast<const uint4*>(gb + off_e + 2 * kChunkBytes);
+          wv[3] = *reinterpret_cast<const uint4*>(gb + off_o + 2 * kChunkBytes);
+        } else {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) wv[c] = *reinterpret_cast<const uint4*>(gb + c * kW8ChunkBytes + off_e);
+        }
+      };
+      load_row(base);
       // the A slot's previous step has been multiplied, and the D slot this step will fill has been read out
       if ((t >= AD2 && !wait_h(done_a + ((t - AD2) & (DD2 - 1)) * 8, static_cast<uint32_t>((t - AD2) / DD2) & 1u, p.hint,
                                kSpinLimit)) ||
           (t >= DD2 &&
            !wait_h(dempty_a + (t & (DD2 - 1)) * 8, static_cast<uint32_t>(t / DD2 - 1) & 1u, p.hint, kSpinLimit))) {
-        GAVE_UP(7, t);
         atomicExch(p.status, W4A16_ETIMEOUT);
         break;
       }
@@ -605,27 +600,35 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
       uint32_t* side_w = reinterpret_cast<uint32_t*>(side) + ((t & 7) * kStepGroups) * kTileRows + r;
 #pragma unroll
       for (int j = 0; j < kStepGroups; ++j) {
-        const uint8_t* gb = base + j * kTileGroupBytes;
-        if (j > 0) {
-          w0 = *reinterpret_cast<const uint4*>(gb + off_e);
-          w1 = *reinterpret_cast<const uint4*>(gb + off_o);
-          w2 = *reinterpret_cast<const uint4*>(gb + off_e + 2 * kChunkBytes);
-          w3 = *reinterpret_cast<const uint4*>(gb + off_o + 2 * kChunkBytes);
-        }
-        const uint32_t sc = *reinterpret_cast<const uint16_t*>(gb + kTgScaleOff + 2 * r);
-        const uint32_t zp = *(gb + kTgZpOff + r);
-        const uint32_t ww[16] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w,
-                                 w2.x, w2.y, w2.z, w2.w, w3.x, w3.y, w3.z, w3.w};
+        const uint8_t* gb = base + j * kBlock;
+        if (j > 0) load_row(gb);
         uint32_t v[32];
+        uint32_t sz;  // (bf16 scale << 16) | zero-point nibble
+        if constexpr (WB == 4) {
+          const uint32_t sc = *reinterpret_cast<const uint16_t*>(gb + kTgScaleOff + 2 * r);
+          sz = (sc << 16) | *(gb + kTgZpOff + r);
+          const uint32_t ww[16] = {wv[0].x, wv[0].y, wv[0].z, wv[0].w, wv[1].x, wv[1].y, wv[1].z, wv[1].w,
+                                   wv[2].x, wv[2].y, wv[2].z, wv[2].w, wv[3].x, wv[3].y, wv[3].z, wv[3].w};
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          v[2 * i] = ww[i] & 0x0F0F0F0Fu;
-          v[2 * i + 1] = (ww[i] >> 4) & 0x0F0F0F0Fu;
+          for (int i = 0; i < 16; ++i) {
+            v[2 * i] = ww[i] & 0x0F0F0F0Fu;
+            v[2 * i + 1] = (ww[i] >> 4) & 0x0F0F0F0Fu;
+          }
+        } else {
+          // int8 codes are the operand as they are; symmetric, so the zero-point field stays 0
+          sz = static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(gb + kW8ScaleOff + 2 * r)) << 16;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            v[4 * c] = wv[c].x;
+            v[4 * c + 1] = wv[c].y;
+            v[4 * c + 2] = wv[c].z;
+            v[4 * c + 3] = wv[c].w;
+          }
         }
         const uint32_t a_t = lane_t + a * GE::kAColsS + j * kAColsG;
         tmem_st16(a_t, reinterpret_cast<const uint32_t(&)[16]>(v[0]));
         tmem_st16(a_t + 16, reinterpret_cast<const uint32_t(&)[16]>(v[16]));
-        side_w[j * kTileRows] = (sc << 16) | zp;
+        side_w[j * kTileRows] = sz;
       }
       tmem_wait_st();
       tc_fence_before();
@@ -701,7 +704,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
       // A round is one or two steps (two unless the first ends its segment): one wait per issuer (a commit
       // covers everything its thread issued before), GB groups' tensor-memory loads in flight together.
       if (!wait_h(done_a + (t & (DD2 - 1)) * 8, static_cast<uint32_t>(t / DD2) & 1u, p.hint, kSpinLimit)) {
-        GAVE_UP(8, t);
         atomicExch(p.status, W4A16_ETIMEOUT);
         ok = false;
         break;
@@ -709,14 +711,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
       const uint2 e0 = table[t & (kTable - 1)];  // written before the step's weights were requested
       const bool two = !((e0.x >> 17) & 1u) && t + 1 < T;
       if (two && !wait_h(done_a + ((t + 1) & (DD2 - 1)) * 8, static_cast<uint32_t>((t + 1) / DD2) & 1u, p.hint, kSpinLimit)) {
-        GAVE_UP(9, t);
         atomicExch(p.status, W4A16_ETIMEOUT);
         ok = false;
         break;
       }
-#ifdef W4A16_TRACE
-      if (tid == 0 && t == 0) TL(4);
-#endif
       tc_fence_after();
       const uint2 e1 = two ? table[(t + 1) & (kTable - 1)] : e0;
       const int ng0 = static_cast<int>((e0.x >> 16) & 1u) + 1;
@@ -835,7 +833,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
         for (int i = 0; i < TM; ++i) fin[i] = 0.f;
       }
     }
-    if (tid == 0) TL(5);
     if (p.argmax) {
       // ---- fused argmax: thread -> warp -> CTA -> grid, larger value then lower index ----
       const int nfix = 32 * CW * ((M + TM - 1) / TM);  // threads of all active fix-up warps
@@ -907,7 +904,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   // every role ends here: tensor memory goes back only after all its readers and writers are done
   tc_fence_before();
   __syncthreads();
-  if (tid == 0) TL(6);
   if (warp == kWMma) {
     tc_fence_after();
     tmem_dealloc(*reinterpret_cast<volatile uint32_t*>(tmem_slot), kTmemCols);
@@ -947,6 +943,11 @@ const Config& config() {
   return c;
 }
 
+// arrival tickets per (token set, tile, lane quarter) + the argmax ticket, for layers of up to max_out rows
+size_t counter_bytes(int max_out) {
+  return (3 * (static_cast<size_t>(max_out) / kTileRows + 2) * CW + 8) * sizeof(unsigned);
+}
+
 constexpr int kMaxCtasPerSm = 2;  // what the scratch is sized for (the grid itself is one CTA per SM)
 
 int tile_rows() { return kTileRows; }
@@ -964,8 +965,9 @@ int cache_groups_for(int tiles, int G, int grid) {
   return per_cta < G ? per_cta : G;
 }
 
-template <int MT>
+template <int MT, int WB>
 int launch_cfg(SkinnyParams& p, int grid, cudaStream_t st, int smem_optin) {
+  constexpr int kStageBytes = Fmt<WB>::kStage;
   const int groups = cache_groups_for(p.tiles, p.G, grid);
   p.b_bytes = groups * 384 * p.M + 256;
   p.xs_bytes = groups * MT * 8;
@@ -975,10 +977,10 @@ int launch_cfg(SkinnyParams& p, int grid, cudaStream_t st, int smem_optin) {
   // uses would belong to different warps, and a warp that runs ahead could take "the other warp's copy has
   // not landed yet" for "my copy has landed".
   p.depth = config().depth;
-  int smem = total_smem<MT>(p.depth, p.b_bytes, p.xs_bytes);
+  int smem = total_smem<MT>(p.depth, kStageBytes, p.b_bytes, p.xs_bytes);
   while (smem > limit && p.depth > 2) {
     p.depth -= 2;
-    smem = total_smem<MT>(p.depth, p.b_bytes, p.xs_bytes);
+    smem = total_smem<MT>(p.depth, kStageBytes, p.b_bytes, p.xs_bytes);
   }
   if (smem > smem_optin)
     return fail(W4A16_EINVAL, "decode kernel needs %d bytes of shared memory for in_f = %d, M = %d; the device offers %d",
@@ -987,7 +989,7 @@ int launch_cfg(SkinnyParams& p, int grid, cudaStream_t st, int smem_optin) {
   int dev = 0;
   W4_CUDA(cudaGetDevice(&dev));
   if (attr_set[dev & 63] < smem) {
-    W4_CUDA(cudaFuncSetAttribute(k_skinny<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    W4_CUDA(cudaFuncSetAttribute(k_skinny<MT, WB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set[dev & 63] = smem;
   }
   cudaLaunchConfig_t cfg = {};
@@ -1000,22 +1002,48 @@ int launch_cfg(SkinnyParams& p, int grid, cudaStream_t st, int smem_optin) {
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
   cfg.numAttrs = config().pdl ? 1 : 0;
-  W4_CUDA(cudaLaunchKernelEx(&cfg, k_skinny<MT>, p));
+  W4_CUDA(cudaLaunchKernelEx(&cfg, k_skinny<MT, WB>, p));
   return W4A16_OK;
 }
 
 // Most tokens one launch can take: the digit rows of `groups` k groups (384 B per group and token) must
 // fit beside a two-stage weight ring.
-int max_batch(int groups, int smem_optin) {
-  const int fixed = 2 * kStageBytes + kSide * kTileRows * 4 + kTable * 8 + 64 * 8 + 16 + 256;
+int max_batch(int groups, int stage_bytes, int smem_optin) {
+  const int fixed = 2 * stage_bytes + kSide * kTileRows * 4 + kTable * 8 + 64 * 8 + 16 + 256;
   int mb = (smem_optin - fixed) / (groups * (384 + 8));
   if (mb > kMaxBatch) mb = kMaxBatch;
   return mb;
 }
 
-int launch_skinny(SkinnyParams& p, const w4a16_weights_t* w, const uint16_t* x, int M, w4a16_scratch_t* s,
-                  cudaStream_t st) {
+// A validated layer in either weight format, as the launcher sees it.
+struct LayerRef {
+  const uint8_t* stream = nullptr;
+  int out_f = 0, in_f = 0, num_groups = 0, wbits = 4;
+};
+int layer_of(LayerRef& L, const w4a16_weights_t* w) {
   if (int rc = check_weights(w)) return rc;
+  L = LayerRef{reinterpret_cast<const uint8_t*>(w->qweight), w->out_f, w->in_f, w->num_groups, 4};
+  return W4A16_OK;
+}
+int layer_of(LayerRef& L, const w4a16_w8_weights_t* w) {
+  if (int rc = check_w8(w)) return rc;
+  L = LayerRef{reinterpret_cast<const uint8_t*>(w->qweight), w->out_f, w->in_f, w->num_groups, 8};
+  return W4A16_OK;
+}
+
+template <int WB>
+int launch_batch(SkinnyParams& q, int grid, cudaStream_t st, int smem_optin) {
+  if (q.M == 1) return launch_cfg<1, WB>(q, grid, st, smem_optin);
+  if (q.M == 2) return launch_cfg<2, WB>(q, grid, st, smem_optin);
+  if (q.M <= 4) return launch_cfg<4, WB>(q, grid, st, smem_optin);   // token sets (2, M - 2)
+  if (q.M == 5) return launch_cfg<5, WB>(q, grid, st, smem_optin);   // (3, 2)
+  if (q.M == 6) return launch_cfg<6, WB>(q, grid, st, smem_optin);   // (3, 3)
+  if (q.M <= 8) return launch_cfg<8, WB>(q, grid, st, smem_optin);   // (4, M - 4)
+  return launch_cfg<10, WB>(q, grid, st, smem_optin);                // (5, M - 5)
+}
+
+int launch_skinny(SkinnyParams& p, const LayerRef* w, const uint16_t* x, int M, w4a16_scratch_t* s,
+                  cudaStream_t st) {
   W4_REQUIRE(x != nullptr && (reinterpret_cast<uintptr_t>(x) & 15) == 0, "x null or not 16-byte aligned");
   W4_REQUIRE(M >= 1 && M <= 16, "M = %d outside [1,16]", M);
   W4_REQUIRE(s != nullptr && s->xf && s->xgsum && s->partial, "scratch not allocated");
@@ -1023,7 +1051,7 @@ int launch_skinny(SkinnyParams& p, const w4a16_weights_t* w, const uint16_t* x, 
   const DeviceInfo* di = device_info();
   if (!di) return W4A16_ECUDA;
   const int TR = tile_rows();
-  p.stream = reinterpret_cast<const uint8_t*>(w->qweight);
+  p.stream = w->stream;
   p.N = w->out_f;
   p.K = w->in_f;
   p.G = w->num_groups;
@@ -1039,12 +1067,12 @@ int launch_skinny(SkinnyParams& p, const w4a16_weights_t* w, const uint16_t* x, 
   p.mg_grid = magic(grid);
   p.mg_G = magic(p.G);
   if (int rc = w4a16_scratch_check(s, w->out_f, M)) return rc;
-  const int mb = max_batch(cache_groups_for(p.tiles, p.G, grid), di->smem_optin);
+  const int mb = max_batch(cache_groups_for(p.tiles, p.G, grid), w->wbits == 4 ? Fmt<4>::kStage : Fmt<8>::kStage,
+                           di->smem_optin);
   if (mb < 1)
     return fail(W4A16_EINVAL, "in_f = %d is too wide for the decode kernel's activation cache", w->in_f);
   // token batches: one launch for M <= mb, else equal halves (each launch streams the weights once)
   const int nb = (M + mb - 1) / mb;
-  static int launch_counter = 0;
   const SkinnyParams base = p;
   for (int b = 0, m0 = 0; b < nb; ++b) {
     const int m1 = static_cast<int>(static_cast<long long>(M) * (b + 1) / nb);
@@ -1057,15 +1085,8 @@ int launch_skinny(SkinnyParams& p, const w4a16_weights_t* w, const uint16_t* x, 
     for (int r = 0; r < base.npeers; ++r) q.y_peers[r] = base.y_peers[r] + static_cast<size_t>(m0) * base.ldy;
     if (base.ids) q.ids = base.ids + m0;
     if (base.pairs_out) q.pairs_out = static_cast<Pair*>(base.pairs_out) + m0;
-    q.trace_id = launch_counter++;
-    int rc;
-    if (q.M == 1) rc = launch_cfg<1>(q, grid, st, di->smem_optin);
-    else if (q.M == 2) rc = launch_cfg<2>(q, grid, st, di->smem_optin);
-    else if (q.M <= 4) rc = launch_cfg<4>(q, grid, st, di->smem_optin);   // token sets (2, M - 2)
-    else if (q.M == 5) rc = launch_cfg<5>(q, grid, st, di->smem_optin);   // (3, 2)
-    else if (q.M == 6) rc = launch_cfg<6>(q, grid, st, di->smem_optin);   // (3, 3)
-    else if (q.M <= 8) rc = launch_cfg<8>(q, grid, st, di->smem_optin);   // (4, M - 4)
-    else rc = launch_cfg<10>(q, grid, st, di->smem_optin);                // (5, M - 5)
+    const int rc = w->wbits == 4 ? launch_batch<4>(q, grid, st, di->smem_optin)
+                                 : launch_batch<8>(q, grid, st, di->smem_optin);
     if (rc) return rc;
     m0 = m1;
   }
@@ -1077,20 +1098,70 @@ int launch_skinny(SkinnyParams& p, const w4a16_weights_t* w, const uint16_t* x, 
 
 using namespace w4a16;
 
+namespace {
+template <class W>
+int run_gemm(void* y, int y_is_f32, const W* w, const uint16_t* x, int M, w4a16_scratch_t* s, void* stream) {
+  LayerRef L;
+  if (int rc = layer_of(L, w)) return rc;
+  SkinnyParams p = {};
+  p.y = y;
+  p.y_f32 = y_is_f32 ? 1 : 0;
+  p.ldy = L.out_f;
+  return launch_skinny(p, &L, x, M, s, static_cast<cudaStream_t>(stream));
+}
+template <class W>
+int run_argmax(int32_t* ids, uint16_t* logits, void* pairs, int row_offset, const W* w, const uint16_t* x, int M,
+               w4a16_scratch_t* s, void* stream) {
+  W4_REQUIRE(ids != nullptr || pairs != nullptr, "lm_head_argmax: both ids and pairs are null");
+  LayerRef L;
+  if (int rc = layer_of(L, w)) return rc;
+  SkinnyParams p = {};
+  p.y = logits;
+  p.ldy = L.out_f;
+  p.argmax = 1;
+  p.ids = ids;
+  p.pairs_out = pairs;
+  p.row_offset = row_offset;
+  return launch_skinny(p, &L, x, M, s, static_cast<cudaStream_t>(stream));
+}
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------
+// GEMV without any scratch argument and without any allocation, for callers that cannot call
+// cudaMalloc: code that runs after the serving process has handed every remaining byte of HBM
+// to its KV cache, or on a path where the implicit device-wide synchronisation of an allocation
+// is not acceptable. The split-tile partial sums and arrival counters live in this file-scope
+// device array instead; every GPU that loads the library carries it (about 5.3 MB) until exit.
+constexpr int kStaticMaxCtas = 320;     // 2 CTAs x 160 SMs
+constexpr int kStaticMaxOut = 65536;    // widest layer the static scratch serves
+constexpr size_t kStaticPartialBytes = static_cast<size_t>(kStaticMaxCtas) * 2 * kTileRows * 16 * sizeof(float);
+constexpr size_t kStaticCounterBytes = ((kStaticMaxOut / kTileRows + 2) * 8 + 8) * sizeof(unsigned);
+constexpr size_t kStaticPairBytes = static_cast<size_t>(kStaticMaxCtas) * 16 * 8;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticPartialBytes + kStaticCounterBytes + kStaticPairBytes];
+
+namespace {
+// The array's name is only a host-side handle: the device address has to be asked for, once per device
+// and with that device current. The first use on a device does this and clears the counters on `stream`.
+// Guarded: two host threads may make their first call at the same time.
+int static_scratch_base(unsigned char** out, int device, cudaStream_t stream) {
+  static unsigned char* base[64] = {};
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lk(mu);
+  unsigned char* b = base[device & 63];
+  if (!b) {
+    void* p0 = nullptr;
+    W4_CUDA(cudaGetSymbolAddress(&p0, g_static_scratch));
+    b = static_cast<unsigned char*>(p0);
+    W4_CUDA(cudaMemsetAsync(b + kStaticPartialBytes, 0, kStaticCounterBytes, stream));
+    base[device & 63] = b;
+  }
+  *out = b;
+  return W4A16_OK;
+}
+}  // namespace
+
 extern "C" {
 
-#ifdef W4A16_TRACE
-__attribute__((visibility("default"))) int w4a16_debug_where(int* dst) {
-  W4_CUDA(cudaDeviceSynchronize());
-  W4_CUDA(cudaMemcpyFromSymbol(dst, g_where, sizeof(int) * 8));
-  return 0;
-}
-__attribute__((visibility("default"))) int w4a16_debug_timeline(long long* dst, int n) {
-  W4_CUDA(cudaDeviceSynchronize());
-  W4_CUDA(cudaMemcpyFromSymbol(dst, g_tline, sizeof(long long) * n));
-  return 0;
-}
-#endif
 
 int w4a16_scratch_alloc(w4a16_scratch_t* s, int max_in, int max_out, int min_group, int max_m) {
   W4_REQUIRE(s != nullptr, "scratch_alloc: null struct");
@@ -1105,8 +1176,7 @@ int w4a16_scratch_alloc(w4a16_scratch_t* s, int max_in, int max_out, int min_gro
   s->max_splits = di->sms * kMaxCtasPerSm;  // CTAs of the persistent grid
   // two partial tiles per CTA (head and tail of its unit range), widest tile, 16 tokens
   s->partial_elems = static_cast<size_t>(s->max_splits) * 2 * kTileRows * 16;
-  // arrival tickets per (token set, tile, lane quarter) + the argmax ticket
-  const size_t counters = (3 * (static_cast<size_t>(max_out) / kTileRows + 2) * CW + 8) * sizeof(unsigned);
+  const size_t counters = counter_bytes(max_out);
   const size_t pairs = static_cast<size_t>(s->max_splits) * 16 * sizeof(Pair);
   void *xf = nullptr, *cn = nullptr, *pa = nullptr;
   cudaError_t e = cudaMalloc(&xf, pairs);
@@ -1161,36 +1231,43 @@ int w4a16_choose_splits(int out_f, int num_groups) {
   return s < 1 ? 1 : s;
 }
 
+int w4a16_scratch_reset(w4a16_scratch_t* s, void* stream) {
+  W4_REQUIRE(s != nullptr && s->xgsum != nullptr, "scratch_reset: scratch not allocated");
+  W4_CUDA(cudaMemsetAsync(s->xgsum, 0, counter_bytes(s->max_out), static_cast<cudaStream_t>(stream)));
+  return W4A16_OK;
+}
+
 int w4a16_gemv(void* y, int y_is_f32, const w4a16_weights_t* w, const uint16_t* x, w4a16_scratch_t* s,
                void* stream) {
   W4_REQUIRE(y != nullptr, "gemv: y is null");
-  SkinnyParams p = {};
-  p.y = y;
-  p.y_f32 = y_is_f32 ? 1 : 0;
-  p.ldy = w ? w->out_f : 0;
-  return launch_skinny(p, w, x, 1, s, static_cast<cudaStream_t>(stream));
+  return run_gemm(y, y_is_f32, w, x, 1, s, stream);
 }
 
 int w4a16_gemm_skinny(uint16_t* y, const w4a16_weights_t* w, const uint16_t* x, int M, w4a16_scratch_t* s,
                       void* stream) {
   W4_REQUIRE(y != nullptr, "gemm_skinny: y is null");
-  SkinnyParams p = {};
-  p.y = y;
-  p.ldy = w ? w->out_f : 0;
-  return launch_skinny(p, w, x, M, s, static_cast<cudaStream_t>(stream));
+  return run_gemm(y, 0, w, x, M, s, stream);
 }
 
 int w4a16_lm_head_argmax(int32_t* ids, uint16_t* logits, void* pairs, int row_offset, const w4a16_weights_t* w,
                          const uint16_t* x, int M, w4a16_scratch_t* s, void* stream) {
-  W4_REQUIRE(ids != nullptr || pairs != nullptr, "lm_head_argmax: both ids and pairs are null");
-  SkinnyParams p = {};
-  p.y = logits;
-  p.ldy = w ? w->out_f : 0;
-  p.argmax = 1;
-  p.ids = ids;
-  p.pairs_out = pairs;
-  p.row_offset = row_offset;
-  return launch_skinny(p, w, x, M, s, static_cast<cudaStream_t>(stream));
+  return run_argmax(ids, logits, pairs, row_offset, w, x, M, s, stream);
+}
+
+int w4a16_w8_gemv(uint16_t* y, const w4a16_w8_weights_t* w, const uint16_t* x, w4a16_scratch_t* s, void* stream) {
+  W4_REQUIRE(y != nullptr, "w8_gemv: y is null");
+  return run_gemm(y, 0, w, x, 1, s, stream);
+}
+
+int w4a16_w8_gemm_skinny(uint16_t* y, const w4a16_w8_weights_t* w, const uint16_t* x, int M, w4a16_scratch_t* s,
+                         void* stream) {
+  W4_REQUIRE(y != nullptr, "w8_gemm_skinny: y is null");
+  return run_gemm(y, 0, w, x, M, s, stream);
+}
+
+int w4a16_w8_lm_head_argmax(int32_t* ids, uint16_t* logits, void* pairs, int row_offset, const w4a16_w8_weights_t* w,
+                            const uint16_t* x, int M, w4a16_scratch_t* s, void* stream) {
+  return run_argmax(ids, logits, pairs, row_offset, w, x, M, s, stream);
 }
 
 int w4a16_argmax_pairs_reduce(int32_t* ids, const void* pairs, int nranks, int M, void* stream) {
@@ -1201,19 +1278,6 @@ int w4a16_argmax_pairs_reduce(int32_t* ids, const void* pairs, int nranks, int M
   return W4A16_OK;
 }
 
-// ---------------------------------------------------------------------------------------------
-// GEMV without any scratch argument and without any allocation, for callers that cannot call
-// cudaMalloc: code that runs after the serving process has handed every remaining byte of HBM
-// to its KV cache, or on a path where the implicit device-wide synchronisation of an allocation
-// is not acceptable. The split-tile partial sums and arrival counters live in this file-scope
-// device array instead; every GPU that loads the library carries it (about 5.3 MB) until exit.
-constexpr int kStaticMaxCtas = 320;     // 2 CTAs x 160 SMs
-constexpr int kStaticMaxOut = 65536;    // widest layer the static scratch serves
-constexpr size_t kStaticPartialBytes = static_cast<size_t>(kStaticMaxCtas) * 2 * kTileRows * 16 * sizeof(float);
-constexpr size_t kStaticCounterBytes = ((kStaticMaxOut / kTileRows + 2) * 8 + 8) * sizeof(unsigned);
-constexpr size_t kStaticPairBytes = static_cast<size_t>(kStaticMaxCtas) * 16 * 8;
-static __device__ __align__(256) unsigned char g_static_scratch[kStaticPartialBytes + kStaticCounterBytes + kStaticPairBytes];
-
 int w4a16_gemv_static(void* y, int y_is_f32, const w4a16_weights_t* w, const uint16_t* x, void* stream) {
   W4_REQUIRE(y != nullptr, "gemv_static: y is null");
   W4_REQUIRE(w != nullptr, "gemv_static: null weights");
@@ -1223,18 +1287,10 @@ int w4a16_gemv_static(void* y, int y_is_f32, const w4a16_weights_t* w, const uin
   if (!di) return W4A16_ECUDA;
   W4_REQUIRE(di->sms * kMaxCtasPerSm <= kStaticMaxCtas, "gemv_static: %d SMs exceed the static scratch limit of %d CTAs",
              di->sms, kStaticMaxCtas);
-  // The array's name is only a host-side handle: the device address has to be asked for, once
-  // per device and with that device current. The first call on a device does this (and clears the
-  // counters), so it should come before any stream capture.
-  static unsigned char* base[64] = {};
-  unsigned char* b = base[di->device & 63];
-  if (!b) {
-    void* p0 = nullptr;
-    W4_CUDA(cudaGetSymbolAddress(&p0, g_static_scratch));
-    b = static_cast<unsigned char*>(p0);
-    W4_CUDA(cudaMemsetAsync(b + kStaticPartialBytes, 0, kStaticCounterBytes, static_cast<cudaStream_t>(stream)));
-    base[di->device & 63] = b;
-  }
+  // The first call on a device looks the array up (and clears its counters), so it should come before any
+  // stream capture.
+  unsigned char* b = nullptr;
+  if (int rc = static_scratch_base(&b, di->device, static_cast<cudaStream_t>(stream))) return rc;
   w4a16_scratch_t s = {};
   s.partial = reinterpret_cast<float*>(b);
   s.xgsum = reinterpret_cast<float*>(b + kStaticPartialBytes);
@@ -1243,11 +1299,16 @@ int w4a16_gemv_static(void* y, int y_is_f32, const w4a16_weights_t* w, const uin
   s.max_splits = kStaticMaxCtas;
   s.max_m = 1;
   s.partial_elems = kStaticPartialBytes / sizeof(float);
-  SkinnyParams p = {};
-  p.y = y;
-  p.y_f32 = y_is_f32 ? 1 : 0;
-  p.ldy = w->out_f;
-  return launch_skinny(p, w, x, 1, &s, static_cast<cudaStream_t>(stream));
+  return run_gemm(y, y_is_f32, w, x, 1, &s, stream);
+}
+
+int w4a16_gemv_static_reset(void* stream) {
+  const DeviceInfo* di = device_info();
+  if (!di) return W4A16_ECUDA;
+  unsigned char* b = nullptr;
+  if (int rc = static_scratch_base(&b, di->device, static_cast<cudaStream_t>(stream))) return rc;
+  W4_CUDA(cudaMemsetAsync(b + kStaticPartialBytes, 0, kStaticCounterBytes, static_cast<cudaStream_t>(stream)));
+  return W4A16_OK;
 }
 
 int w4a16_shard_rows(int out_f, int nranks, int rank, int* row_begin, int* row_end) {
@@ -1269,7 +1330,8 @@ int w4a16_gemm_skinny_sharded(uint16_t* const* y_peers, int nranks, int rank, in
   W4_REQUIRE(y_peers != nullptr, "gemm_skinny_sharded: null peer table");
   if (nranks < 1 || nranks > 8 || rank < 0 || rank >= nranks)
     return fail(W4A16_ECOMM, "gemm_skinny_sharded: rank %d of %d (1..8 ranks)", rank, nranks);
-  W4_REQUIRE(w_shard != nullptr, "gemm_skinny_sharded: null weights");
+  LayerRef L;
+  if (int rc = layer_of(L, w_shard)) return rc;
   if (row_begin < 0 || row_begin % kRowGranule != 0 || row_begin + w_shard->out_f > out_f_total)
     return fail(W4A16_ECOMM, "gemm_skinny_sharded: rows [%d,%d) outside [0,%d)", row_begin,
                 row_begin + w_shard->out_f, out_f_total);
@@ -1282,7 +1344,7 @@ int w4a16_gemm_skinny_sharded(uint16_t* const* y_peers, int nranks, int rank, in
   for (int r = 0; r < nranks; ++r)
     if (r != rank) p.y_peers[q++] = y_peers[r];
   p.npeers = q;
-  return launch_skinny(p, w_shard, x, M, s, static_cast<cudaStream_t>(stream));
+  return launch_skinny(p, &L, x, M, s, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

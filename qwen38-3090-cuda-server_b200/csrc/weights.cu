@@ -138,6 +138,18 @@ __global__ void k_dequant_rows(uint16_t* __restrict__ dst, const uint8_t* __rest
   }
 }
 
+// A wait that nothing satisfies: the same bounded mbarrier wait the kernels use, on a barrier nobody
+// arrives at. It gives up after `polls` tests, reports through the status word and the kernel returns.
+__global__ void k_wait_timeout_selftest(int* status, uint32_t polls) {
+  __shared__ uint64_t bar;
+  const uint32_t bar_a = smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    mbar_init(bar_a, 1);
+    fence_mbar_init();
+    if (!mbar_wait_bounded(bar_a, 0, polls)) atomicExch(status, W4A16_ETIMEOUT);
+  }
+}
+
 int grid_for(long long n, int block) {
   long long g = (n + block - 1) / block;
   return static_cast<int>(g < 1 ? 1 : (g > 65535 * 16 ? 65535 * 16 : g));
@@ -177,6 +189,22 @@ int w4a16_device_status(void) {
   return v;
 }
 
+int w4a16_device_status_clear(void) {
+  const int zero = 0;
+  W4_CUDA(cudaDeviceSynchronize());
+  W4_CUDA(cudaMemcpyToSymbol(g_status_word, &zero, sizeof(int)));
+  return W4A16_OK;
+}
+
+int w4a16_selftest_wait_timeout(int polls, void* stream) {
+  W4_REQUIRE(polls >= 1 && polls <= 4096, "selftest_wait_timeout: polls = %d outside [1,4096]", polls);
+  const DeviceInfo* di = device_info();
+  if (!di) return W4A16_ECUDA;
+  k_wait_timeout_selftest<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(di->status, static_cast<uint32_t>(polls));
+  W4_CUDA(cudaGetLastError());
+  return W4A16_OK;
+}
+
 int w4a16_weights_alloc(w4a16_weights_t* w, int out_f, int in_f, int group_size, void* stream) {
   W4_REQUIRE(w != nullptr, "weights_alloc: null struct");
   W4_REQUIRE(group_size == kGroup, "weights_alloc: group_size %d unsupported (only 128)", group_size);
@@ -204,8 +232,9 @@ int w4a16_weights_alloc(w4a16_weights_t* w, int out_f, int in_f, int group_size,
     return fail(W4A16_ECUDA, "weights_alloc(%d x %d): %s", out_f, in_f, cudaGetErrorString(e));
   }
   if (out_f % kTileRows != 0) {
-    // rows of the last tile past out_f: zero scales, so they contribute nothing and are never stored
-    e = cudaMemset(q, 0, qb);
+    // rows of the last tile past out_f: zero scales, so they contribute nothing and are never stored.
+    // On the caller's stream, so that it is ordered before the repack that follows on that stream.
+    e = cudaMemsetAsync(q, 0, qb, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) {
       cudaFree(q);
       cudaFree(s);

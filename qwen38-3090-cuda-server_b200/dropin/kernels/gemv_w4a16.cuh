@@ -1,7 +1,7 @@
 // Drop-in replacement for src/kernels/gemv_w4a16.cuh of the reference server.
 //
 // Same namespace, struct fields and launcher signatures as the reference header
-// (src/kernels/gemv_w4a16.cuh:50-60,64-69,85-90,94-110,124-135,187-188), so that
+// (src/kernels/gemv_w4a16.cuh:50-60,64-69,85-90,94-110,124-135,148-166,187-188), so that
 // src/model, src/spec, src/draft and the reference's own gates compile against it
 // unchanged. Every launcher is a thin inline shim over the C ABI of
 // libw4a16_b200.so (include/w4a16_b200.h); a non-zero status becomes the
@@ -11,7 +11,8 @@
 //   * the three weight buffers stay independent cudaFree-able allocations, but the
 //     whole weight stream lives behind `qweight`; `scale` and `zp` are placeholders;
 //   * gemm_small_w4a16 and gemm_mma_w4a16 are the same kernel;
-//   * lm_head_argmax_w4a16 is new: GEMV / skinny GEMM with the argmax fused in;
+//   * lm_head_argmax_w4a16 / lm_head_argmax_w8a16 are new: GEMV / skinny GEMM with the argmax fused in;
+//   * W8A16Weights keeps both pointers as independent allocations, the int8 stream lives behind `qweight`;
 //   * group_size must be 128 (the only size the served checkpoint uses).
 #pragma once
 #include <cuda_bf16.h>
@@ -122,6 +123,49 @@ inline void lm_head_argmax_w4a16(int32_t* ids, const W4A16Weights& w, const __nv
   detail::check(w4a16_lm_head_argmax(ids, reinterpret_cast<uint16_t*>(logits), nullptr, 0, detail::cw(w),
                                      reinterpret_cast<const uint16_t*>(x), M, detail::cs(s), stream),
                 "lm_head_argmax_w4a16");
+}
+
+// ---- INT8 g128 lm_head (src/kernels/gemv_w4a16.cuh:148-166) ----
+struct W8A16Weights {
+  int8_t*        qweight = nullptr;   // private int8 stream (codes and scales per 128-row x 128-k block)
+  __nv_bfloat16* scale   = nullptr;   // placeholder allocation: freed by the caller like the reference's
+  int out_f = 0, in_f = 0, group_size = 0, num_groups = 0;
+  size_t total_bytes() const {
+    return size_t(out_f) * in_f + size_t(out_f) * num_groups * 2;
+  }
+};
+
+namespace detail {
+static_assert(sizeof(W8A16Weights) == sizeof(w4a16_w8_weights_t), "W8A16Weights must mirror w4a16_w8_weights_t");
+inline w4a16_w8_weights_t* cw8(W8A16Weights& w) { return reinterpret_cast<w4a16_w8_weights_t*>(&w); }
+inline const w4a16_w8_weights_t* cw8(const W8A16Weights& w) { return reinterpret_cast<const w4a16_w8_weights_t*>(&w); }
+}  // namespace detail
+
+inline void quantize_w8a16(W8A16Weights& dst, const __nv_bfloat16* src, int out_f, int in_f, int group_size,
+                           cudaStream_t stream = 0) {
+  detail::check(w4a16_w8_quantize(detail::cw8(dst), reinterpret_cast<const uint16_t*>(src), out_f, in_f, group_size,
+                                  stream),
+                "quantize_w8a16");
+}
+inline void gemv_w8a16(__nv_bfloat16* y, const W8A16Weights& w, const __nv_bfloat16* x, GemvScratch& s,
+                       cudaStream_t stream = 0) {
+  detail::check(w4a16_w8_gemv(reinterpret_cast<uint16_t*>(y), detail::cw8(w), reinterpret_cast<const uint16_t*>(x),
+                              detail::cs(s), stream),
+                "gemv_w8a16");
+}
+inline void gemm_small_w8a16(__nv_bfloat16* y, const W8A16Weights& w, const __nv_bfloat16* x, int M, GemvScratch& s,
+                             cudaStream_t stream = 0) {
+  detail::check(w4a16_w8_gemm_skinny(reinterpret_cast<uint16_t*>(y), detail::cw8(w),
+                                     reinterpret_cast<const uint16_t*>(x), M, detail::cs(s), stream),
+                "gemm_small_w8a16");
+}
+inline void w8a16_free(W8A16Weights& w) { detail::check(w4a16_w8_free(detail::cw8(w)), "w8a16_free"); }
+// New: the INT8 lm_head with the argmax fused in (same contract as lm_head_argmax_w4a16).
+inline void lm_head_argmax_w8a16(int32_t* ids, const W8A16Weights& w, const __nv_bfloat16* x, int M,
+                                 GemvScratch& s, __nv_bfloat16* logits = nullptr, cudaStream_t stream = 0) {
+  detail::check(w4a16_w8_lm_head_argmax(ids, reinterpret_cast<uint16_t*>(logits), nullptr, 0, detail::cw8(w),
+                                        reinterpret_cast<const uint16_t*>(x), M, detail::cs(s), stream),
+                "lm_head_argmax_w8a16");
 }
 
 }  // namespace qwen

@@ -4,7 +4,8 @@
     python shape_bench.py --case gemv:17408x5120:1 [--case skinny:34816x5120:9 ...]
                           [--iters 50] [--ring-mb 768] [--json out.json]
 
-case = kind:NxK:M with kind in {gemv, skinny, lmhead, prefill}. Each case cycles through a ring of
+case = kind:NxK:M with kind in {gemv, skinny, lmhead, prefill} for the int4 weights and
+{gemv8, skinny8, lmhead8} for the int8 lm_head variant. Each case cycles through a ring of
 distinct weight copies whose total size exceeds `--ring-mb` (several times the 126 MB L2),
 so every launch streams its weights from HBM. The launches are captured back to back into
 one CUDA graph (as the decode step is) and timed with CUDA events; the figure is the mean
@@ -19,25 +20,31 @@ import json
 import os
 import sys
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 PKG = "qwen38-3090-cuda-server_b200"
 
 
 def run_case(pkg, synth, torch, kind, N, K, M, iters, ring_mb, warmup=5, graph=True):
     G = K // 128
-    wbytes = N * K // 2 + N * G * 3
+    w8 = kind.endswith("8")
+    wbytes = (N * K + N * G * 2) if w8 else (N * K // 2 + N * G * 3)
     copies = max(1, min(64, -(-ring_mb * (1 << 20) // wbytes))) if ring_mb > 0 else 1
     if kind == "prefill":
         copies = 1  # compute bound: one weight copy
     gen = torch.Generator(device="cuda").manual_seed(N * 31 + K)
     ws = []
-    for _ in range(copies):
+    for _ in range(copies if not w8 else 0):
         packed = torch.randint(-2 ** 31, 2 ** 31 - 1, (N, K // 8), dtype=torch.int32, device="cuda", generator=gen)
         scale = (torch.randn((N, G), device="cuda", generator=gen).abs() * 0.02 + 1e-4).to(torch.bfloat16)
         zp = torch.randint(-2 ** 31, 2 ** 31 - 1, (N // 8, G), dtype=torch.int32, device="cuda", generator=gen)
         ws.append(pkg.awq_repack(packed, scale, zp))
         del packed, scale, zp
+    for _ in range(copies if w8 else 0):
+        src = (torch.randn((N, K), device="cuda", generator=gen) * 0.02).to(torch.bfloat16)
+        ws.append(pkg.quantize_w8a16(src))
+        torch.cuda.synchronize()
+        del src
     x = torch.randn((M, K), device="cuda", generator=gen).to(torch.bfloat16)
     y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
     ids = torch.zeros(M, dtype=torch.int32, device="cuda")
@@ -54,6 +61,12 @@ def run_case(pkg, synth, torch, kind, N, K, M, iters, ring_mb, warmup=5, graph=T
             pkg.lm_head_argmax(ids, w, x, M, s)
         elif kind == "prefill":
             pkg.gemm_w4a16(y, w, x, M, gws)
+        elif kind == "gemv8":
+            pkg.gemv_w8a16(y, w, x, s)
+        elif kind == "skinny8":
+            pkg.gemm_small_w8a16(y, w, x, M, s)
+        elif kind == "lmhead8":
+            pkg.lm_head_argmax_w8(ids, w, x, M, s)
         else:
             raise SystemExit(f"unknown kind {kind}")
 
@@ -83,12 +96,15 @@ def run_case(pkg, synth, torch, kind, N, K, M, iters, ring_mb, warmup=5, graph=T
         e1.record()
         torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / iters
-    out_bytes = 4 * M if kind == "lmhead" else 2 * M * N
-    alg = synth.algorithmic_bytes(N, K, M, out_bytes=out_bytes)
+    out_bytes = 4 * M if kind.startswith("lmhead") else 2 * M * N
+    if w8:  # int8 codes + bf16 scales + activations in + output
+        alg = N * K + 2 * N * G + 2 * M * K + out_bytes
+    else:
+        alg = synth.algorithmic_bytes(N, K, M, out_bytes=out_bytes)
     status = pkg.device_status()
     pkg.gemv_scratch_free(s)
     for w in ws:
-        pkg.awq_free(w)
+        pkg.w8a16_free(w) if w8 else pkg.awq_free(w)
     if gws is not None:
         pkg.gemm_workspace_free(gws)
     return {"kind": kind, "N": N, "K": K, "M": M, "us": us, "algorithmic_bytes": alg,

@@ -53,7 +53,9 @@ def solve_cell(q, deq):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    here = os.path.dirname(os.path.abspath(__file__))
+    default = os.environ.get("W4A16_REFERENCE_DIR") or os.path.join(here, "..", "..", "..", "reference")
+    ref = sys.argv[1] if len(sys.argv) > 1 else default
     fx = os.path.join(ref, "tests", "fixtures", "dequant")
     man = json.load(open(os.path.join(fx, "manifest.json")))
     gs = man["group_size"]

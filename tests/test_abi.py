@@ -37,6 +37,10 @@ def test_host_side_argument_errors_need_no_gpu(pkg):
     assert L.w4a16_shard_rows(5120, 8, 8, ctypes.byref(b), ctypes.byref(e)) == -5   # rank out of range
     assert L.w4a16_shard_rows(5136, 8, 0, ctypes.byref(b), ctypes.byref(e)) == -5   # not whole blocks
     assert L.w4a16_gemv(None, 0, None, None, None, None) == -1
+    w8 = pkg.W8Weights()
+    assert L.w4a16_w8_quantize(ctypes.byref(w8), None, 128, 512, 128, None) == -1   # null source
+    assert L.w4a16_w8_gemv(None, None, None, None, None) == -1
+    assert L.w4a16_selftest_wait_timeout(0, None) == -1
 
 
 def test_struct_layouts_match_header(pkg):
@@ -44,3 +48,4 @@ def test_struct_layouts_match_header(pkg):
     assert ctypes.sizeof(pkg.Weights) == 40
     assert ctypes.sizeof(pkg.Scratch) == 56
     assert ctypes.sizeof(pkg.Workspace) == 32
+    assert ctypes.sizeof(pkg.W8Weights) == 32   # 2 pointers + 4 ints

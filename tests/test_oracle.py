@@ -4,7 +4,10 @@ import os
 import numpy as np
 import pytest
 
-REF_FIXTURES = "/root/reference/tests/fixtures/dequant"
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+# the reference checkout: W4A16_REFERENCE_DIR, else a directory named "reference" beside this repository
+REFERENCE = os.environ.get("W4A16_REFERENCE_DIR") or os.path.join(os.path.dirname(ROOT), "reference")
+REF_FIXTURES = os.path.join(REFERENCE, "tests", "fixtures", "dequant")
 
 
 def test_golden_has_all_reference_tensors(golden):
@@ -126,6 +129,44 @@ def test_quantizer_round_trip(oracle, synth):
     assert np.all(np.abs(deq - synth.bf16_bits_to_f32(src)) <= 0.5 * s * 1.02 + 16 * s * 2 ** -8)
     q = oracle.unpack_q(packed)
     assert q.min() == -8 and q.max() == 7
+
+
+def test_w8_quantizer_properties(oracle, synth):
+    # src/kernels/gemv_w4a16.cu:479-499 of the reference: symmetric int8 per group of 128
+    rng = np.random.default_rng(10)
+    v = rng.standard_normal((32, 384)).astype(np.float32) * 0.03
+    v[3, 128:256] = 0.0           # an all-zero group: scale 0, codes 0
+    src = synth.f32_to_bf16_bits(v)
+    q, scale = oracle.quant_w8(src, 128)
+    f = synth.bf16_bits_to_f32(src)
+    assert q.min() >= -127 and q.max() <= 127
+    assert np.all(q[3, 128:256] == 0) and scale[3, 1] == 0
+    g = f.reshape(32, 3, 128)
+    mx = np.abs(g).max(axis=2)
+    # the largest element of every non-zero group maps to +-127, the scale is bf16(max/127)
+    assert np.all(np.abs(q.reshape(32, 3, 128)).max(axis=2)[mx > 0] == 127)
+    assert np.array_equal(scale, synth.f32_to_bf16_bits((mx / np.float32(127.0)).astype(np.float32)))
+    # codes are rn(v * (127/max)) in fp32, recomputed here with numpy's fp32 arithmetic
+    inv = np.where(mx > 0, np.float32(127.0) / np.where(mx > 0, mx, 1).astype(np.float32), np.float32(0)).astype(np.float32)
+    want = np.clip(np.rint(g * inv[:, :, None]), -127, 127).astype(np.int8).reshape(32, 384)
+    assert np.array_equal(q, want)
+    # round trip: |q*s - v| <= s/2 plus the bf16 rounding of the scale
+    s = np.repeat(synth.bf16_bits_to_f32(scale), 128, axis=1)
+    assert np.all(np.abs(q * s - f) <= 0.5 * s * 1.01 + 127 * s * 2 ** -8)
+
+
+def test_w8_gemm_f64_equals_numpy(oracle, synth):
+    src = synth.make_activations(96, 512, seed=12, sigma=0.05)
+    q, scale = oracle.quant_w8(src)
+    x = synth.make_activations(4, 512, seed=13)
+    w = q.astype(np.float64) * np.repeat(synth.bf16_bits_to_f32(scale).astype(np.float64), 128, axis=1)
+    want = synth.bf16_bits_to_f32(x).astype(np.float64) @ w.T
+    got = oracle.gemm_w8_f64(q, scale, x)
+    assert np.allclose(got, want, rtol=1e-12, atol=1e-12)
+    rows = np.array([0, 50, 95], np.int64)
+    assert np.array_equal(oracle.gemm_w8_f64(q, scale, x, rows=rows), got[:, rows])
+    ids, gaps, logits = oracle.argmax_with_gaps(got)
+    assert np.array_equal(ids, oracle.argmax_bf16(logits)) and np.all(gaps >= 0)
 
 
 def test_synthetic_config_totals(synth):
