@@ -36,9 +36,14 @@
 //       fix-up      4 warps    tcgen05.ld of the int32 sums, the fp32 step above, the split-tile
 //                  (+4)        reduction, output / fused argmax; for M >= 3 a second warp per lane
 //                              quarter takes half of the tokens
-//       converters  9 warps    after griddepcontrol.wait: bf16 x -> digit rows of the B operand, once per
-//                  (+fix-up)   CTA, for exactly the k groups it multiplies; issuers start on a group as
-//                              soon as its rows are in
+//       converters  9 warps    M = 1 only; after griddepcontrol.wait: bf16 x -> digit rows of the B operand,
+//                  (+fix-up)   once per CTA, for exactly the k groups it multiplies; issuers start on a
+//                              group as soon as its rows are in
+//   * M >= 2 (verify blocks): the digit rows are made ONCE per call by a small pre-pass kernel
+//     (k_digits) into the scratch and every CTA streams the rows of the groups it multiplies through
+//     a second ring of bulk copies (they come from L2), instead of 148 identical conversions of M
+//     tokens and a cache of M x K digit bytes per CTA. 3 M <= 48 rows of B: one launch for every
+//     M <= 16. The converter warps become more fix-up warps (up to three token sets).
 #include <cfloat>
 #include <climits>
 #include <cstdlib>
@@ -74,23 +79,24 @@ constexpr int kFixBar = 1;                 // named barrier of the fix-up warps
 constexpr int kTmemCols = 512;             // all of tensor memory; the next launch's CTA, resident beside this one,
                                            // gets it when this CTA exits (it cannot multiply before that anyway)
 constexpr int kAColsG = 32;                // 128 int8 along k = 32 columns of 32 bits per group
-constexpr int kMaxBatch = 10;              // tokens per launch; larger M runs as two launches
 
 
 // Per token-count geometry. N = rows of the B operand the tensor core reads (3 digit rows per token are
 // real). Ring depths are in steps: AD2 for A, DD2 for D and for the ring of "step done" barriers.
-template <int MT>
+template <int MT, bool ST>
 struct Geo {
-  static constexpr int N = MT <= 5 ? 16 : 32;
-  static constexpr int AD2 = 4;
+  static constexpr int N = MT <= 5 ? 16 : (MT <= 10 ? 32 : 48);
+  static constexpr int AD2 = N == 48 ? 2 : 4;
   static constexpr int DD2 = N == 16 ? 8 : 4;
+  static constexpr bool kStream = ST;  // digit rows streamed from the pre-pass output instead of converted here
+  static_assert(ST || MT == 1, "only the M = 1 kernel converts activations itself");
   static constexpr int kAColsS = kStepGroups * kAColsG;  // A columns per step
   static constexpr int kDColsS = kStepGroups * N;        // D columns per step
   static constexpr int kDCol0 = AD2 * kAColsS;           // first D column
   static constexpr int GB = MT == 1 ? 4 : (MT == 2 ? 2 : 1);  // groups whose tensor-memory loads are in flight together
-  // fix-up warps per lane quarter: two token sets for M >= 3 (three were slower). The launcher picks MT so
-  // that the sets are balanced: TM = ceil(M / 2).
-  static constexpr int FW = MT <= 1 ? 1 : 2;
+  // fix-up warps per lane quarter: two token sets from M = 2, three from M = 9 (the fix-up is latency-bound
+  // per token). The launcher picks MT so that the sets are balanced: TM = ceil(MT / FW).
+  static constexpr int FW = MT <= 1 ? 1 : (MT <= 8 ? 2 : 3);
   static constexpr int TM = (MT + FW - 1) / FW;               // tokens per fix-up warp
   static_assert(kDCol0 + DD2 * kDColsS <= kTmemCols, "tensor memory budget");
   static_assert(AD2 <= DD2 && 2 <= DD2 / 2, "ring depths");
@@ -105,8 +111,12 @@ struct SkinnyParams {
   long long ldy;  // elements between rows of y
   int y_col0;     // first column of this launch's rows inside y
   int M, N, K, G, tiles;
-  int b_bytes;       // bytes of the B region (digit rows of the groups this CTA multiplies)
-  int xs_bytes;      // bytes of the (sum, 2^-p) region
+  int b_bytes;       // bytes of the B region (M = 1: digit rows of the groups this CTA multiplies; else the digit ring)
+  int xs_bytes;      // bytes of the (sum, 2^-p) region (M = 1)
+  const uint8_t* dig;  // M >= 2: pre-pass output, db_bytes per k group: [8 chunks of 16 k][3 M digit rows] 16 B, then M x (sum, 2^-p)
+  int db_bytes;
+  int bdepth;        // M >= 2: steps in the digit ring (a power of two)
+  int bshift;        //         and its log2
   unsigned long long mg_grid, mg_G;  // ceil(2^40 / d) for d = gridDim.x and G: exact division by multiply
   uint32_t hint;     // suspend-time hint of the mbarrier waits, ns
   int depth;         // weight ring stages
@@ -229,6 +239,12 @@ __device__ __forceinline__ void umma_s8_ts(uint32_t d_tmem, uint32_t a_tmem, uin
       "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld1(uint32_t taddr, uint32_t* d) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(d[0]) : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld2(uint32_t taddr, uint32_t* d) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0,%1}, [%2];" : "=r"(d[0]), "=r"(d[1]) : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t* d) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
                : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
@@ -248,6 +264,21 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* d) {
         "=r"(d[9]), "=r"(d[10]), "=r"(d[11]), "=r"(d[12]), "=r"(d[13]), "=r"(d[14]), "=r"(d[15])
       : "r"(taddr)
       : "memory");
+}
+// Columns [C0, C0 + CNT) of this thread's lane, relative to `base`, as the fewest loads whose start column is
+// a multiple of their own width (the completion is awaited once, by the caller, for all of them).
+template <int C0, int CNT>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t base, uint32_t* d) {
+  if constexpr (CNT > 0) {
+    constexpr int W = (C0 % 16 == 0 && CNT >= 16) ? 16 : (C0 % 8 == 0 && CNT >= 8) ? 8 : (C0 % 4 == 0 && CNT >= 4) ? 4
+                      : (C0 % 2 == 0 && CNT >= 2) ? 2 : 1;
+    if constexpr (W == 16) tmem_ld16(base + C0, d);
+    else if constexpr (W == 8) tmem_ld8(base + C0, d);
+    else if constexpr (W == 4) tmem_ld4(base + C0, d);
+    else if constexpr (W == 2) tmem_ld2(base + C0, d);
+    else tmem_ld1(base + C0, d);
+    tmem_ld_cols<C0 + W, CNT - W>(base, d + W);
+  }
 }
 // Ticket counter with release + acquire in one operation: the partial rows written before it (by the whole
 // warp, ordered by __syncwarp) are visible to whoever draws a later ticket, and whoever draws the last one
@@ -274,14 +305,14 @@ __device__ __forceinline__ float small_int_to_float(uint32_t v) {
 // use as consecutive 16-byte rows (an 8-row core matrix every 128 bytes). The rows the tensor core reads
 // beyond them are the next chunk's bytes: they only produce accumulator columns nobody reads, and the
 // whole K range of a token fits: 384 bytes per group for M = 1.
-template <int MT>
-__host__ __device__ constexpr int bar_count(int depth) {
-  return 2 * depth + Geo<MT>::AD2 + 2 * Geo<MT>::DD2 + 2;
+template <int MT, bool ST>
+__host__ __device__ constexpr int bar_count(int depth, int bdepth) {
+  return 2 * depth + Geo<MT, ST>::AD2 + 2 * Geo<MT, ST>::DD2 + 2 + (ST ? 2 * bdepth : 0);
 }
-template <int MT>
-__host__ __device__ inline int total_smem(int depth, int stage_bytes, int b_bytes, int xs_bytes) {
+template <int MT, bool ST>
+__host__ __device__ inline int total_smem(int depth, int stage_bytes, int b_bytes, int xs_bytes, int bdepth) {
   return depth * stage_bytes + b_bytes + kSide * kTileRows * 4 + xs_bytes + kTable * 8 + 256 * 4 +
-         bar_count<MT>(depth) * 8 + 16;
+         bar_count<MT, ST>(depth, bdepth) * 8 + 16;
 }
 
 // One token's 128 values of one k group (this lane: k = 4 lane .. 4 lane + 3, `rv`) -> three int8 digit
@@ -324,11 +355,12 @@ __device__ __forceinline__ void convert_group(uint2 rv, uint8_t* bslot, int lbo,
   if (lane == 0) *xs = make_float2(static_cast<float>(tot), inv);
 }
 
-template <int MT, int WB>
+template <int MT, int WB, bool ST>
 __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
-  using GE = Geo<MT>;
+  using GE = Geo<MT, ST>;
   constexpr int kBlock = Fmt<WB>::kBlock, kStageBytes = Fmt<WB>::kStage;
   constexpr int N = GE::N, AD2 = GE::AD2, DD2 = GE::DD2;
+  constexpr bool kStream = GE::kStream;
   constexpr int SLOT = kTileRows * MT;  // floats per partial tile
   extern __shared__ __align__(128) uint8_t smem[];
 
@@ -340,7 +372,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   uint2* table = reinterpret_cast<uint2*>(xsinv + p.xs_bytes);
   uint32_t* ready = reinterpret_cast<uint32_t*>(table + kTable);  // [slot]: tokens whose digit rows are written
   uint64_t* bars = reinterpret_cast<uint64_t*>(ready + 256);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + bar_count<MT>(DS));
+  const int BD = p.bdepth, BS = p.bshift;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + bar_count<MT, ST>(DS, BD));
   int* sflag = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, lane = tid & 31;
@@ -353,7 +386,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   // the digit rows of the groups this CTA multiplies, (g_first + j) % G for j < min(G, u1 - u0), live in slot j
   const int g_first = u0 - static_cast<int>(fdiv(static_cast<uint32_t>(u0), p.mg_G)) * G;
   auto cache_slot = [&](int g) { return g - g_first + (g < g_first ? G : 0); };
-  const int b_slot = 384 * M, b_lbo = 48 * M;
+  // bytes between the digit rows of consecutive groups (cache slots for M = 1, ring slots otherwise), and
+  // between the 16-k chunks of one group
+  const int b_slot = kStream ? p.db_bytes : 384 * M, b_lbo = 48 * M;
   int T;  // steps of this CTA
   {
     SegIter si;
@@ -373,16 +408,21 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   const uint32_t dempty_a = done_a + DD2 * 8;       // [DD2] D slot read out (4 fix-up warps)
   const uint32_t bready_a = dempty_a + DD2 * 8;     // every needed group's digit rows are written
   const uint32_t tmemrdy_a = bready_a + 8;          // tensor memory allocated, base address published
+  const uint32_t bfull_a = tmemrdy_a + 8;           // [BD]  M >= 2: digit rows of a step landed (tx bytes)
+  const uint32_t bempty_a = bfull_a + BD * 8;       // [BD]  M >= 2: every fix-up warp is done with the step's slot
 
   if (tid < 256) ready[tid] = 0u;
   {
     // barrier i of the block [wfull | wempty | afull | done | dempty | bready | tmemrdy]: arrival counts
-    const int nb = bar_count<MT>(DS);
+    // (+ [bfull | bempty] for M >= 2)
+    const int nb = bar_count<MT, ST>(DS, BD), nb0 = 2 * DS + AD2 + 2 * DD2 + 2;
+    const uint32_t nfix = CW * ((M + GE::TM - 1) / GE::TM);                // active fix-up warps
     if (tid < nb) {
-      uint32_t cnt = 1;                                                    // wfull, done, tmemrdy
+      uint32_t cnt = 1;                                                    // wfull, done, tmemrdy, bfull
       if (tid >= DS && tid < 2 * DS + AD2) cnt = 4;                        // wempty, afull: 4 unpack warps
-      else if (tid >= 2 * DS + AD2 + DD2 && tid < 2 * DS + AD2 + 2 * DD2) cnt = CW * ((M + GE::TM - 1) / GE::TM);  // dempty: every active fix-up warp
-      else if (tid == nb - 2) cnt = kTeam;                                 // bready
+      else if (tid >= 2 * DS + AD2 + DD2 && tid < 2 * DS + AD2 + 2 * DD2) cnt = nfix;  // dempty
+      else if (tid == nb0 - 2) cnt = kTeam;                                // bready
+      else if (tid >= nb0 + BD) cnt = nfix;                                // bempty
       mbar_init(wfull_a + tid * 8, cnt);
     }
     fence_mbar_init();
@@ -399,7 +439,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   }
 
   bool team_ok = true;
-  const bool converts = warp < CW || warp == 14 || warp >= kWConv0;
+  const bool converts = !kStream && (warp < CW || warp == 14 || warp >= kWConv0);
   if (converts) {
     // ================================================================ activations -> digit rows, once per CTA
     // The fix-up warps (idle until the first sums exist) and nine warps that do nothing else. The unpack
@@ -416,7 +456,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
       for (int j = 0; j < kBatch; ++j) {
         const int i = i0 + j * kTeam;
         if (i < total) {
-          const int gj = MT == 1 ? i : i / M, m = i - gj * M;  // (no division on the M = 1 path)
+          const int gj = i, m = 0;
           int g = g_first + gj;
           if (g >= G) g -= G;
           rv[j] = __ldcg(reinterpret_cast<const uint2*>(p.x + static_cast<size_t>(m) * p.K + g * kGroup) + lane);
@@ -426,7 +466,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
       for (int j = 0; j < kBatch; ++j) {
         const int i = i0 + j * kTeam;
         if (i < total) {
-          const int gj = MT == 1 ? i : i / M, m = i - gj * M;
+          const int gj = i, m = 0;
           convert_group(rv[j], bq + gj * b_slot, b_lbo, m, reinterpret_cast<float2*>(xsinv) + gj * MT + m, lane);
           // publish the item: B was written through the generic proxy, the tensor core reads it through the
           // async one; the slot counts as ready once all M tokens are in. Slots are numbered in the order the
@@ -478,8 +518,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
             ok = false;
             break;
           }
-          const int s0 = cache_slot(sg.g0 + gl);
-          const int s1 = ng == 2 ? cache_slot(sg.g0 + gl + 1) : s0;
+          // where the step's digit rows are: cache slots (M = 1) or the two halves of digit-ring slot t % BD
+          const int s0 = kStream ? 2 * (t & (BD - 1)) : cache_slot(sg.g0 + gl);
+          const int s1 = ng == 2 ? (kStream ? s0 + 1 : cache_slot(sg.g0 + gl + 1)) : s0;
           table[t & (kTable - 1)] =
               make_uint2(step_word(s0, s1, ng, gl + kStepGroups >= sg.L, sg.whole), static_cast<uint32_t>(sg.tile));
           mbar_expect_tx(wfull_a + st * 8, ng * kBlock);
@@ -518,7 +559,13 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
           break;
         }
         const uint32_t e = table[t & (kTable - 1)].x;
-        if (!all_ready) {
+        if constexpr (kStream) {
+          // the step's digit rows have landed in their ring slot (bulk copy: async proxy, as the MMA reads them)
+          if (!wait_h(bfull_a + (t & (BD - 1)) * 8, static_cast<uint32_t>(t >> BS) & 1u, p.hint, kSpinLimit)) {
+            atomicExch(p.status, W4A16_ETIMEOUT);
+            break;
+          }
+        } else if (!all_ready) {
           // the digit rows of this step's two slots (all M tokens each) must be in shared memory
           const volatile uint32_t* rdy = ready;
           const uint32_t s0 = e & 0xFFu, s1 = (e >> 8) & 0xFFu, need = static_cast<uint32_t>(M);
@@ -643,6 +690,43 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
         wph ^= 1;
       }
     }
+  } else if (warp == 14) {
+    // ================================================================ digit-row producer (M >= 2)
+    // One thread walks the same unit range as the weight producer and brings each step's digit rows (and the
+    // tokens' (sum, 2^-p) pairs behind them) from the pre-pass output into the digit ring: one bulk copy per
+    // step, two consecutive groups. The pre-pass is the previous kernel in the stream, so this thread - and
+    // only this one - waits for it; the weights are already streaming meanwhile.
+    if constexpr (kStream) {
+      if (lane == 0 && team_ok) {
+        pdl_wait();
+        SegIter it;
+        it.init(u0, u1, G, p.mg_G);
+        Seg sg;
+        int t = 0;
+        bool ok = true;
+        const uint32_t db = static_cast<uint32_t>(p.db_bytes);
+        while (ok && it.next(sg)) {
+          const uint8_t* src = p.dig + static_cast<size_t>(sg.g0) * db;
+          for (int gl = 0; gl < sg.L; gl += kStepGroups, ++t) {
+            const int ng = (sg.L - gl < kStepGroups) ? sg.L - gl : kStepGroups;
+            const int sl = t & (BD - 1);
+            // slot free: every fix-up warp has finished the step that used it last (so its MMAs are long done)
+            if (t >= BD && !mbar_wait_bounded_relaxed(bempty_a + sl * 8, static_cast<uint32_t>((t >> BS) - 1) & 1u, kSpinLimit)) {
+              atomicExch(p.status, W4A16_ETIMEOUT);
+              ok = false;
+              break;
+            }
+            mbar_expect_tx(bfull_a + sl * 8, ng * db);
+            bulk_g2s(bq_a + sl * 2 * db, src + static_cast<size_t>(gl) * db, ng * db, bfull_a + sl * 8);
+          }
+        }
+        // every copy this thread started has to land before the CTA may exit
+        for (int i = 0; i < BD && i < t; ++i) {
+          const int k = t - 1 - i;
+          mbar_wait_bounded_relaxed(bfull_a + (k & (BD - 1)) * 8, static_cast<uint32_t>(k >> BS) & 1u, 1u << 14);
+        }
+      }
+    }
   } else if (warp < CW || warp >= kWConv0) {
     // ================================================================ fix-up warps
     // One warp per TMEM lane quarter and token set: warps 0..3 take the first TM tokens, warps 16..19 and
@@ -694,12 +778,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
 
     bool ok = team_ok;
     constexpr int GB = GE::GB;
-    constexpr int kB0 = (3 * m0) / 16;                                       // first 16-column block of this set
-    constexpr int kB1 = (3 * (m0 + TM) - 1) / 16 < N / 16 ? (3 * (m0 + TM) - 1) / 16 : N / 16 - 1;  // last one
-    constexpr int NLD = MT == 1 ? 4 : (MT == 2 ? 8 : 16 * (kB1 - kB0 + 1));
-    constexpr int kC0 = MT <= 2 ? 0 : 16 * kB0;                              // column of dv[.][0]
+    // accumulator columns this warp reads per group: token m's three sums sit in columns 3 m .. 3 m + 2
+    constexpr int kC0 = 3 * m0;                                              // column of dv[.][0]
+    constexpr int kTok = MT - m0 < TM ? (MT - m0 > 0 ? MT - m0 : 0) : TM;   // tokens of this set that exist for this MT
+    constexpr int NLD = MT == 1 ? 4 : 3 * TM;
     const uint32_t* side_r = reinterpret_cast<const uint32_t*>(side) + r;
-    const float2* xs_tab = reinterpret_cast<const float2*>(xsinv);
+    const float2* xs_tab = reinterpret_cast<const float2*>(xsinv);  // M = 1; otherwise the pairs sit behind the slot's digit rows
     for (int t = 0; ok && t < T;) {
       // A round is one or two steps (two unless the first ends its segment): one wait per issuer (a commit
       // covers everything its thread issued before), GB groups' tensor-memory loads in flight together.
@@ -732,11 +816,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
               const int ts = t + (k >> 1);
               const uint32_t d_t = lane_t + (ts & (DD2 - 1)) * GE::kDColsS + (k & 1) * N;
               if constexpr (MT == 1) tmem_ld4(d_t, dv[j]);
-              else if constexpr (MT == 2) tmem_ld8(d_t, dv[j]);
-              else {
-#pragma unroll
-                for (int i = 0; i <= kB1 - kB0; ++i) tmem_ld16(d_t + 16 * (kB0 + i), dv[j] + 16 * i);
-              }
+              else tmem_ld_cols<kC0, 3 * kTok>(d_t, dv[j]);
               sz[j] = side_r[((ts & 7) * kStepGroups + (k & 1)) * kTileRows];
             }
           }
@@ -758,11 +838,11 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
               const float s = __uint_as_float(sz[j] & 0xFFFF0000u);
               const float z = __uint_as_float(0x4B000000u | (sz[j] & 0xFFu)) - 8388608.0f;
 #pragma unroll
-              for (int i = 0; i < TM; ++i)
+              for (int i = 0; i < (MT == 1 ? 1 : kTok); ++i)
                 if (m0 + i < M) {
-                  // (tokens past MT never pass the test above; the clamp only keeps their dead indices in range)
-                  const int c = 3 * (m0 + i) - kC0 + 2 < NLD ? 3 * (m0 + i) - kC0 : NLD - 3;
-                  const float2 xv = xs_tab[slot * MT + m0 + i];  // (sum of X, 2^-p)
+                  const int c = 3 * i;
+                  const float2 xv = kStream ? reinterpret_cast<const float2*>(bq + slot * b_slot + 384 * M)[m0 + i]
+                                            : xs_tab[slot * MT + m0 + i];  // (sum of X, 2^-p)
                   const float d0 = small_int_to_float(dv[j][c]);
                   const float d1 = small_int_to_float(dv[j][c + 1]);
                   const float d2 = small_int_to_float(dv[j][c + 2]);
@@ -771,6 +851,14 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
                 }
             }
           }
+        }
+      }
+      if constexpr (kStream) {
+        // this warp has read the round's (sum, 2^-p) pairs: its share of the digit-ring slots is released
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(bempty_a + (t & (BD - 1)) * 8);
+          if (two) mbar_arrive(bempty_a + ((t + 1) & (BD - 1)) * 8);
         }
       }
       const uint2 el = two ? e1 : e0;  // the round's last step
@@ -910,6 +998,23 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   }
 }
 
+// Pre-pass of the M >= 2 calls: one warp per (k group, token) turns the token's 128 bf16 values of the
+// group into three digit rows of the B operand and its (sum, 2^-p) pair, laid out per group exactly as
+// the main kernel's digit ring wants them: [8 chunks of 16 k][3 M rows] 16 B, then M pairs. Small CTAs
+// (four warps, at most 32 registers) so that they fit beside a resident main-kernel CTA of the previous
+// layer and are ready to run the moment that layer completes.
+__global__ void __launch_bounds__(128, 16) k_digits(const uint16_t* __restrict__ x, uint8_t* __restrict__ dig, int M,
+                                                    int K, int G, int db_bytes) {
+  pdl_launch_dependents();
+  pdl_wait();  // the previous kernel produced x (and the main kernel before it may still be reading `dig`)
+  const int item = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (item >= G * M) return;
+  const int g = item / M, m = item - g * M;
+  const uint2 rv = __ldcg(reinterpret_cast<const uint2*>(x + static_cast<size_t>(m) * K + g * kGroup) + lane);
+  uint8_t* blk = dig + static_cast<size_t>(g) * db_bytes;
+  convert_group(rv, blk, 48 * M, m, reinterpret_cast<float2*>(blk + 384 * M) + m, lane);
+}
+
 __global__ void k_pairs_reduce(int32_t* ids, const Pair* pairs, int nranks, int M) {
   const int m = blockIdx.x * blockDim.x + threadIdx.x;
   if (m >= M) return;
@@ -926,11 +1031,13 @@ struct Config {
   int depth;     // weight ring stages (two blocks, 17152 B, each); even
   int pdl;
   int hint;      // suspend-time hint of the in-kernel mbarrier waits, ns
+  int gemv_prepass;  // M = 1 through the pre-pass + digit ring as well (experiment; default off)
 };
 
 const Config& config() {
   static Config c = [] {
-    Config k{8, 1, 2000};
+    Config k{8, 1, 2000, 0};
+    if (const char* e = getenv("W4A16_GEMV_PREPASS")) k.gemv_prepass = atoi(e) != 0;
     if (const char* e = getenv("W4A16_DEPTH")) k.depth = atoi(e);
     if (const char* e = getenv("W4A16_PDL")) k.pdl = atoi(e) != 0;
     if (const char* e = getenv("W4A16_HINT")) k.hint = atoi(e);
@@ -947,6 +1054,9 @@ const Config& config() {
 size_t counter_bytes(int max_out) {
   return (3 * (static_cast<size_t>(max_out) / kTileRows + 2) * CW + 8) * sizeof(unsigned);
 }
+
+// bytes of the per-CTA argmax pair area at the front of the scratch's `xf` buffer
+size_t pair_bytes(int max_splits) { return (static_cast<size_t>(max_splits) * 16 * sizeof(Pair) + 255) & ~static_cast<size_t>(255); }
 
 constexpr int kMaxCtasPerSm = 2;  // what the scratch is sized for (the grid itself is one CTA per SM)
 
@@ -965,31 +1075,65 @@ int cache_groups_for(int tiles, int G, int grid) {
   return per_cta < G ? per_cta : G;
 }
 
-template <int MT, int WB>
+template <int MT, int WB, bool ST>
+int launch_kernel(const SkinnyParams& p, int grid, cudaStream_t st, int smem);
+
+template <int MT, int WB, bool ST = true>
 int launch_cfg(SkinnyParams& p, int grid, cudaStream_t st, int smem_optin) {
   constexpr int kStageBytes = Fmt<WB>::kStage;
+  constexpr bool kStream = ST;
   const int groups = cache_groups_for(p.tiles, p.G, grid);
+  const int limit = smem_optin;
+  if constexpr (kStream) {
+    // weight ring first (up to the configured depth), then the deepest digit ring that still fits
+    static const int kTry[][2] = {{8, 8}, {8, 4}, {6, 4}, {4, 4}, {4, 2}, {2, 2}};
+    int smem = 0;
+    bool found = false;
+    for (const auto& c : kTry) {
+      if (c[0] > config().depth) continue;
+      p.depth = c[0];
+      p.bdepth = c[1];
+      p.bshift = c[1] == 8 ? 3 : (c[1] == 4 ? 2 : 1);
+      p.b_bytes = p.bdepth * kStepGroups * p.db_bytes;
+      p.xs_bytes = 0;
+      smem = total_smem<MT, ST>(p.depth, kStageBytes, p.b_bytes, p.xs_bytes, p.bdepth);
+      if (smem <= limit) {
+        found = true;
+        break;
+      }
+    }
+    if (!found)
+      return fail(W4A16_EINVAL, "decode kernel needs %d bytes of shared memory for M = %d; the device offers %d", smem,
+                  p.M, smem_optin);
+    return launch_kernel<MT, WB, ST>(p, grid, st, smem);
+  }
   p.b_bytes = groups * 384 * p.M + 256;
   p.xs_bytes = groups * MT * 8;
-  const int limit = smem_optin;
+  p.bdepth = 0;
+  p.bshift = 0;
   // The depth stays EVEN. The two unpack warps of a lane quarter take alternate steps, and a parity wait on
   // an mbarrier only tells the current phase from the previous one: with an odd depth a stage's consecutive
   // uses would belong to different warps, and a warp that runs ahead could take "the other warp's copy has
   // not landed yet" for "my copy has landed".
   p.depth = config().depth;
-  int smem = total_smem<MT>(p.depth, kStageBytes, p.b_bytes, p.xs_bytes);
+  int smem = total_smem<MT, ST>(p.depth, kStageBytes, p.b_bytes, p.xs_bytes, 0);
   while (smem > limit && p.depth > 2) {
     p.depth -= 2;
-    smem = total_smem<MT>(p.depth, kStageBytes, p.b_bytes, p.xs_bytes);
+    smem = total_smem<MT, ST>(p.depth, kStageBytes, p.b_bytes, p.xs_bytes, 0);
   }
   if (smem > smem_optin)
     return fail(W4A16_EINVAL, "decode kernel needs %d bytes of shared memory for in_f = %d, M = %d; the device offers %d",
                 smem, p.K, p.M, smem_optin);
+  return launch_kernel<MT, WB, ST>(p, grid, st, smem);
+}
+
+template <int MT, int WB, bool ST>
+int launch_kernel(const SkinnyParams& p, int grid, cudaStream_t st, int smem) {
   static int attr_set[64] = {};
   int dev = 0;
   W4_CUDA(cudaGetDevice(&dev));
   if (attr_set[dev & 63] < smem) {
-    W4_CUDA(cudaFuncSetAttribute(k_skinny<MT, WB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    W4_CUDA(cudaFuncSetAttribute(k_skinny<MT, WB, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set[dev & 63] = smem;
   }
   cudaLaunchConfig_t cfg = {};
@@ -1002,18 +1146,20 @@ int launch_cfg(SkinnyParams& p, int grid, cudaStream_t st, int smem_optin) {
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
   cfg.numAttrs = config().pdl ? 1 : 0;
-  W4_CUDA(cudaLaunchKernelEx(&cfg, k_skinny<MT, WB>, p));
+  W4_CUDA(cudaLaunchKernelEx(&cfg, k_skinny<MT, WB, ST>, p));
   return W4A16_OK;
 }
 
-// Most tokens one launch can take: the digit rows of `groups` k groups (384 B per group and token) must
-// fit beside a two-stage weight ring.
-int max_batch(int groups, int stage_bytes, int smem_optin) {
+// M = 1: the digit rows of `groups` k groups (384 B + one pair per group) must fit beside a two-stage
+// weight ring.
+bool gemv_cache_fits(int groups, int stage_bytes, int smem_optin) {
   const int fixed = 2 * stage_bytes + kSide * kTileRows * 4 + kTable * 8 + 64 * 8 + 16 + 256;
-  int mb = (smem_optin - fixed) / (groups * (384 + 8));
-  if (mb > kMaxBatch) mb = kMaxBatch;
-  return mb;
+  return groups * (384 + 8) <= smem_optin - fixed;
 }
+
+// bytes of the pre-pass output per k group: 3 M digit rows of 128 k, then M (sum, 2^-p) pairs, rounded up
+// to the 16 bytes a bulk copy wants
+int digit_block_bytes(int M) { return 384 * M + ((8 * M + 15) & ~15); }
 
 // A validated layer in either weight format, as the launcher sees it.
 struct LayerRef {
@@ -1033,13 +1179,18 @@ int layer_of(LayerRef& L, const w4a16_w8_weights_t* w) {
 
 template <int WB>
 int launch_batch(SkinnyParams& q, int grid, cudaStream_t st, int smem_optin) {
-  if (q.M == 1) return launch_cfg<1, WB>(q, grid, st, smem_optin);
+  // MT is picked so that the token sets of the fix-up warps are balanced: sets of ceil(MT / sets) tokens
+  if (q.M == 1) return q.dig ? launch_cfg<1, WB, true>(q, grid, st, smem_optin) : launch_cfg<1, WB, false>(q, grid, st, smem_optin);
   if (q.M == 2) return launch_cfg<2, WB>(q, grid, st, smem_optin);
-  if (q.M <= 4) return launch_cfg<4, WB>(q, grid, st, smem_optin);   // token sets (2, M - 2)
-  if (q.M == 5) return launch_cfg<5, WB>(q, grid, st, smem_optin);   // (3, 2)
-  if (q.M == 6) return launch_cfg<6, WB>(q, grid, st, smem_optin);   // (3, 3)
-  if (q.M <= 8) return launch_cfg<8, WB>(q, grid, st, smem_optin);   // (4, M - 4)
-  return launch_cfg<10, WB>(q, grid, st, smem_optin);                // (5, M - 5)
+  if (q.M <= 4) return launch_cfg<4, WB>(q, grid, st, smem_optin);    // (2, M - 2)
+  if (q.M == 5) return launch_cfg<5, WB>(q, grid, st, smem_optin);    // (3, 2)
+  if (q.M == 6) return launch_cfg<6, WB>(q, grid, st, smem_optin);    // (3, 3)
+  if (q.M <= 8) return launch_cfg<8, WB>(q, grid, st, smem_optin);    // (4, M - 4)
+  if (q.M == 9) return launch_cfg<9, WB>(q, grid, st, smem_optin);    // (3, 3, 3)
+  if (q.M == 10) return launch_cfg<10, WB>(q, grid, st, smem_optin);  // (4, 4, 2)
+  if (q.M <= 12) return launch_cfg<12, WB>(q, grid, st, smem_optin);  // (4, 4, M - 8)
+  if (q.M <= 15) return launch_cfg<15, WB>(q, grid, st, smem_optin);  // (5, 5, M - 10)
+  return launch_cfg<16, WB>(q, grid, st, smem_optin);                 // (6, 6, 4)
 }
 
 int launch_skinny(SkinnyParams& p, const LayerRef* w, const uint16_t* x, int M, w4a16_scratch_t* s,
@@ -1067,29 +1218,34 @@ int launch_skinny(SkinnyParams& p, const LayerRef* w, const uint16_t* x, int M, 
   p.mg_grid = magic(grid);
   p.mg_G = magic(p.G);
   if (int rc = w4a16_scratch_check(s, w->out_f, M)) return rc;
-  const int mb = max_batch(cache_groups_for(p.tiles, p.G, grid), w->wbits == 4 ? Fmt<4>::kStage : Fmt<8>::kStage,
-                           di->smem_optin);
-  if (mb < 1)
-    return fail(W4A16_EINVAL, "in_f = %d is too wide for the decode kernel's activation cache", w->in_f);
-  // token batches: one launch for M <= mb, else equal halves (each launch streams the weights once)
-  const int nb = (M + mb - 1) / mb;
-  const SkinnyParams base = p;
-  for (int b = 0, m0 = 0; b < nb; ++b) {
-    const int m1 = static_cast<int>(static_cast<long long>(M) * (b + 1) / nb);
-    SkinnyParams q = base;
-    q.M = m1 - m0;
-    q.x = x + static_cast<size_t>(m0) * w->in_f;
-    if (base.y)
-      q.y = base.y_f32 ? static_cast<void*>(static_cast<float*>(base.y) + static_cast<size_t>(m0) * base.ldy)
-                       : static_cast<void*>(static_cast<uint16_t*>(base.y) + static_cast<size_t>(m0) * base.ldy);
-    for (int r = 0; r < base.npeers; ++r) q.y_peers[r] = base.y_peers[r] + static_cast<size_t>(m0) * base.ldy;
-    if (base.ids) q.ids = base.ids + m0;
-    if (base.pairs_out) q.pairs_out = static_cast<Pair*>(base.pairs_out) + m0;
-    const int rc = w->wbits == 4 ? launch_batch<4>(q, grid, st, di->smem_optin)
-                                 : launch_batch<8>(q, grid, st, di->smem_optin);
-    if (rc) return rc;
-    m0 = m1;
+  p.M = M;
+  p.x = x;
+  const bool prepass = M >= 2 || (config().gemv_prepass && s->max_m >= 2 && p.G <= s->max_groups);
+  if (!prepass) {
+    if (!gemv_cache_fits(cache_groups_for(p.tiles, p.G, grid), w->wbits == 4 ? Fmt<4>::kStage : Fmt<8>::kStage,
+                         di->smem_optin))
+      return fail(W4A16_EINVAL, "in_f = %d is too wide for the decode kernel's activation cache", w->in_f);
+  } else {
+    // the pre-pass: digit rows of all M tokens, once per call, into the scratch (behind the argmax pairs)
+    if (M > s->max_m || p.G > s->max_groups)
+      return fail(W4A16_ESCRATCH, "scratch: sized for max_m = %d and in_f <= %d, got M = %d, in_f = %d", s->max_m,
+                  s->max_groups * kGroup, M, w->in_f);
+    p.db_bytes = digit_block_bytes(M);
+    uint8_t* dig = reinterpret_cast<uint8_t*>(s->xf) + pair_bytes(s->max_splits);
+    p.dig = dig;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((p.G * M + 3) / 4);
+    cfg.blockDim = dim3(128);
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = config().pdl ? 1 : 0;
+    W4_CUDA(cudaLaunchKernelEx(&cfg, k_digits, x, dig, M, p.K, p.G, p.db_bytes));
   }
+  if (int rc = w->wbits == 4 ? launch_batch<4>(p, grid, st, di->smem_optin) : launch_batch<8>(p, grid, st, di->smem_optin))
+    return rc;
   return W4A16_OK;
 }
 
@@ -1177,7 +1333,9 @@ int w4a16_scratch_alloc(w4a16_scratch_t* s, int max_in, int max_out, int min_gro
   // two partial tiles per CTA (head and tail of its unit range), widest tile, 16 tokens
   s->partial_elems = static_cast<size_t>(s->max_splits) * 2 * kTileRows * 16;
   const size_t counters = counter_bytes(max_out);
-  const size_t pairs = static_cast<size_t>(s->max_splits) * 16 * sizeof(Pair);
+  // per-CTA argmax pairs, then (max_m >= 2) the pre-pass output: digit rows of max_m tokens for every k group
+  const size_t pairs = pair_bytes(s->max_splits) +
+                       (max_m >= 2 ? static_cast<size_t>(s->max_groups) * digit_block_bytes(max_m > 16 ? 16 : max_m) : 0);
   void *xf = nullptr, *cn = nullptr, *pa = nullptr;
   cudaError_t e = cudaMalloc(&xf, pairs);
   if (e == cudaSuccess) e = cudaMalloc(&cn, counters);
