@@ -72,7 +72,9 @@ struct Fmt {
   static constexpr int kBlock = WB == 4 ? kTileGroupBytes : kW8BlockBytes;  // bytes per (row tile, group)
   static constexpr int kStage = kStepGroups * kBlock;                        // 17152 / 33280
 };
-constexpr int kSide = 16;                  // (scale, zp) side ring: 8 steps x 2 groups
+constexpr int kSideSteps = 12;             // (scale, zp) side ring, in steps: a slot is rewritten by the unpack warps
+                                           // A-ring + D-ring depths (at most 4 + 8 steps) after the fix-up read it
+constexpr int kSide = kSideSteps * 2;      // in groups
 constexpr int kTable = 64;                 // step table entries (ring)
 constexpr uint32_t kSpinLimit = 1u << 20;  // polls before a wait gives up
 constexpr int kFixBar = 1;                 // named barrier of the fix-up warps
@@ -85,22 +87,27 @@ constexpr int kAColsG = 32;                // 128 int8 along k = 32 columns of 3
 // real). Ring depths are in steps: AD2 for A, DD2 for D and for the ring of "step done" barriers.
 template <int MT, bool ST>
 struct Geo {
-  static constexpr int N = MT <= 5 ? 16 : (MT <= 10 ? 32 : 48);
-  static constexpr int AD2 = N == 48 ? 2 : 4;
-  static constexpr int DD2 = N == 16 ? 8 : 4;
   static constexpr bool kStream = ST;  // digit rows streamed from the pre-pass output instead of converted here
   static_assert(ST || MT == 1, "only the M = 1 kernel converts activations itself");
+  // Token sets: the fix-up warps of one lane quarter split the tokens into FW sets of TM tokens; set F owns the
+  // accumulator columns [CB F, CB F + 3 TM), so every set runs the SAME code on its own aligned column block
+  // (one copy of the fix-up code per kernel: the instruction footprint of all roles has to stay cache resident).
+  //   MT:        1    2    4    6    8    9   12   15   16
+  //   FW x TM: 1x1  2x1  2x2  2x3  2x4  3x3  3x4  3x5  2x8
+  static constexpr int FW = MT <= 1 ? 1 : ((MT == 9 || MT == 12 || MT == 15) ? 3 : 2);
+  static constexpr int TM = (MT + FW - 1) / FW;                // tokens per fix-up warp
+  static constexpr int CB = !ST ? 16 : (3 * TM <= 8 ? 8 : (3 * TM <= 16 ? 16 : 24));  // accumulator columns per set
+  static constexpr int N = !ST ? 16 : ((FW * CB + 15) / 16) * 16;  // rows of the B operand the tensor core reads
+  static constexpr int AD2 = N == 48 ? 2 : 4;
+  static constexpr int DD2 = N == 16 ? 8 : 4;
   static constexpr int kAColsS = kStepGroups * kAColsG;  // A columns per step
   static constexpr int kDColsS = kStepGroups * N;        // D columns per step
   static constexpr int kDCol0 = AD2 * kAColsS;           // first D column
-  static constexpr int GB = MT == 1 ? 4 : (MT == 2 ? 2 : 1);  // groups whose tensor-memory loads are in flight together
-  // fix-up warps per lane quarter: two token sets from M = 2, three from M = 9 (the fix-up is latency-bound
-  // per token). The launcher picks MT so that the sets are balanced: TM = ceil(MT / FW).
-  static constexpr int FW = MT <= 1 ? 1 : (MT <= 8 ? 2 : 3);
-  static constexpr int TM = (MT + FW - 1) / FW;               // tokens per fix-up warp
+  static constexpr int GB = 4;                           // M = 1: groups whose tensor-memory loads are in flight together
+  static_assert(3 * TM <= CB && FW * CB <= N, "token sets must fit their column blocks");
   static_assert(kDCol0 + DD2 * kDColsS <= kTmemCols, "tensor memory budget");
   static_assert(AD2 <= DD2 && 2 <= DD2 / 2, "ring depths");
-  static_assert(kStepGroups * DD2 <= kSide, "a (scale, zp) slot is read before the D slot of its step is released");
+  static_assert(AD2 + DD2 <= kSideSteps, "a (scale, zp) slot must have been read before the unpack warps reuse it");
 };
 
 struct SkinnyParams {
@@ -113,7 +120,7 @@ struct SkinnyParams {
   int M, N, K, G, tiles;
   int b_bytes;       // bytes of the B region (M = 1: digit rows of the groups this CTA multiplies; else the digit ring)
   int xs_bytes;      // bytes of the (sum, 2^-p) region (M = 1)
-  const uint8_t* dig;  // M >= 2: pre-pass output, db_bytes per k group: [8 chunks of 16 k][3 M digit rows] 16 B, then M x (sum, 2^-p)
+  const uint8_t* dig;  // pre-pass output: G blocks of db_bytes = [8 chunks of 16 k][3 M digit rows] 16 B, then G x M (sum, 2^-p) pairs
   int db_bytes;
   int bdepth;        // M >= 2: steps in the digit ring (a power of two)
   int bshift;        //         and its log2
@@ -204,11 +211,11 @@ struct SegIter {
 };
 
 // Step table entry, written by the producer, read by the MMA issuers and the fix-up warps:
-//   x = slot0 | slot1 << 8 | (groups - 1) << 16 | last step of its segment << 17 | whole tile << 18
+//   x = slot0 | slot1 << 8 | (groups - 1) << 16 | last step of its segment << 17 | whole tile << 18 | first k group << 19
 //   y = row tile
-__device__ __forceinline__ uint32_t step_word(int slot0, int slot1, int ng, bool seg_last, bool whole) {
+__device__ __forceinline__ uint32_t step_word(int slot0, int slot1, int ng, bool seg_last, bool whole, int g0) {
   return static_cast<uint32_t>(slot0) | (static_cast<uint32_t>(slot1) << 8) | (static_cast<uint32_t>(ng - 1) << 16) |
-         (seg_last ? 1u << 17 : 0u) | (whole ? 1u << 18 : 0u);
+         (seg_last ? 1u << 17 : 0u) | (whole ? 1u << 18 : 0u) | (static_cast<uint32_t>(g0) << 19);
 }
 
 // ---- PTX used only here ------------------------------------------------------------------
@@ -239,12 +246,6 @@ __device__ __forceinline__ void umma_s8_ts(uint32_t d_tmem, uint32_t a_tmem, uin
       "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-__device__ __forceinline__ void tmem_ld1(uint32_t taddr, uint32_t* d) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(d[0]) : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld2(uint32_t taddr, uint32_t* d) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0,%1}, [%2];" : "=r"(d[0]), "=r"(d[1]) : "r"(taddr) : "memory");
-}
 __device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t* d) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
                : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
@@ -265,19 +266,17 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* d) {
       : "r"(taddr)
       : "memory");
 }
-// Columns [C0, C0 + CNT) of this thread's lane, relative to `base`, as the fewest loads whose start column is
-// a multiple of their own width (the completion is awaited once, by the caller, for all of them).
+// Columns [C0, C0 + CNT) of this thread's lane, relative to `base` (a multiple of CNT's block size; C0 and CNT
+// multiples of 8), as loads of 16 or 8 columns whose start is a multiple of their width; the caller awaits
+// them all at once.
 template <int C0, int CNT>
-__device__ __forceinline__ void tmem_ld_cols(uint32_t base, uint32_t* d) {
+__device__ __forceinline__ void tmem_ld_span(uint32_t base, uint32_t* d) {
   if constexpr (CNT > 0) {
-    constexpr int W = (C0 % 16 == 0 && CNT >= 16) ? 16 : (C0 % 8 == 0 && CNT >= 8) ? 8 : (C0 % 4 == 0 && CNT >= 4) ? 4
-                      : (C0 % 2 == 0 && CNT >= 2) ? 2 : 1;
+    // (a 24-column block starts at a multiple of 8 only: three loads of 8)
+    constexpr int W = (C0 % 16 == 0 && CNT == 16) ? 16 : 8;
     if constexpr (W == 16) tmem_ld16(base + C0, d);
-    else if constexpr (W == 8) tmem_ld8(base + C0, d);
-    else if constexpr (W == 4) tmem_ld4(base + C0, d);
-    else if constexpr (W == 2) tmem_ld2(base + C0, d);
-    else tmem_ld1(base + C0, d);
-    tmem_ld_cols<C0 + W, CNT - W>(base, d + W);
+    else tmem_ld8(base + C0, d);
+    tmem_ld_span<C0 + W, CNT - W>(base, d + W);
   }
 }
 // Ticket counter with release + acquire in one operation: the partial rows written before it (by the whole
@@ -316,14 +315,15 @@ __host__ __device__ inline int total_smem(int depth, int stage_bytes, int b_byte
 }
 
 // One token's 128 values of one k group (this lane: k = 4 lane .. 4 lane + 3, `rv`) -> three int8 digit
-// rows of the B operand at `bslot` (rows 3m, 3m+1, 3m+2) and (sum of X, 2^-p) at `xs`.
+// rows of the B operand at `bslot` (rows row0, row0 + 1, row0 + 2 of every 16-k chunk, chunks `lbo` bytes apart)
+// and (sum of X, 2^-p) at `xs`.
 //   X = rint(x * 2^p), p chosen per group so that the largest |X| lies in [2^21, 2^22).
 //   The fp32 magic constant 1.5 * 2^23 makes the FMA deliver X in the low mantissa bits; adding 0x808080
 //   turns the balanced base-256 digits (d0, d1 in [-128,127], |d2| <= 64) into plain bytes, the XOR
 //   with 0x808080 turns those bytes back into signed digits: X = d0 + 2^8 d1 + 2^16 d2.
 // K index j of the operand holds k = 8 (j/8) + perm(j%8) with perm = {0,4,1,5,2,6,3,7}: the order in which
 // the two nibble masks deliver a packed word's weights.
-__device__ __forceinline__ void convert_group(uint2 rv, uint8_t* bslot, int lbo, int m, float2* xs, int lane) {
+__device__ __forceinline__ void convert_group(uint2 rv, uint8_t* bslot, int lbo, int row0, float2* xs, int lane) {
   const uint32_t mx = __vmaxu2(rv.x & 0x7FFF7FFFu, rv.y & 0x7FFF7FFFu);
   const uint32_t am = max(mx & 0xFFFFu, mx >> 16);               // bf16 bits of the lane's largest magnitude
   const uint32_t e = __reduce_max_sync(0xffffffffu, am) >> 7;    // its biased exponent, group-wide
@@ -348,7 +348,7 @@ __device__ __forceinline__ void convert_group(uint2 rv, uint8_t* bslot, int lbo,
   const uint32_t Q2 = __shfl_xor_sync(0xffffffffu, P2, 1);
   // even lane: k offsets 0..3 of its 8-block -> operand bytes {E0,O0,E1,O1}; odd lane: {E2,O2,E3,O3}
   const uint32_t sel = (lane & 1) ? 0x3726u : 0x5140u;
-  uint8_t* dst = bslot + (lane >> 2) * lbo + 4 * (lane & 3) + 48 * m;
+  uint8_t* dst = bslot + (lane >> 2) * lbo + 4 * (lane & 3) + 16 * row0;
   *reinterpret_cast<uint32_t*>(dst) = __byte_perm(P0, Q0, sel);
   *reinterpret_cast<uint32_t*>(dst + 16) = __byte_perm(P1, Q1, sel);
   *reinterpret_cast<uint32_t*>(dst + 32) = __byte_perm(P2, Q2, sel);
@@ -388,7 +388,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   auto cache_slot = [&](int g) { return g - g_first + (g < g_first ? G : 0); };
   // bytes between the digit rows of consecutive groups (cache slots for M = 1, ring slots otherwise), and
   // between the 16-k chunks of one group
-  const int b_slot = kStream ? p.db_bytes : 384 * M, b_lbo = 48 * M;
+  const int b_slot = kStream ? p.db_bytes : 384 * M, b_lbo = kStream ? 16 * N : 48 * M;
   int T;  // steps of this CTA
   {
     SegIter si;
@@ -409,7 +409,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   const uint32_t bready_a = dempty_a + DD2 * 8;     // every needed group's digit rows are written
   const uint32_t tmemrdy_a = bready_a + 8;          // tensor memory allocated, base address published
   const uint32_t bfull_a = tmemrdy_a + 8;           // [BD]  M >= 2: digit rows of a step landed (tx bytes)
-  const uint32_t bempty_a = bfull_a + BD * 8;       // [BD]  M >= 2: every fix-up warp is done with the step's slot
+  const uint32_t bempty_a = bfull_a + BD * 8;       // [BD]  M >= 2: the step's MMAs have completed (seen by the first fix-up warp)
 
   if (tid < 256) ready[tid] = 0u;
   {
@@ -421,8 +421,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
       uint32_t cnt = 1;                                                    // wfull, done, tmemrdy, bfull
       if (tid >= DS && tid < 2 * DS + AD2) cnt = 4;                        // wempty, afull: 4 unpack warps
       else if (tid >= 2 * DS + AD2 + DD2 && tid < 2 * DS + AD2 + 2 * DD2) cnt = nfix;  // dempty
-      else if (tid == nb0 - 2) cnt = kTeam;                                // bready
-      else if (tid >= nb0 + BD) cnt = nfix;                                // bempty
+      else if (tid == nb0 - 2) cnt = kStream ? 1 : kTeam;                  // bready
       mbar_init(wfull_a + tid * 8, cnt);
     }
     fence_mbar_init();
@@ -522,7 +521,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
           const int s0 = kStream ? 2 * (t & (BD - 1)) : cache_slot(sg.g0 + gl);
           const int s1 = ng == 2 ? (kStream ? s0 + 1 : cache_slot(sg.g0 + gl + 1)) : s0;
           table[t & (kTable - 1)] =
-              make_uint2(step_word(s0, s1, ng, gl + kStepGroups >= sg.L, sg.whole), static_cast<uint32_t>(sg.tile));
+              make_uint2(step_word(s0, s1, ng, gl + kStepGroups >= sg.L, sg.whole, sg.g0 + gl), static_cast<uint32_t>(sg.tile));
           mbar_expect_tx(wfull_a + st * 8, ng * kBlock);
           bulk_g2s(ring_a + st * kStageBytes, src + static_cast<size_t>(gl) * kBlock, ng * kBlock, wfull_a + st * 8);
           if (++st == DS) {
@@ -553,8 +552,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
       const uint32_t step16 = (2 * b_lbo) >> 4, slot16 = static_cast<uint32_t>(b_slot) >> 4;
       for (int t = mine; ok && t < T; t += 2) {
         const int a = t & (AD2 - 1), d = t & (DD2 - 1);
-        // A written; its writers also saw the D slot drained and the step's weights (and table entry) landed
-        if (!wait_h(afull_a + a * 8, static_cast<uint32_t>(t / AD2) & 1u, p.hint, kSpinLimit)) {
+        // A written (its writers also saw the step's weights and table entry landed), and the D slot this
+        // step fills has been read out by every fix-up warp
+        if (!wait_h(afull_a + a * 8, static_cast<uint32_t>(t / AD2) & 1u, p.hint, kSpinLimit) ||
+            (t >= DD2 && !wait_h(dempty_a + d * 8, static_cast<uint32_t>(t / DD2 - 1) & 1u, p.hint, kSpinLimit))) {
           atomicExch(p.status, W4A16_ETIMEOUT);
           break;
         }
@@ -635,16 +636,15 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
         }
       };
       load_row(base);
-      // the A slot's previous step has been multiplied, and the D slot this step will fill has been read out
-      if ((t >= AD2 && !wait_h(done_a + ((t - AD2) & (DD2 - 1)) * 8, static_cast<uint32_t>((t - AD2) / DD2) & 1u, p.hint,
-                               kSpinLimit)) ||
-          (t >= DD2 &&
-           !wait_h(dempty_a + (t & (DD2 - 1)) * 8, static_cast<uint32_t>(t / DD2 - 1) & 1u, p.hint, kSpinLimit))) {
+      // the A slot's previous step has been multiplied (whether the D slot is free is the issuer's concern: the
+      // operand can be unpacked while the fix-up warps are still reading the sums of DD2 steps ago)
+      if (t >= AD2 && !wait_h(done_a + ((t - AD2) & (DD2 - 1)) * 8, static_cast<uint32_t>((t - AD2) / DD2) & 1u, p.hint,
+                              kSpinLimit)) {
         atomicExch(p.status, W4A16_ETIMEOUT);
         break;
       }
       tc_fence_after();
-      uint32_t* side_w = reinterpret_cast<uint32_t*>(side) + ((t & 7) * kStepGroups) * kTileRows + r;
+      uint32_t* side_w = reinterpret_cast<uint32_t*>(side) + ((t % kSideSteps) * kStepGroups) * kTileRows + r;
 #pragma unroll
       for (int j = 0; j < kStepGroups; ++j) {
         const uint8_t* gb = base + j * kBlock;
@@ -705,12 +705,15 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
         int t = 0;
         bool ok = true;
         const uint32_t db = static_cast<uint32_t>(p.db_bytes);
+        // all (sum, 2^-p) pairs of the call, once: G x M x 8 bytes, read by the fix-up warps to the end
+        mbar_expect_tx(bready_a, static_cast<uint32_t>(p.xs_bytes));
+        bulk_g2s(xsinv_a, p.dig + static_cast<size_t>(G) * db, static_cast<uint32_t>(p.xs_bytes), bready_a);
         while (ok && it.next(sg)) {
           const uint8_t* src = p.dig + static_cast<size_t>(sg.g0) * db;
           for (int gl = 0; gl < sg.L; gl += kStepGroups, ++t) {
             const int ng = (sg.L - gl < kStepGroups) ? sg.L - gl : kStepGroups;
             const int sl = t & (BD - 1);
-            // slot free: every fix-up warp has finished the step that used it last (so its MMAs are long done)
+            // slot free: the MMAs of the step that used it last have completed
             if (t >= BD && !mbar_wait_bounded_relaxed(bempty_a + sl * 8, static_cast<uint32_t>((t >> BS) - 1) & 1u, kSpinLimit)) {
               atomicExch(p.status, W4A16_ETIMEOUT);
               ok = false;
@@ -721,6 +724,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
           }
         }
         // every copy this thread started has to land before the CTA may exit
+        mbar_wait_bounded_relaxed(bready_a, 0, 1u << 14);
         for (int i = 0; i < BD && i < t; ++i) {
           const int k = t - 1 - i;
           mbar_wait_bounded_relaxed(bfull_a + (k & (BD - 1)) * 8, static_cast<uint32_t>(k >> BS) & 1u, 1u << 14);
@@ -732,12 +736,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
     // One warp per TMEM lane quarter and token set: warps 0..3 take the first TM tokens, warps 16..19 and
     // 20..23 (idle after converting) the next ones when M is larger. Each keeps its own running sums, so
     // the sets never have to be combined; a D slot is released when every active warp has loaded from it.
-    auto fixup = [&](auto ftag) {
-    constexpr int F = decltype(ftag)::value;  // this warp's token set
-    constexpr int TM = GE::TM, m0 = F * TM;   // its tokens: m0 .. m0 + TM - 1 (those below M)
+    auto fixup = [&](const int F) {           // F: this warp's token set
+    constexpr int TM = GE::TM, CB = GE::CB;
+    const int m0 = F * TM;                    // its tokens: m0 .. m0 + TM - 1 (those below M)
     const int q = warp & 3, r = q * 32 + lane;
     const int fslot = F * CW + q;             // this warp's index among the fix-up warps
-    const uint32_t lane_t = tmem + (static_cast<uint32_t>(q * 32) << 16) + GE::kDCol0;
+    const uint32_t lane_t = tmem + (static_cast<uint32_t>(q * 32) << 16) + GE::kDCol0 + (kStream ? F * CB : 0);
     unsigned* tickets = p.counters + static_cast<size_t>(F) * p.tiles * CW;  // [tile][quarter] of this token set
 
     float fin[TM];
@@ -778,12 +782,18 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
 
     bool ok = team_ok;
     constexpr int GB = GE::GB;
-    // accumulator columns this warp reads per group: token m's three sums sit in columns 3 m .. 3 m + 2
-    constexpr int kC0 = 3 * m0;                                              // column of dv[.][0]
-    constexpr int kTok = MT - m0 < TM ? (MT - m0 > 0 ? MT - m0 : 0) : TM;   // tokens of this set that exist for this MT
-    constexpr int NLD = MT == 1 ? 4 : 3 * TM;
+    // accumulator columns this warp reads per group: its CB-column block, token m0 + i's three sums in columns
+    // 3 i .. 3 i + 2 of it
+    constexpr int NLD = kStream ? CB : 4;
     const uint32_t* side_r = reinterpret_cast<const uint32_t*>(side) + r;
-    const float2* xs_tab = reinterpret_cast<const float2*>(xsinv);  // M = 1; otherwise the pairs sit behind the slot's digit rows
+    const float2* xs_tab = reinterpret_cast<const float2*>(xsinv);  // (sum, 2^-p): per cache slot (M = 1), else [k group][token]
+    if constexpr (kStream) {
+      // the pair table of the call arrives once, by bulk copy
+      if (!wait_h(bready_a, 0, p.hint, kSpinLimit)) {
+        atomicExch(p.status, W4A16_ETIMEOUT);
+        ok = false;
+      }
+    }
     for (int t = 0; ok && t < T;) {
       // A round is one or two steps (two unless the first ends its segment): one wait per issuer (a commit
       // covers everything its thread issued before), GB groups' tensor-memory loads in flight together.
@@ -800,10 +810,18 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
         break;
       }
       tc_fence_after();
+      if constexpr (kStream) {
+        // the round's MMAs are done with their digit rows: the ring slots go back to the digit producer
+        if (F == 0 && q == 0 && lane == 0) {
+          mbar_arrive(bempty_a + (t & (BD - 1)) * 8);
+          if (two) mbar_arrive(bempty_a + ((t + 1) & (BD - 1)) * 8);
+        }
+      }
       const uint2 e1 = two ? table[(t + 1) & (kTable - 1)] : e0;
       const int ng0 = static_cast<int>((e0.x >> 16) & 1u) + 1;
       const int rg = two ? ng0 + static_cast<int>((e1.x >> 16) & 1u) + 1 : ng0;  // groups of the round (ng0 == 2 if two)
       // group k of the round: step t + (k >> 1), position k & 1
+      if constexpr (!kStream || MT == 1) {
 #pragma unroll
       for (int k0 = 0; k0 < 4; k0 += GB) {
         if (k0 < rg) {
@@ -815,9 +833,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
             if (k < rg) {
               const int ts = t + (k >> 1);
               const uint32_t d_t = lane_t + (ts & (DD2 - 1)) * GE::kDColsS + (k & 1) * N;
-              if constexpr (MT == 1) tmem_ld4(d_t, dv[j]);
-              else tmem_ld_cols<kC0, 3 * kTok>(d_t, dv[j]);
-              sz[j] = side_r[((ts & 7) * kStepGroups + (k & 1)) * kTileRows];
+              tmem_ld4(d_t, dv[j]);
+              sz[j] = side_r[((ts % kSideSteps) * kStepGroups + (k & 1)) * kTileRows];
             }
           }
           tmem_wait_ld();
@@ -838,27 +855,82 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
               const float s = __uint_as_float(sz[j] & 0xFFFF0000u);
               const float z = __uint_as_float(0x4B000000u | (sz[j] & 0xFFu)) - 8388608.0f;
 #pragma unroll
-              for (int i = 0; i < (MT == 1 ? 1 : kTok); ++i)
-                if (m0 + i < M) {
-                  const int c = 3 * i;
-                  const float2 xv = kStream ? reinterpret_cast<const float2*>(bq + slot * b_slot + 384 * M)[m0 + i]
-                                            : xs_tab[slot * MT + m0 + i];  // (sum of X, 2^-p)
-                  const float d0 = small_int_to_float(dv[j][c]);
-                  const float d1 = small_int_to_float(dv[j][c + 1]);
-                  const float d2 = small_int_to_float(dv[j][c + 2]);
-                  const float dot = fmaf(d2, 65536.f, fmaf(d1, 256.f, d0));
-                  fin[i] = fmaf(s * xv.y, fmaf(-z, xv.x, dot), fin[i]);
-                }
+              {
+                // (sum of X, 2^-p): by cache slot, or (pre-pass) by k group
+                const float2 xv = xs_tab[kStream ? ((ew >> 19) & 0xFFu) + (k & 1) : slot];
+                const float d0 = small_int_to_float(dv[j][0]);
+                const float d1 = small_int_to_float(dv[j][1]);
+                const float d2 = small_int_to_float(dv[j][2]);
+                const float dot = fmaf(d2, 65536.f, fmaf(d1, 256.f, d0));
+                fin[0] = fmaf(s * xv.y, fmaf(-z, xv.x, dot), fin[0]);
+              }
             }
           }
         }
       }
-      if constexpr (kStream) {
-        // this warp has read the round's (sum, 2^-p) pairs: its share of the digit-ring slots is released
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(bempty_a + (t & (BD - 1)) * 8);
-          if (two) mbar_arrive(bempty_a + ((t + 1) & (BD - 1)) * 8);
+      } else {
+        // Per step: both groups' tensor-memory loads in flight together, one wait, and the step's D slot goes
+        // back at once (the issuer of step t + DD2 is waiting for it); then the two groups are added up. (With
+        // 24-column blocks the registers only allow one group at a time.)
+        constexpr int kInFlight = NLD <= 16 ? 2 : 1;
+        uint32_t dv[kInFlight][NLD];
+        auto add_group = [&](const uint32_t* d, uint32_t szv, int g) {
+          const float2* xs_g = xs_tab + g * M + m0;
+          const float s = __uint_as_float(szv & 0xFFFF0000u);
+          const float z = __uint_as_float(0x4B000000u | (szv & 0xFFu)) - 8388608.0f;
+#pragma unroll
+          for (int i = 0; i < TM; ++i) {
+            // No test for "token exists" here: the TM chains stay independent straight-line code. A set's
+            // tokens past M add up whatever their columns and the pair table's next entries hold, and are
+            // never stored.
+            const float2 xv = xs_g[i];  // (sum of X, 2^-p)
+            const float d0 = small_int_to_float(d[3 * i]);
+            const float d1 = small_int_to_float(d[3 * i + 1]);
+            const float d2 = small_int_to_float(d[3 * i + 2]);
+            const float dot = fmaf(d2, 65536.f, fmaf(d1, 256.f, d0));
+            fin[i] = fmaf(s * xv.y, fmaf(-z, xv.x, dot), fin[i]);
+          }
+        };
+#pragma unroll
+        for (int sI = 0; sI < 2; ++sI) {
+          if (sI == 0 || two) {
+            const int ts = t + sI;
+            const uint32_t ew = sI ? e1.x : e0.x;
+            const int ng = static_cast<int>((ew >> 16) & 1u) + 1;
+            const uint32_t d_t = lane_t + (ts & (DD2 - 1)) * GE::kDColsS;
+            const int g0 = static_cast<int>((ew >> 19) & 0xFFu);  // the step's first k group: row of the pair table
+            const uint32_t* side_s = side_r + ((ts % kSideSteps) * kStepGroups) * kTileRows;
+            auto release = [&]() {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(dempty_a + (ts & (DD2 - 1)) * 8);
+            };
+            if constexpr (kInFlight == 2) {
+              uint32_t sz[2];
+              tmem_ld_span<0, NLD>(d_t, dv[0]);
+              sz[0] = side_s[0];
+              if (ng == 2) {
+                tmem_ld_span<0, NLD>(d_t + N, dv[1]);
+                sz[1] = side_s[kTileRows];
+              }
+              tmem_wait_ld();
+              release();
+              add_group(dv[0], sz[0], g0);
+              if (ng == 2) add_group(dv[kInFlight - 1], sz[1], g0 + 1);
+            } else {
+              tmem_ld_span<0, NLD>(d_t, dv[0]);
+              const uint32_t sz0 = side_s[0], sz1 = side_s[kTileRows];
+              tmem_wait_ld();
+              if (ng == 1) release();
+              add_group(dv[0], sz0, g0);
+              if (ng == 2) {
+                tmem_ld_span<0, NLD>(d_t + N, dv[0]);
+                tmem_wait_ld();
+                release();
+                add_group(dv[0], sz1, g0 + 1);
+              }
+            }
+          }
         }
       }
       const uint2 el = two ? e1 : e0;  // the round's last step
@@ -980,13 +1052,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
     }
     };
     const int fset = warp < CW ? 0 : (warp - kWConv0) / CW + 1;
-    if (fset == 0) fixup(std::integral_constant<int, 0>{});
-    if constexpr (GE::FW >= 2) {
-      if (fset == 1 && GE::TM < M) fixup(std::integral_constant<int, 1>{});
-    }
-    if constexpr (GE::FW >= 3) {
-      if (fset == 2 && 2 * GE::TM < M) fixup(std::integral_constant<int, 2>{});
-    }
+    if (fset < GE::FW && fset * GE::TM < M) fixup(fset);
   }
 
   // every role ends here: tensor memory goes back only after all its readers and writers are done
@@ -1000,19 +1066,23 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
 
 // Pre-pass of the M >= 2 calls: one warp per (k group, token) turns the token's 128 bf16 values of the
 // group into three digit rows of the B operand and its (sum, 2^-p) pair, laid out per group exactly as
-// the main kernel's digit ring wants them: [8 chunks of 16 k][3 M rows] 16 B, then M pairs. Small CTAs
+// the main kernel's digit ring wants them ([8 chunks of 16 k][3 M rows] 16 B), the pairs as one [G][M] table
+// behind all groups' rows. Small CTAs
 // (four warps, at most 32 registers) so that they fit beside a resident main-kernel CTA of the previous
 // layer and are ready to run the moment that layer completes.
 __global__ void __launch_bounds__(128, 16) k_digits(const uint16_t* __restrict__ x, uint8_t* __restrict__ dig, int M,
-                                                    int K, int G, int db_bytes) {
+                                                    int K, int G, int db_bytes, int tm, int cb) {
   pdl_launch_dependents();
   pdl_wait();  // the previous kernel produced x (and the main kernel before it may still be reading `dig`)
   const int item = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (item >= G * M) return;
   const int g = item / M, m = item - g * M;
   const uint2 rv = __ldcg(reinterpret_cast<const uint2*>(x + static_cast<size_t>(m) * K + g * kGroup) + lane);
-  uint8_t* blk = dig + static_cast<size_t>(g) * db_bytes;
-  convert_group(rv, blk, 48 * M, m, reinterpret_cast<float2*>(blk + 384 * M) + m, lane);
+  float2* pairs = reinterpret_cast<float2*>(dig + static_cast<size_t>(G) * db_bytes);
+  // token m belongs to set m / tm; its digit rows are rows cb (m / tm) + 3 (m % tm) .. + 2 of every 16-k chunk,
+  // a chunk being db_bytes / 8 bytes (N rows of 16 bytes)
+  const int f = m / tm;
+  convert_group(rv, dig + static_cast<size_t>(g) * db_bytes, db_bytes >> 3, cb * f + 3 * (m - f * tm), pairs + g * M + m, lane);
 }
 
 __global__ void k_pairs_reduce(int32_t* ids, const Pair* pairs, int nranks, int M) {
@@ -1095,7 +1165,7 @@ int launch_cfg(SkinnyParams& p, int grid, cudaStream_t st, int smem_optin) {
       p.bdepth = c[1];
       p.bshift = c[1] == 8 ? 3 : (c[1] == 4 ? 2 : 1);
       p.b_bytes = p.bdepth * kStepGroups * p.db_bytes;
-      p.xs_bytes = 0;
+      p.xs_bytes = (p.G * p.M * 8 + 15) & ~15;
       smem = total_smem<MT, ST>(p.depth, kStageBytes, p.b_bytes, p.xs_bytes, p.bdepth);
       if (smem <= limit) {
         found = true;
@@ -1157,9 +1227,34 @@ bool gemv_cache_fits(int groups, int stage_bytes, int smem_optin) {
   return groups * (384 + 8) <= smem_optin - fixed;
 }
 
-// bytes of the pre-pass output per k group: 3 M digit rows of 128 k, then M (sum, 2^-p) pairs, rounded up
-// to the 16 bytes a bulk copy wants
-int digit_block_bytes(int M) { return 384 * M + ((8 * M + 15) & ~15); }
+// The template instance that serves M tokens (sets as balanced as the instances allow), and through it the
+// geometry the pre-pass has to write for: tokens per set, accumulator columns per set, rows of the B operand.
+int instance_for(int M) {
+  return M <= 2 ? M : (M <= 4 ? 4 : (M <= 6 ? 6 : (M <= 8 ? 8 : (M == 9 ? 9 : (M <= 12 ? 12 : (M <= 15 ? 15 : 16))))));
+}
+template <int MT>
+void geometry_of(int& tm, int& cb, int& nrows) {
+  tm = Geo<MT, true>::TM;
+  cb = Geo<MT, true>::CB;
+  nrows = Geo<MT, true>::N;
+}
+void set_geometry(int M, int& tm, int& cb, int& nrows) {
+  switch (instance_for(M)) {
+    case 1: geometry_of<1>(tm, cb, nrows); break;
+    case 2: geometry_of<2>(tm, cb, nrows); break;
+    case 4: geometry_of<4>(tm, cb, nrows); break;
+    case 6: geometry_of<6>(tm, cb, nrows); break;
+    case 8: geometry_of<8>(tm, cb, nrows); break;
+    case 9: geometry_of<9>(tm, cb, nrows); break;
+    case 12: geometry_of<12>(tm, cb, nrows); break;
+    case 15: geometry_of<15>(tm, cb, nrows); break;
+    default: geometry_of<16>(tm, cb, nrows); break;
+  }
+}
+// pre-pass output: per k group the B operand's digit rows, [8 chunks of 16 k][at most 48 rows] 16 B; behind all
+// groups' rows the table of (sum, 2^-p) pairs, G x M x 8 bytes (+ 16 so that a bulk copy of the rounded-up size
+// stays inside)
+size_t prepass_bytes(int G, int M) { return static_cast<size_t>(G) * (128 * 48 + 8 * M) + 16; }
 
 // A validated layer in either weight format, as the launcher sees it.
 struct LayerRef {
@@ -1179,18 +1274,17 @@ int layer_of(LayerRef& L, const w4a16_w8_weights_t* w) {
 
 template <int WB>
 int launch_batch(SkinnyParams& q, int grid, cudaStream_t st, int smem_optin) {
-  // MT is picked so that the token sets of the fix-up warps are balanced: sets of ceil(MT / sets) tokens
-  if (q.M == 1) return q.dig ? launch_cfg<1, WB, true>(q, grid, st, smem_optin) : launch_cfg<1, WB, false>(q, grid, st, smem_optin);
-  if (q.M == 2) return launch_cfg<2, WB>(q, grid, st, smem_optin);
-  if (q.M <= 4) return launch_cfg<4, WB>(q, grid, st, smem_optin);    // (2, M - 2)
-  if (q.M == 5) return launch_cfg<5, WB>(q, grid, st, smem_optin);    // (3, 2)
-  if (q.M == 6) return launch_cfg<6, WB>(q, grid, st, smem_optin);    // (3, 3)
-  if (q.M <= 8) return launch_cfg<8, WB>(q, grid, st, smem_optin);    // (4, M - 4)
-  if (q.M == 9) return launch_cfg<9, WB>(q, grid, st, smem_optin);    // (3, 3, 3)
-  if (q.M == 10) return launch_cfg<10, WB>(q, grid, st, smem_optin);  // (4, 4, 2)
-  if (q.M <= 12) return launch_cfg<12, WB>(q, grid, st, smem_optin);  // (4, 4, M - 8)
-  if (q.M <= 15) return launch_cfg<15, WB>(q, grid, st, smem_optin);  // (5, 5, M - 10)
-  return launch_cfg<16, WB>(q, grid, st, smem_optin);                 // (6, 6, 4)
+  switch (instance_for(q.M)) {
+    case 1: return q.dig ? launch_cfg<1, WB, true>(q, grid, st, smem_optin) : launch_cfg<1, WB, false>(q, grid, st, smem_optin);
+    case 2: return launch_cfg<2, WB>(q, grid, st, smem_optin);    // token sets (1, 1)
+    case 4: return launch_cfg<4, WB>(q, grid, st, smem_optin);    // (2, M - 2)
+    case 6: return launch_cfg<6, WB>(q, grid, st, smem_optin);    // (3, M - 3)
+    case 8: return launch_cfg<8, WB>(q, grid, st, smem_optin);    // (4, M - 4)
+    case 9: return launch_cfg<9, WB>(q, grid, st, smem_optin);    // (3, 3, 3)
+    case 12: return launch_cfg<12, WB>(q, grid, st, smem_optin);  // (4, 4, M - 8)
+    case 15: return launch_cfg<15, WB>(q, grid, st, smem_optin);  // (5, 5, M - 10)
+    default: return launch_cfg<16, WB>(q, grid, st, smem_optin);  // (8, 8)
+  }
 }
 
 int launch_skinny(SkinnyParams& p, const LayerRef* w, const uint16_t* x, int M, w4a16_scratch_t* s,
@@ -1230,7 +1324,6 @@ int launch_skinny(SkinnyParams& p, const LayerRef* w, const uint16_t* x, int M, 
     if (M > s->max_m || p.G > s->max_groups)
       return fail(W4A16_ESCRATCH, "scratch: sized for max_m = %d and in_f <= %d, got M = %d, in_f = %d", s->max_m,
                   s->max_groups * kGroup, M, w->in_f);
-    p.db_bytes = digit_block_bytes(M);
     uint8_t* dig = reinterpret_cast<uint8_t*>(s->xf) + pair_bytes(s->max_splits);
     p.dig = dig;
     cudaLaunchConfig_t cfg = {};
@@ -1242,7 +1335,10 @@ int launch_skinny(SkinnyParams& p, const LayerRef* w, const uint16_t* x, int M, 
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = config().pdl ? 1 : 0;
-    W4_CUDA(cudaLaunchKernelEx(&cfg, k_digits, x, dig, M, p.K, p.G, p.db_bytes));
+    int tm = 1, cb = 8, nrows = 16;
+    set_geometry(M, tm, cb, nrows);
+    p.db_bytes = 128 * nrows;
+    W4_CUDA(cudaLaunchKernelEx(&cfg, k_digits, x, dig, M, p.K, p.G, p.db_bytes, tm, cb));
   }
   if (int rc = w->wbits == 4 ? launch_batch<4>(p, grid, st, di->smem_optin) : launch_batch<8>(p, grid, st, di->smem_optin))
     return rc;
@@ -1335,7 +1431,7 @@ int w4a16_scratch_alloc(w4a16_scratch_t* s, int max_in, int max_out, int min_gro
   const size_t counters = counter_bytes(max_out);
   // per-CTA argmax pairs, then (max_m >= 2) the pre-pass output: digit rows of max_m tokens for every k group
   const size_t pairs = pair_bytes(s->max_splits) +
-                       (max_m >= 2 ? static_cast<size_t>(s->max_groups) * digit_block_bytes(max_m > 16 ? 16 : max_m) : 0);
+                       (max_m >= 2 ? prepass_bytes(s->max_groups, max_m > 16 ? 16 : max_m) : 0);
   void *xf = nullptr, *cn = nullptr, *pa = nullptr;
   cudaError_t e = cudaMalloc(&xf, pairs);
   if (e == cudaSuccess) e = cudaMalloc(&cn, counters);
