@@ -250,6 +250,129 @@ def other_configs(pkg, synth, torch, layers, scratch, stream, peak_hbm, peak_tf,
     return out
 
 
+def sharded_configs(pkg, synth, torch, dist, symm_mem, comm, rank, world, local, peak_hbm, peak_tf):
+    """The sharded forms of configs 2, 3 and 4 on `world` GPUs: the MLP layers of the verify pass (gate|up and
+    down column-sharded, fused all-gather, flag wait between them), the vocab-sharded lm_head with the pair
+    exchange inside the kernel, and the column-sharded prefill GEMM. Times are the slowest rank's."""
+    dev = torch.device("cuda", local)
+    gen = torch.Generator(device="cuda")
+    out = {}
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+
+    def sym(numel, dtype):
+        t = symm_mem.empty(numel, dtype=dtype, device=dev)
+        t.zero_()
+        h = symm_mem.rendezvous(t, dist.group.WORLD)
+        return t, [int(b) for b in h.buffer_ptrs]
+
+    def sync_all():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, iters, regions=3):
+        """CUDA graph of `iters` calls of fn(i), median over `regions` replays, max over ranks; us per call."""
+        with torch.cuda.stream(stream):
+            fn(0)
+            torch.cuda.synchronize()
+            dist.barrier()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for i in range(iters):
+                    fn(i)
+            g.replay()
+            torch.cuda.synchronize()
+            ms = time_regions(torch, stream, g.replay, 1, regions, sync_all)
+        t = torch.tensor(ms, device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return statistics.median([float(v) for v in t]) * 1e3 / iters
+
+    scratch = pkg.gemv_scratch_alloc(17408, 34816, 128, 16)
+    # ---- config 2: the MLP of the verify pass, sharded (a ring of 8 distinct layers: 8 x 140 MB per pass) ----
+    I, H, copies = 17408, 5120, 8
+    gu, dn = [], []
+    for c in range(copies):
+        b, e = pkg.shard_rows(2 * I, world, rank)
+        gu.append((make_layer_weights(pkg, torch, gen, e - b, H, 5000 + 10 * c + rank), b))
+        b, e = pkg.shard_rows(H, world, rank)
+        dn.append((make_layer_weights(pkg, torch, gen, e - b, I, 6000 + 10 * c + rank), b))
+    verify = {}
+    for M in (1, 9, 16):
+        x0 = torch.randn((M, H), device="cuda").to(torch.bfloat16)
+        x1 = torch.randn((M, I), device="cuda").to(torch.bfloat16)
+        y_gu, p_gu = sym(M * 2 * I, torch.bfloat16)
+        y_dn, p_dn = sym(M * H, torch.bfloat16)
+        torch.cuda.synchronize()
+        dist.barrier()
+
+        def mlp(i):
+            # gate|up, then down; each waits for every rank's flag of the layer before it. (down reads a
+            # pre-filled activation buffer: the SwiGLU between the two is not part of this path.)
+            w, b = gu[i % copies]
+            pkg.gemm_skinny_gather(p_gu, comm, 2 * I, b, w, x0, M, scratch, wait_prev=True, stream=stream)
+            w, b = dn[i % copies]
+            pkg.gemm_skinny_gather(p_dn, comm, H, b, w, x1, M, scratch, wait_prev=True, stream=stream)
+
+        us = timed(mlp, 4 * copies)  # long graphs: the ranks' launch skew is paid once per replay
+        alg = synth.algorithmic_bytes(2 * I, H, M) + synth.algorithmic_bytes(H, I, M)
+        verify[f"M{M}"] = {"us_per_mlp": round(us, 2), "aggregate_tbps": round(alg / us / 1e6, 3)}
+        del y_gu, y_dn
+    out["config2_sharded_mlp_gate_up_down"] = verify
+
+    # ---- config 3: vocab-sharded lm_head, one launch per call (ring of weight copies larger than L2) ----
+    V = 248320
+    b, e = pkg.shard_rows(V, world, rank)
+    shard_bytes = (e - b) * H // 2 + (e - b) * (H // 128) * 3
+    ncopy = max(2, min(16, -(-800 * (1 << 20) // shard_bytes)))
+    heads = [make_layer_weights(pkg, torch, gen, e - b, H, 7000 + 10 * c + rank) for c in range(ncopy)]
+    table, p_table = sym(world * 16 * 2, torch.int32)
+    head = {}
+    hscratch = pkg.gemv_scratch_alloc(H, e - b, 128, 16)
+    for M in (1, 9):
+        hx = torch.randn((M, H), device="cuda").to(torch.bfloat16)
+        ids = torch.zeros(M, dtype=torch.int32, device="cuda")
+        torch.cuda.synchronize()
+        dist.barrier()
+        us = timed(lambda i: pkg.lm_head_argmax_sharded(ids, p_table, comm, b, heads[i % ncopy], hx, M, hscratch,
+                                                        stream=stream), 4 * ncopy)
+        alg = synth.algorithmic_bytes(V, H, M, out_bytes=4 * M)
+        head[f"M{M}"] = {"us": round(us, 2), "aggregate_tbps": round(alg / us / 1e6, 3), "ring_copies": ncopy}
+    out["config3_sharded_lm_head_argmax_int4"] = head
+    for w in heads:
+        pkg.awq_free(w)
+    pkg.gemv_scratch_free(hscratch)
+
+    # ---- config 4: column-sharded prefill, M = 4096 ----
+    pre = {}
+    ws = pkg.gemm_workspace_alloc(4096)
+    Mp = 4096
+    for name, N, K, wl in (("gate_up_34816x5120", 2 * I, H, gu), ("down_5120x17408", H, I, dn)):
+        A = torch.randn((Mp, K), device="cuda").to(torch.bfloat16)
+        C, p_c = sym(Mp * N, torch.bfloat16)
+        torch.cuda.synchronize()
+        dist.barrier()
+
+        def pf(i):
+            w, b0 = wl[i % copies]
+            pkg.gemm_w4a16_sharded(p_c, comm, N, b0, w, A, Mp, ws, stream=stream)
+            pkg.wait_gather(comm, stream=stream)
+
+        us = timed(pf, 8)
+        tf = 2.0 * Mp * N * K / us / 1e6
+        recv = (world - 1) / world * Mp * N * 2
+        pre[name] = {"us": round(us, 1), "aggregate_tflops": round(tf, 1),
+                     "frac_of_measured_bf16_x_gpus": round(tf / (peak_tf * world), 3),
+                     "nvlink_bytes_received_per_rank": int(recv),
+                     "nvlink_bound_us_at_770GBps": round(recv / 770e3, 1)}
+        del C
+    out["config4_sharded_prefill_M4096"] = pre
+    pkg.gemm_workspace_free(ws)
+    for w, _ in gu + dn:
+        pkg.awq_free(w)
+    pkg.gemv_scratch_free(scratch)
+    return out
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -315,6 +438,11 @@ def run_ours(args):
         y_dev.zero_()
         hdl = symm_mem.rendezvous(y_dev, dist.group.WORLD)
         peer_bases = [int(b) for b in hdl.buffer_ptrs]
+        # completion flags: one 256-byte block per rank
+        flag_block = symm_mem.empty(64, dtype=torch.int32, device=torch.device("cuda", local))
+        flag_block.zero_()
+        fh = symm_mem.rendezvous(flag_block, dist.group.WORLD)
+        comm_obj = pkg.make_comm([int(b) for b in fh.buffer_ptrs], rank)
         torch.cuda.synchronize()
         dist.barrier()
     else:
@@ -328,8 +456,10 @@ def run_ours(args):
             x = x_dev[x_off[i]: x_off[i] + L["K"]]
             y = y_dev[y_off[i]: y_off[i] + L["N"]]
             if L["kind"] in sharded and comm == "fused":
-                pkg.gemm_skinny_sharded([b + 2 * y_off[i] for b in peer_bases], rank, L["N"], L["row0"], L["w"], x, 1,
-                                        scratch)
+                # the slice goes to every rank's arena, then this rank's flag; the launch itself first waits for
+                # every rank's flag of the previous layer (a real decode step consumes the gathered activations)
+                pkg.gemm_skinny_gather([b + 2 * y_off[i] for b in peer_bases], comm_obj, L["N"], L["row0"], L["w"], x, 1,
+                                       scratch, wait_prev=True)
             elif L["kind"] in sharded:
                 pkg.gemv_w4a16(y_parts[i], L["w"], x, scratch)
                 dist.all_gather_into_tensor(y, y_parts[i])
@@ -430,8 +560,11 @@ def run_ours(args):
     peak = float(peaks.get("hbm_gbs", FALLBACK_HBM_GBS))
     peak_tf = float(peaks.get("bf16_tflops", FALLBACK_BF16_TFLOPS))
     extras = None
-    if rank == 0 and world == 1 and os.environ.get("W4A16_BENCH_EXTRAS", "1") != "0":
-        extras = other_configs(pkg, synth, torch, layers, scratch, stream, peak, peak_tf, ms_step)
+    if os.environ.get("W4A16_BENCH_EXTRAS", "1") != "0":
+        if world == 1:
+            extras = other_configs(pkg, synth, torch, layers, scratch, stream, peak, peak_tf, ms_step)
+        elif comm == "fused":
+            extras = sharded_configs(pkg, synth, torch, dist, symm_mem, comm_obj, rank, world, local, peak, peak_tf)
         status = status or pkg.device_status()
 
     if rank == 0:
@@ -452,7 +585,7 @@ def run_ours(args):
         cfg = base_config(synth)
         run = {"launch": "cuda_graph" if graphed else "eager",
                "parallelism": "single" if world == 1 else
-               (f"column_shard_x{world}({len(sharded)}_of_6_layer_kinds)+fused_peer_store_all_gather"
+               (f"column_shard_x{world}({len(sharded)}_of_6_layer_kinds)+fused_peer_store_all_gather+flag_wait_per_layer"
                 if comm == "fused" else f"column_shard_x{world}+nccl_all_gather")}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,

@@ -187,6 +187,30 @@ int w4a16_w8_lm_head_argmax(int32_t* ids, uint16_t* logits, void* pairs, int row
                             const w4a16_w8_weights_t* w, const uint16_t* x, int M,
                             w4a16_scratch_t* s, void* stream);
 
+/* A linear layer (M <= 16 tokens) with its elementwise neighbours fused in; every part is optional:
+ *   ln_weight != NULL  RMSNorm in front (src/kernels/elementwise.cu:8-33, called at src/model/model.cu:681,774):
+ *                      xn = bf16(x * rsqrt(mean(x^2) + ln_eps) * (1 + ln_weight)), the layer multiplies xn;
+ *                      xn_out (may be NULL) receives xn [M][in_f] for callers that need it elsewhere.
+ *   W4A16_EPILOGUE_SWIGLU    swiglu (elementwise.cu:40-49, model.cu:781): the weights hold gate and up rows
+ *                      INTERLEAVED (w4a16_repack_into_swiglu), y is [M][out_f / 2]:
+ *                      y = bf16(g / (1 + exp(-g)) * u) with g, u the bf16-rounded gate and up outputs.
+ *   W4A16_EPILOGUE_RESIDUAL  residual_add (elementwise.cu:35-38, model.cu:777,785): y [M][out_f] is the running
+ *                      hidden state, updated in place: y = bf16(float(y) + float(bf16(W x))).
+ * The scratch must have been allocated with max_m >= 2 whenever ln_weight is given (the norm runs in the
+ * pre-pass kernel that otherwise only serves M >= 2). */
+#define W4A16_EPILOGUE_NONE 0
+#define W4A16_EPILOGUE_SWIGLU 1
+#define W4A16_EPILOGUE_RESIDUAL 2
+int w4a16_linear_fused(uint16_t* y, const w4a16_weights_t* w, const uint16_t* x, int M,
+                       const uint16_t* ln_weight, float ln_eps, uint16_t* xn_out, int epilogue,
+                       w4a16_scratch_t* s, void* stream);
+/* awq_repack_into for a fused gate|up layer that will run with W4A16_EPILOGUE_SWIGLU: logical row o of the
+ * [gate (inter rows) | up (inter rows)] layer lands in physical row 2 o (gate) or 2 (o - inter) + 1 (up), so
+ * that a gate row and its up row are neighbours. dst_row_offset and out_f are in logical rows, as for
+ * w4a16_repack_into; `inter` is the logical number of gate rows of the container (out_f_total / 2). */
+int w4a16_repack_into_swiglu(const w4a16_weights_t* w, int dst_row_offset, const uint32_t* packed,
+                             const uint16_t* scale, const uint32_t* zp, int out_f, int inter, void* stream);
+
 /* w4a16_dequant_rows (gemm_w4a16.cuh:45-48, gemm_w4a16.cu:15-38,56-61): rows
  * [row0,row0+nrows) -> row-major bf16 [nrows][in_f], bf16(float(q-zp)*float(s)). */
 int w4a16_dequant_rows(uint16_t* dst, const w4a16_weights_t* w, int row0, int nrows, void* stream);
@@ -203,6 +227,51 @@ int w4a16_gemm_prefill(uint16_t* C, const w4a16_weights_t* w, const uint16_t* A,
  * counterpart (the reference is single-GPU; README.md:123). Rank r of nranks owns
  * rows [row_begin,row_end) of an out_f-row layer; both are multiples of 16. */
 int w4a16_shard_rows(int out_f, int nranks, int rank, int* row_begin, int* row_end);
+/* Completion flags of the fused exchanges. Every rank owns one 256-byte block of zero-initialised,
+ * peer-mapped device memory (a symmetric-memory allocation, an IPC mapping ...): words [0, nranks) are
+ * counters written by the ranks (word r by rank r: every signalling launch adds 65536 in total, each CTA
+ * its share with a system-scope release add over NVLink right after its own last store), word 16 is the
+ * rank's own count of signalling launches. blocks[r] is rank r's block as mapped here; blocks[rank] is the local one. All ranks must issue
+ * the same sequence of signalling launches on a communicator (every w4a16_*_gather / *_sharded call below
+ * signals once). Zero the blocks and make that visible on every rank (a host barrier) before the first
+ * call. Every wait is bounded (about a second): on expiry the waiting kernel records W4A16_ETIMEOUT in
+ * the device status word and carries on. No reference counterpart (the reference is single-GPU). */
+typedef struct w4a16_comm {
+  uint32_t* blocks[8];
+  int nranks, rank;
+} w4a16_comm_t;
+/* w4a16_gemm_skinny_sharded with the completion signal: when the grid's last CTA has stored its slice,
+ * this rank's flag is raised on every rank. wait_prev != 0: before x is read, the kernel waits until
+ * every rank has signalled its PREVIOUS launch on this communicator, i.e. x may be the gathered output
+ * of that launch (layer i+1 consuming layer i without a host barrier or a collective in between). */
+int w4a16_gemm_skinny_gather(uint16_t* const* y_peers, const w4a16_comm_t* comm, int wait_prev,
+                             int out_f_total, int row_begin, const w4a16_weights_t* w_shard,
+                             const uint16_t* x, int M, w4a16_scratch_t* s, void* stream);
+/* For consumers that are not kernels of this library: one tiny kernel on `stream` that returns once every
+ * rank has signalled the last launch of this communicator (bounded; W4A16_ETIMEOUT in the status word
+ * when the wait runs out). */
+int w4a16_wait_gather(const w4a16_comm_t* comm, void* stream);
+/* Vocab-sharded lm_head in ONE launch: the fused per-shard argmax, then this rank's M (max, global index)
+ * pairs are stored into every rank's pair table (pairs_peers[r]: rank r's table of nranks x 16 pairs of
+ * {float, int32}, peer-mapped, 8-byte aligned), the flag is raised, the other ranks' pairs are awaited
+ * and reduced: larger value, else lower index. ids[M] is complete on every rank when the kernel ends;
+ * 8 M bytes per peer cross the link, no logits. row_offset = first vocabulary row of this shard. */
+int w4a16_lm_head_argmax_sharded(int32_t* ids, void* const* pairs_peers, const w4a16_comm_t* comm,
+                                 int wait_prev, int row_offset, const w4a16_weights_t* w_shard,
+                                 const uint16_t* x, int M, w4a16_scratch_t* s, void* stream);
+int w4a16_w8_lm_head_argmax_sharded(int32_t* ids, void* const* pairs_peers, const w4a16_comm_t* comm,
+                                    int wait_prev, int row_offset, const w4a16_w8_weights_t* w_shard,
+                                    const uint16_t* x, int M, w4a16_scratch_t* s, void* stream);
+
+/* gemm_w4a16 on this rank's shard of a column-sharded layer: the epilogue stores every finished tile into
+ * every rank's full C[M][out_f_total] at column row_begin (plain peer stores over NVLink, overlapped with
+ * the tensor-core work on the next tiles), then raises this rank's flag; a consumer waits with
+ * w4a16_wait_gather. Each rank receives (nranks - 1) / nranks of M x out_f_total x 2 bytes, which bounds
+ * the call at large M (285 MB for M = 4096 on the gate|up layer). No reference counterpart. */
+int w4a16_gemm_prefill_sharded(uint16_t* const* C_peers, const w4a16_comm_t* comm, int out_f_total,
+                               int row_begin, const w4a16_weights_t* w_shard, const uint16_t* A, int M,
+                               w4a16_workspace_t* ws, void* stream);
+
 /* Skinny GEMM on this rank's shard whose epilogue stores the [M][shard rows] slice
  * straight into every rank's full Y[M][out_f_total] at column row_begin: the
  * all-gather fused into the kernel over NVLink peer stores. y_peers[nranks] are

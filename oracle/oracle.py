@@ -64,11 +64,14 @@ def lib():
                                             _i32p, C.c_void_p, C.c_void_p]
         L.oracle_quant_i4.argtypes = [_u16p, _i64, _i64, _i64, _u32p, _u16p, _u32p]
         L.oracle_quant_w8.argtypes = [_u16p, _i64, _i64, _i64, _i8p, _u16p]
+        L.oracle_rmsnorm.argtypes = [_u16p, _u16p, _i64, _i64, C.c_float, _u16p]
+        L.oracle_residual_add.argtypes = [_u16p, _u16p, _i64]
+        L.oracle_swiglu.argtypes = [_u16p, _i64, _i64, _u16p]
         L.oracle_gemm_w8_f64.argtypes = [_i8p, _u16p, _i64, _i64, _i64, _u16p, _i64, C.c_void_p, _i64, _f64p]
         for f in ("oracle_f32_to_bf16", "oracle_bf16_to_f32", "oracle_unpack_q", "oracle_unpack_zp",
                   "oracle_dequant_f32", "oracle_dequant_bf16", "oracle_gemm_f64", "oracle_gemm_f32",
                   "oracle_argmax_bf16", "oracle_lm_head_argmax", "oracle_quant_i4", "oracle_quant_w8",
-                  "oracle_gemm_w8_f64"):
+                  "oracle_gemm_w8_f64", "oracle_rmsnorm", "oracle_residual_add", "oracle_swiglu"):
             getattr(L, f).restype = None
         _lib = L
     return _lib
@@ -260,3 +263,29 @@ def argmax_with_gaps(y64):
         e = np.frexp(abs(best) if best != 0 else 1e-30)[1]
         gaps[m] = (best - second) / 2.0 ** (e - 8)
     return ids, gaps, logits
+
+
+# ------------------------------------------------------------------ elementwise neighbours of a linear layer
+def rmsnorm(x, w, eps=1e-6):
+    """bf16 bits [rows, dim], weights bf16 bits [dim] -> bf16 bits [rows, dim]: x * rsqrt(mean(x^2)+eps) * (1 + w)."""
+    x, w = _c(x, np.uint16), _c(w, np.uint16)
+    rows, dim = x.shape
+    out = np.empty((rows, dim), np.uint16)
+    lib().oracle_rmsnorm(x, w, rows, dim, eps, out)
+    return out
+
+
+def residual_add(h, x):
+    """bf16 bits: returns bf16(float(h) + float(x)) (the reference updates h in place)."""
+    out = _c(h, np.uint16).copy()
+    lib().oracle_residual_add(out.reshape(-1), _c(x, np.uint16).reshape(-1), out.size)
+    return out
+
+
+def swiglu(fused):
+    """bf16 bits [rows, 2*inter] laid out [gate | up] -> bf16 bits [rows, inter] = silu(gate) * up."""
+    fused = _c(fused, np.uint16)
+    rows, two = fused.shape
+    out = np.empty((rows, two // 2), np.uint16)
+    lib().oracle_swiglu(fused, rows, two // 2, out)
+    return out

@@ -21,6 +21,7 @@
  *   min/max int4 quantiser ........... src/model/model.cu:140-172
  *   symmetric int8 quantiser ......... src/kernels/gemv_w4a16.cu:479-499
  *   int8 GEMV / GEMM (s * sum q x) ... src/kernels/gemv_w4a16.cu:501-523,525-568
+ *   rmsnorm, residual_add, swiglu .... src/kernels/elementwise.cu:8-49,162-171
  *
  * On-disk ("compressed-tensors pack-quantized") layout, all little endian:
  *   packed [N][K/8] u32 : element i of a row is bits [4(i%8), 4(i%8)+4) of word i/8
@@ -328,4 +329,53 @@ ORACLE_API void oracle_gemm_w8_f64(const int8_t* q, const uint16_t* scale, int64
       out[m * R + r] = acc;
     }
   }
+}
+
+/* ---- the elementwise neighbours of a linear layer (fp32 arithmetic, bf16 in and out) ----
+ * rmsnorm: 256 threads per row; thread t sums x[i]^2 over i = t, t+256, ... in fp32, a shuffle tree adds
+ * the 32 lanes of a warp (offsets 16, 8, 4, 2, 1), thread 0 adds the 8 warp sums in order;
+ * inv = rsqrt(sum / dim + eps); out = bf16(x * inv * (1 + w)). The summation order is restated exactly;
+ * rsqrtf is the correctly rounded 1/sqrt here (the device instruction may differ in the last place). */
+ORACLE_API void oracle_rmsnorm(const uint16_t* x, const uint16_t* w, int64_t rows, int64_t dim, float eps,
+                               uint16_t* out) {
+  for (int64_t r = 0; r < rows; ++r) {
+    const uint16_t* xr = x + r * dim;
+    float part[256];
+    for (int t = 0; t < 256; ++t) {
+      float a = 0.f;
+      for (int64_t i = t; i < dim; i += 256) {
+        const float v = bf16_to_f32(xr[i]);
+        a += v * v;
+      }
+      part[t] = a;
+    }
+    float warp[8];
+    for (int wv = 0; wv < 8; ++wv) {
+      float l[32];
+      for (int j = 0; j < 32; ++j) l[j] = part[wv * 32 + j];
+      for (int sft = 16; sft > 0; sft >>= 1)
+        for (int j = 0; j < 32; ++j) l[j] = l[j] + (j + sft < 32 ? l[j + sft] : l[j]);  /* shfl_down: lane 0 is exact */
+      warp[wv] = l[0];
+    }
+    float t = 0.f;
+    for (int wv = 0; wv < 8; ++wv) t += warp[wv];
+    const float inv = (float)(1.0 / sqrt((double)(t / (float)dim + eps)));
+    for (int64_t i = 0; i < dim; ++i)
+      out[r * dim + i] = f32_to_bf16(bf16_to_f32(xr[i]) * inv * (1.0f + bf16_to_f32(w[i])));
+  }
+}
+
+/* out[i] = bf16(float(out[i]) + float(x[i])) */
+ORACLE_API void oracle_residual_add(uint16_t* out, const uint16_t* x, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) out[i] = f32_to_bf16(bf16_to_f32(out[i]) + bf16_to_f32(x[i]));
+}
+
+/* fused [rows][2 inter] = [gate | up] -> out [rows][inter] = bf16(g / (1 + exp(-g)) * u), fp32 */
+ORACLE_API void oracle_swiglu(const uint16_t* fused, int64_t rows, int64_t inter, uint16_t* out) {
+  for (int64_t r = 0; r < rows; ++r)
+    for (int64_t i = 0; i < inter; ++i) {
+      const float g = bf16_to_f32(fused[r * 2 * inter + i]);
+      const float u = bf16_to_f32(fused[r * 2 * inter + inter + i]);
+      out[r * inter + i] = f32_to_bf16((g / (1.f + expf(-g))) * u);
+    }
 }

@@ -52,6 +52,11 @@ class W8Weights(C.Structure):
         return self.out_f * self.in_f + self.out_f * self.num_groups * 2
 
 
+class Comm(C.Structure):
+    """w4a16_comm_t: every rank's 256-byte flag block (peer-mapped), number of ranks, this rank."""
+    _fields_ = [("blocks", C.c_void_p * 8), ("nranks", C.c_int), ("rank", C.c_int)]
+
+
 class Scratch(C.Structure):
     """w4a16_scratch_t == qwen::GemvScratch (src/kernels/gemv_w4a16.cuh:94-104)."""
     _fields_ = [("xf", C.c_void_p), ("xgsum", C.c_void_p), ("partial", C.c_void_p),
@@ -101,6 +106,20 @@ _SIGNATURES = {
     "w4a16_workspace_free": (C.c_int, [C.POINTER(Workspace)]),
     "w4a16_gemm_prefill": (C.c_int, [C.c_void_p, C.POINTER(Weights), C.c_void_p, C.c_int,
                                      C.POINTER(Workspace), C.c_void_p]),
+    "w4a16_gemm_skinny_gather": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(Comm), C.c_int, C.c_int, C.c_int,
+                                           C.POINTER(Weights), C.c_void_p, C.c_int, C.POINTER(Scratch), C.c_void_p]),
+    "w4a16_wait_gather": (C.c_int, [C.POINTER(Comm), C.c_void_p]),
+    "w4a16_lm_head_argmax_sharded": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(Comm), C.c_int, C.c_int,
+                                               C.POINTER(Weights), C.c_void_p, C.c_int, C.POINTER(Scratch), C.c_void_p]),
+    "w4a16_w8_lm_head_argmax_sharded": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(Comm), C.c_int, C.c_int,
+                                                  C.POINTER(W8Weights), C.c_void_p, C.c_int, C.POINTER(Scratch),
+                                                  C.c_void_p]),
+    "w4a16_gemm_prefill_sharded": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(Comm), C.c_int, C.c_int,
+                                             C.POINTER(Weights), C.c_void_p, C.c_int, C.POINTER(Workspace), C.c_void_p]),
+    "w4a16_linear_fused": (C.c_int, [C.c_void_p, C.POINTER(Weights), C.c_void_p, C.c_int, C.c_void_p, C.c_float,
+                                     C.c_void_p, C.c_int, C.POINTER(Scratch), C.c_void_p]),
+    "w4a16_repack_into_swiglu": (C.c_int, [C.POINTER(Weights), C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
+                                           C.c_int, C.c_void_p]),
     "w4a16_shard_rows": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "w4a16_gemm_skinny_sharded": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int, C.c_int,
                                             C.POINTER(Weights), C.c_void_p, C.c_int, C.POINTER(Scratch),
@@ -255,6 +274,64 @@ def gemm_skinny_sharded(y_peer_ptrs, rank: int, out_f_total: int, row_begin: int
     arr = (C.c_void_p * n)(*[C.c_void_p(p) for p in y_peer_ptrs])
     check(lib().w4a16_gemm_skinny_sharded(arr, n, rank, out_f_total, row_begin, C.byref(w), _ptr(x), M,
                                           C.byref(s), _stream(stream)))
+
+
+COMM_BLOCK_BYTES = 256
+
+
+def make_comm(block_ptrs, rank: int) -> Comm:
+    """block_ptrs: every rank's zero-initialised 256-byte flag block as mapped on this rank."""
+    c = Comm()
+    for i, ptr in enumerate(block_ptrs):
+        c.blocks[i] = ptr
+    c.nranks, c.rank = len(block_ptrs), rank
+    return c
+
+
+def _ptr_table(ptrs):
+    return (C.c_void_p * len(ptrs))(*[C.c_void_p(p) for p in ptrs])
+
+
+def gemm_skinny_gather(y_peer_ptrs, comm: Comm, out_f_total: int, row_begin: int, w: Weights, x, M: int, s: Scratch,
+                       wait_prev: bool = False, stream=None):
+    """Sharded skinny GEMM with the fused all-gather and its completion flag; wait_prev: x is the gathered
+    output of the previous launch on this communicator."""
+    check(lib().w4a16_gemm_skinny_gather(_ptr_table(y_peer_ptrs), C.byref(comm), 1 if wait_prev else 0, out_f_total,
+                                         row_begin, C.byref(w), _ptr(x), M, C.byref(s), _stream(stream)))
+
+
+def wait_gather(comm: Comm, stream=None):
+    check(lib().w4a16_wait_gather(C.byref(comm), _stream(stream)))
+
+
+def lm_head_argmax_sharded(ids, pair_table_ptrs, comm: Comm, row_offset: int, w, x, M: int, s: Scratch,
+                           wait_prev: bool = False, stream=None):
+    """Vocab-sharded lm_head in one launch (int4 or int8 weights): ids[M] complete on every rank."""
+    fn = lib().w4a16_w8_lm_head_argmax_sharded if isinstance(w, W8Weights) else lib().w4a16_lm_head_argmax_sharded
+    check(fn(_ptr(ids), _ptr_table(pair_table_ptrs), C.byref(comm), 1 if wait_prev else 0, row_offset, C.byref(w),
+             _ptr(x), M, C.byref(s), _stream(stream)))
+
+
+def gemm_w4a16_sharded(c_peer_ptrs, comm: Comm, out_f_total: int, row_begin: int, w: Weights, A, M: int,
+                       ws: Workspace, stream=None):
+    check(lib().w4a16_gemm_prefill_sharded(_ptr_table(c_peer_ptrs), C.byref(comm), out_f_total, row_begin, C.byref(w),
+                                           _ptr(A), M, C.byref(ws), _stream(stream)))
+
+
+EPILOGUE_NONE, EPILOGUE_SWIGLU, EPILOGUE_RESIDUAL = 0, 1, 2
+
+
+def awq_repack_into_swiglu(w: Weights, dst_row_offset: int, packed, scale, zp, inter: int, stream=None):
+    """awq_repack_into for a gate|up container that will run with the fused SwiGLU epilogue (rows interleaved)."""
+    check(lib().w4a16_repack_into_swiglu(C.byref(w), dst_row_offset, _ptr(packed), _ptr(scale), _ptr(zp),
+                                         packed.shape[0], inter, _stream(stream)))
+
+
+def linear_fused(y, w: Weights, x, M: int, s: Scratch, ln_weight=None, ln_eps: float = 1e-6, xn_out=None,
+                 epilogue: int = EPILOGUE_NONE, stream=None):
+    """A linear layer with RMSNorm in front and / or SwiGLU or the residual add behind, in one call."""
+    check(lib().w4a16_linear_fused(_ptr(y), C.byref(w), _ptr(x), M, _ptr(ln_weight), ln_eps, _ptr(xn_out), epilogue,
+                                   C.byref(s), _stream(stream)))
 
 
 def device_status() -> int:

@@ -229,6 +229,49 @@ __device__ __forceinline__ uint32_t sub_bf16x2(uint32_t a, uint32_t b) {
   return d;
 }
 
+// ---- cross-rank flags: system-scope release adds into the peers' flag words, bounded polling with acquire ----
+// A rank's block: words [0, 8) are counters written by the ranks (word r by rank r), word 16 is this rank's own
+// count of signalling launches. Every signalling launch adds exactly kCommUnit to this rank's counter on every
+// rank - each CTA its share, right after its own last store, with release semantics - so "every rank's slice of
+// launch number s has landed" reads: counter[r] >= s * kCommUnit for every r. No CTA waits for another one, and
+// no second fence is needed: a CTA's release covers the stores its threads made before the CTA barrier.
+constexpr int kCommSeq = 16;                   // word of a rank's block
+constexpr unsigned kCommUnit = 1u << 16;       // what one launch adds in total (more than any grid has CTAs)
+constexpr uint32_t kFlagSpinLimit = 1u << 20;  // polls (each a system-scope load and a short sleep): about a second
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_add_release_sys(unsigned* p, unsigned v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Waits until every rank's counter in this rank's block has reached launch number `seq`; false if the limit ran out.
+__device__ __forceinline__ bool wait_flags(const unsigned* local, int n, unsigned seq, uint32_t limit) {
+  const unsigned target = seq * kCommUnit;
+  for (int r = 0; r < n; ++r) {
+    uint32_t spins = 0;
+    while (static_cast<int>(ld_acquire_sys(local + r) - target) < 0) {
+      if (++spins > limit) return false;
+      __nanosleep(64);
+    }
+  }
+  return true;
+}
+// Called by ONE thread of every CTA after the CTA-wide barrier that follows its last store: this CTA's share of
+// the launch's signal goes to every rank (the local block included); CTA 0 also counts the launch.
+__device__ __forceinline__ void signal_cta_done(unsigned* local, unsigned* const* peers, int n, int rank) {
+  const unsigned share = blockIdx.x == 0 ? kCommUnit - (gridDim.x - 1) : 1u;
+  for (int r = 0; r < n; ++r) red_add_release_sys(peers[r] + rank, share);
+  if (blockIdx.x == 0) atomicAdd(local + kCommSeq, 1u);
+}
+// The same for a launch whose exchange is done by a single thread of the grid (the vocab-sharded lm_head).
+__device__ __forceinline__ unsigned signal_whole_launch(unsigned* local, unsigned* const* peers, int n, int rank) {
+  const unsigned seq = atomicAdd(local + kCommSeq, 1u) + 1u;
+  for (int r = 0; r < n; ++r) red_add_release_sys(peers[r] + rank, kCommUnit);
+  return seq;
+}
+
 __device__ __forceinline__ float bf16_bits_to_float(uint16_t h) {
   return __uint_as_float(static_cast<uint32_t>(h) << 16);
 }

@@ -47,9 +47,17 @@ struct PrefillParams {
   CUtensorMap amap;   // A as [M][K] bf16, box 64 k x 256 tokens, 128-byte swizzle, zero fill
   const uint8_t* stream;
   const uint16_t* A;  // [M][K] bf16
-  uint16_t* C;        // [M][N] bf16
+  uint16_t* C;        // [M][ldc] bf16; this launch's rows land in columns [col0, col0 + N)
   int M, N, K, G, row_tiles, tok_tiles;
+  long long ldc;
+  int col0;
   int* status;
+  // column-sharded call: the other ranks' C (peer-mapped) receive the same tile, then the completion flag
+  int npeers;
+  uint16_t* C_peers[8];
+  unsigned* comm_local;
+  unsigned* comm_peers[8];
+  int comm_n, comm_rank;
 };
 
 __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
@@ -295,7 +303,12 @@ __global__ void __launch_bounds__(kPWarps * 32, 1) k_prefill(const __grid_consta
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           const int tok = tt * TN + col0 + i;
-          if (tok < p.M) p.C[static_cast<size_t>(tok) * p.N + r] = float_to_bf16_bits(d[i]);
+          if (tok < p.M) {
+            const size_t o = static_cast<size_t>(tok) * p.ldc + p.col0 + r;
+            const uint16_t hb = float_to_bf16_bits(d[i]);
+            p.C[o] = hb;
+            for (int pq = 0; pq < p.npeers; ++pq) p.C_peers[pq][o] = hb;  // fused all-gather over NVLink
+          }
         }
       }
     }
@@ -307,6 +320,12 @@ __global__ void __launch_bounds__(kPWarps * 32, 1) k_prefill(const __grid_consta
   tc_fence_before();
   __syncwarp();
   if (lane == 0) mbar_arrive(alldone_a);
+  if (p.comm_local) {
+    // every store of this CTA comes from these eight warps: once they are all here, the CTA's share of the
+    // launch's completion signal goes to every rank
+    named_bar_sync(2, PW * 32);
+    if (tid == 0) signal_cta_done(p.comm_local, p.comm_peers, p.comm_n, p.comm_rank);
+  }
 }
 
 }  // namespace
@@ -336,8 +355,9 @@ int w4a16_workspace_free(w4a16_workspace_t* ws) {
   return W4A16_OK;
 }
 
-int w4a16_gemm_prefill(uint16_t* C, const w4a16_weights_t* w, const uint16_t* A, int M, w4a16_workspace_t* ws,
-                       void* stream) {
+namespace {
+int launch_prefill(PrefillParams& p, uint16_t* C, const w4a16_weights_t* w, const uint16_t* A, int M, w4a16_workspace_t* ws,
+                   void* stream) {
   if (int rc = check_weights(w)) return rc;
   W4_REQUIRE(C != nullptr && A != nullptr, "gemm_prefill: null matrix");
   W4_REQUIRE((reinterpret_cast<uintptr_t>(A) & 15) == 0, "gemm_prefill: A not 16-byte aligned");
@@ -345,7 +365,6 @@ int w4a16_gemm_prefill(uint16_t* C, const w4a16_weights_t* w, const uint16_t* A,
   W4_REQUIRE(ws != nullptr, "gemm_prefill: null workspace");
   const DeviceInfo* di = device_info();
   if (!di) return W4A16_ECUDA;
-  PrefillParams p = {};
   p.stream = reinterpret_cast<const uint8_t*>(w->qweight);
   p.A = A;
   p.C = C;
@@ -390,6 +409,38 @@ int w4a16_gemm_prefill(uint16_t* C, const w4a16_weights_t* w, const uint16_t* A,
   k_prefill<<<grid, kPWarps * 32, kPSmem, static_cast<cudaStream_t>(stream)>>>(p);
   W4_CUDA(cudaGetLastError());
   return W4A16_OK;
+}
+}  // namespace
+
+int w4a16_gemm_prefill(uint16_t* C, const w4a16_weights_t* w, const uint16_t* A, int M, w4a16_workspace_t* ws,
+                       void* stream) {
+  PrefillParams p = {};
+  p.ldc = w ? w->out_f : 0;
+  return launch_prefill(p, C, w, A, M, ws, stream);
+}
+
+int w4a16_gemm_prefill_sharded(uint16_t* const* C_peers, const w4a16_comm_t* comm, int out_f_total, int row_begin,
+                               const w4a16_weights_t* w_shard, const uint16_t* A, int M, w4a16_workspace_t* ws,
+                               void* stream) {
+  W4_REQUIRE(C_peers != nullptr && comm != nullptr && w_shard != nullptr, "gemm_prefill_sharded: null argument");
+  if (comm->nranks < 1 || comm->nranks > 8 || comm->rank < 0 || comm->rank >= comm->nranks)
+    return fail(W4A16_ECOMM, "gemm_prefill_sharded: rank %d of %d (1..8 ranks)", comm->rank, comm->nranks);
+  if (row_begin < 0 || row_begin % kRowGranule != 0 || row_begin + w_shard->out_f > out_f_total)
+    return fail(W4A16_ECOMM, "gemm_prefill_sharded: rows [%d,%d) outside [0,%d)", row_begin, row_begin + w_shard->out_f,
+                out_f_total);
+  PrefillParams p = {};
+  p.ldc = out_f_total;
+  p.col0 = row_begin;
+  for (int r = 0; r < comm->nranks; ++r) {
+    if (C_peers[r] == nullptr || comm->blocks[r] == nullptr)
+      return fail(W4A16_ECOMM, "gemm_prefill_sharded: null output or flag block of rank %d", r);
+    p.comm_peers[r] = comm->blocks[r];
+    if (r != comm->rank) p.C_peers[p.npeers++] = C_peers[r];
+  }
+  p.comm_local = comm->blocks[comm->rank];
+  p.comm_n = comm->nranks;
+  p.comm_rank = comm->rank;
+  return launch_prefill(p, C_peers[comm->rank], w_shard, A, M, ws, stream);
 }
 
 }  // extern "C"

@@ -135,9 +135,24 @@ struct SkinnyParams {
   int row_offset;
   void* cta_pairs;  // [grid][16] x {float,int}
   int* status;
-  int npeers;  // extra destinations for y (fused all-gather), 0 = none
-  uint16_t* y_peers[8];
+  int npeers;  // extra destinations for y (fused all-gather / partial sums for a cross-rank reduction), 0 = none
+  void* y_peers[8];  // bf16, or fp32 when y_f32
+  const uint16_t* ln_w;  // RMSNorm fused into the pre-pass: x is normalised with these bf16 weights first (null: off)
+  float ln_eps;
+  uint16_t* xn_out;      // optional [M][K] copy of the normalised activations
+  int epilogue;      // kEpiNone, kEpiSwiglu (rows interleaved gate, up, gate, up ...: y[m][row / 2] = silu(gate) * up)
+                     // or kEpiResidual (y[m][row] = bf16(float(y[m][row]) + float(bf16(sum))))
+  // cross-rank completion flags of the sharded calls (all null / 0 when unused). A rank's block:
+  // words [0, 8) counters written by the ranks (word r by rank r), word 16 this rank's count of signalling launches.
+  unsigned* comm_local;
+  unsigned* comm_peers[8];   // every rank's block, index = rank (the local one included)
+  int comm_n, comm_rank;
+  int comm_wait;             // before x is read: wait until every rank has signalled its previous launch
+  int comm_signal;           // after the last store of the grid: raise this rank's flag on every rank
+  void* pairs_peers[8];      // vocab-sharded lm_head: every rank's [ranks][16] table of (max, index) pairs
 };
+
+constexpr int kEpiNone = 0, kEpiSwiglu = 1, kEpiResidual = 2;
 
 struct Pair {
   float v;
@@ -306,7 +321,7 @@ __device__ __forceinline__ float small_int_to_float(uint32_t v) {
 // whole K range of a token fits: 384 bytes per group for M = 1.
 template <int MT, bool ST>
 __host__ __device__ constexpr int bar_count(int depth, int bdepth) {
-  return 2 * depth + Geo<MT, ST>::AD2 + 2 * Geo<MT, ST>::DD2 + 2 + (ST ? 2 * bdepth : 0);
+  return 2 * depth + Geo<MT, ST>::AD2 + 2 * Geo<MT, ST>::DD2 + 2 + (ST ? 2 * bdepth : 0) + 1;
 }
 template <int MT, bool ST>
 __host__ __device__ inline int total_smem(int depth, int stage_bytes, int b_bytes, int xs_bytes, int bdepth) {
@@ -355,7 +370,10 @@ __device__ __forceinline__ void convert_group(uint2 rv, uint8_t* bslot, int lbo,
   if (lane == 0) *xs = make_float2(static_cast<float>(tot), inv);
 }
 
-template <int MT, int WB, bool ST>
+// COMM: the cross-rank flag code (wait before x is read, signal after the last store, the pair exchange of the
+// vocab-sharded head) is compiled into separate instances, so that single-GPU launches run exactly the code
+// they ran without it.
+template <int MT, int WB, bool ST, bool COMM>
 __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   using GE = Geo<MT, ST>;
   constexpr int kBlock = Fmt<WB>::kBlock, kStageBytes = Fmt<WB>::kStage;
@@ -410,6 +428,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   const uint32_t tmemrdy_a = bready_a + 8;          // tensor memory allocated, base address published
   const uint32_t bfull_a = tmemrdy_a + 8;           // [BD]  M >= 2: digit rows of a step landed (tx bytes)
   const uint32_t bempty_a = bfull_a + BD * 8;       // [BD]  M >= 2: the step's MMAs have completed (seen by the first fix-up warp)
+  const uint32_t commrdy_a = bfull_a + (kStream ? 2 * BD : 0) * 8;  // every rank's flag of the previous launch has been seen
 
   if (tid < 256) ready[tid] = 0u;
   {
@@ -445,6 +464,22 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
     // warps and the issuers do not take part: they fill the A ring from the weights meanwhile. x comes straight from global memory (L2); a round's loads are all in
     // flight before its first conversion.
     pdl_wait();  // the previous kernel produced x
+    if (COMM && p.comm_wait) {
+      // x is a gathered output: every rank's slice of it must have landed here. ONE thread of the CTA polls
+      // the flags (thousands of pollers on one line would stand in the way of the very store they wait
+      // for); the other converting warps park on a barrier of the CTA.
+      if (warp == kWConv0) {
+        if (lane == 0) {
+          if (!wait_flags(p.comm_local, p.comm_n, *reinterpret_cast<volatile unsigned*>(p.comm_local + kCommSeq),
+                          kFlagSpinLimit))
+            atomicExch(p.status, W4A16_ETIMEOUT);
+          mbar_arrive(commrdy_a);
+        }
+        __syncwarp();
+      } else if (!wait_h(commrdy_a, 0, p.hint, 4 * kSpinLimit)) {
+        atomicExch(p.status, W4A16_ETIMEOUT);
+      }
+    }
     const int ti = warp < CW ? warp : (warp == 14 ? CW : warp - kWConv0 + CW + 1);
     const int cnt = (u1 - u0 < G) ? u1 - u0 : G;
     const int total = cnt * M;  // (group, token) items; item i belongs to warp i % kTeam
@@ -754,9 +789,29 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
       best_i[i] = INT_MAX;
     }
 
-    // Final values of one row tile are in registers: write them out / fold into the argmax.
+    // Final values of one row tile are in registers: write them out (plain, with the SwiGLU or the residual add
+    // fused in, to the peers of a sharded call) and / or fold them into the running argmax.
     auto finalize = [&](int tile, const float(&v)[TM]) {
       const int row = tile * kTileRows + r;
+      if (p.epilogue == kEpiSwiglu) {
+        // SwiGLU fused in (replaces the separate kernel over the [M][2 I] buffer): rows come in (gate, up) pairs
+        // on neighbouring lanes; both are rounded to bf16 first, as the unfused path stores them, then
+        // y[m][row / 2] = bf16(gate / (1 + exp(-gate)) * up). All lanes take part in the exchange.
+#pragma unroll
+        for (int i = 0; i < TM; ++i) {
+          const int m = m0 + i;
+          if (m >= M) continue;  // (the same for the whole warp)
+          const float mine = bf16_bits_to_float(float_to_bf16_bits(v[i]));
+          const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+          if (!(lane & 1) && row < p.N) {
+            const uint16_t hb = float_to_bf16_bits((mine / (1.f + expf(-mine))) * other);
+            const size_t o = static_cast<size_t>(m) * p.ldy + p.y_col0 + (row >> 1);
+            static_cast<uint16_t*>(p.y)[o] = hb;
+            for (int pq = 0; pq < p.npeers; ++pq) static_cast<uint16_t*>(p.y_peers[pq])[o] = hb;
+          }
+        }
+        return;
+      }
       if (row >= p.N) return;  // zero-padded rows of the last tile
 #pragma unroll
       for (int i = 0; i < TM; ++i) {
@@ -765,9 +820,17 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
         const uint16_t hb = float_to_bf16_bits(v[i]);
         if (p.y) {
           const size_t o = static_cast<size_t>(m) * p.ldy + p.y_col0 + row;
-          if (p.y_f32) static_cast<float*>(p.y)[o] = v[i];
-          else static_cast<uint16_t*>(p.y)[o] = hb;
-          for (int pq = 0; pq < p.npeers; ++pq) p.y_peers[pq][o] = hb;
+          if (p.y_f32) {
+            static_cast<float*>(p.y)[o] = v[i];
+            for (int pq = 0; pq < p.npeers; ++pq) static_cast<float*>(p.y_peers[pq])[o] = v[i];
+          } else if (p.epilogue == kEpiResidual) {
+            // residual add fused in: the running hidden state is read, the bf16-rounded sum added, written back
+            uint16_t* h = static_cast<uint16_t*>(p.y) + o;
+            *h = float_to_bf16_bits(bf16_bits_to_float(*h) + bf16_bits_to_float(hb));
+          } else {
+            static_cast<uint16_t*>(p.y)[o] = hb;
+            for (int pq = 0; pq < p.npeers; ++pq) static_cast<uint16_t*>(p.y_peers[pq])[o] = hb;
+          }
         }
         if (p.argmax) {
           const float lv = bf16_bits_to_float(hb);
@@ -778,7 +841,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
         }
       }
     };
-
 
     bool ok = team_ok;
     constexpr int GB = GE::GB;
@@ -938,9 +1000,11 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
       if ((el.x >> 17) & 1u) {
         // ---- end of this CTA's segment of row tile el.y ----
         const int tile = static_cast<int>(el.y);
-        if ((el.x >> 18) & 1u) {
-          finalize(tile, fin);
-        } else {
+        bool last = ((el.x >> 18) & 1u) != 0;  // a whole tile is final at once
+        float v[TM];
+#pragma unroll
+        for (int i = 0; i < TM; ++i) v[i] = fin[i];
+        if (!last) {
           // split tile: this warp publishes its 32 rows and moves on; no CTA-wide barrier
           // first and last CTA whose unit range touches this tile (32-bit: U * gridDim.x < 2^32, host-checked)
           const uint32_t X0 = static_cast<uint32_t>(tile) * G, Uu = static_cast<uint32_t>(U);
@@ -959,8 +1023,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
             // The last ticket for these rows: every other piece is already in memory, so this warp adds
             // them up right away (the D ring is deep enough to absorb the pause), in a fixed order.
             if (lane == 0) tickets[tile * CW + q] = 0;  // leave it clean for the next launch
+            last = true;
             __syncwarp();
-            float v[TM];
 #pragma unroll
             for (int i = 0; i < TM; ++i) v[i] = 0.f;
             // four pieces' loads in flight at a time, added in CTA order: bitwise reproducible
@@ -986,9 +1050,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
                     if (m0 + i < M) v[i] += piece[k][i];
                 }
             }
-            finalize(tile, v);
           }
         }
+        if (last) finalize(tile, v);
 #pragma unroll
         for (int i = 0; i < TM; ++i) fin[i] = 0.f;
       }
@@ -1045,9 +1109,32 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
           if (better(qv.v, qv.i, b.v, b.i)) b = qv;
         }
         const int idx = (b.i == INT_MAX) ? 0 : b.i;  // nothing finite: index 0, as a plain scan gives
-        if (p.ids) p.ids[tid] = idx + p.row_offset;
-        if (p.pairs_out)
-          static_cast<Pair*>(p.pairs_out)[tid] = Pair{b.v, (b.i == INT_MAX) ? INT_MAX : b.i + p.row_offset};
+        const Pair mine{b.v, (b.i == INT_MAX) ? INT_MAX : b.i + p.row_offset};
+        if (p.pairs_out) static_cast<Pair*>(p.pairs_out)[tid] = mine;
+        if (COMM && p.comm_signal) {
+          // vocab-sharded head: this rank's pair of every token goes to every rank's table (8 M bytes per
+          // peer, no logits cross the link), then the flag; then the same threads wait for the other ranks'
+          // pairs and pick the winner: larger value, else lower index.
+          for (int r = 0; r < p.comm_n; ++r) static_cast<Pair*>(p.pairs_peers[r])[p.comm_rank * 16 + tid] = mine;
+          __threadfence_system();
+          const unsigned mask = (M >= 32) ? 0xffffffffu : ((1u << M) - 1u);
+          __syncwarp(mask);
+          unsigned seq = 0;
+          if (tid == 0) seq = signal_whole_launch(p.comm_local, p.comm_peers, p.comm_n, p.comm_rank);
+          seq = __shfl_sync(mask, seq, 0);
+          if (!wait_flags(p.comm_local, p.comm_n, seq, kFlagSpinLimit)) atomicExch(p.status, W4A16_ETIMEOUT);
+          const Pair* tab = static_cast<const Pair*>(p.pairs_peers[p.comm_rank]);
+          Pair w{-FLT_MAX, INT_MAX};
+          for (int r = 0; r < p.comm_n; ++r) {
+            Pair qv;
+            qv.v = __ldcg(&tab[r * 16 + tid].v);
+            qv.i = __ldcg(&tab[r * 16 + tid].i);
+            if (better(qv.v, qv.i, w.v, w.i)) w = qv;
+          }
+          if (p.ids) p.ids[tid] = (w.i == INT_MAX) ? 0 : w.i;
+        } else if (p.ids) {
+          p.ids[tid] = idx + p.row_offset;
+        }
       }
     }
     };
@@ -1062,6 +1149,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
     tc_fence_after();
     tmem_dealloc(*reinterpret_cast<volatile uint32_t*>(tmem_slot), kTmemCols);
   }
+  // fused all-gather: every store of this CTA was issued before the barrier above
+  if (COMM && p.comm_signal && !p.argmax && tid == 0) signal_cta_done(p.comm_local, p.comm_peers, p.comm_n, p.comm_rank);
 }
 
 // Pre-pass of the M >= 2 calls: one warp per (k group, token) turns the token's 128 bf16 values of the
@@ -1071,18 +1160,60 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
 // (four warps, at most 32 registers) so that they fit beside a resident main-kernel CTA of the previous
 // layer and are ready to run the moment that layer completes.
 __global__ void __launch_bounds__(128, 16) k_digits(const uint16_t* __restrict__ x, uint8_t* __restrict__ dig, int M,
-                                                    int K, int G, int db_bytes, int tm, int cb) {
+                                                    int K, int G, int db_bytes, int tm, int cb,
+                                                    const unsigned* comm_local, int comm_n, int* status,
+                                                    const uint16_t* __restrict__ ln_w, float ln_eps,
+                                                    uint16_t* __restrict__ xn_out) {
   pdl_launch_dependents();
   pdl_wait();  // the previous kernel produced x (and the main kernel before it may still be reading `dig`)
+  if (comm_local) {
+    // x is a gathered output: every rank's slice of it must have landed here
+    if (threadIdx.x == 0 &&
+        !wait_flags(comm_local, comm_n, *reinterpret_cast<const volatile unsigned*>(comm_local + kCommSeq), kFlagSpinLimit))
+      atomicExch(status, W4A16_ETIMEOUT);
+    __syncthreads();
+  }
   const int item = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (item >= G * M) return;
   const int g = item / M, m = item - g * M;
-  const uint2 rv = __ldcg(reinterpret_cast<const uint2*>(x + static_cast<size_t>(m) * K + g * kGroup) + lane);
+  uint2 rv = __ldcg(reinterpret_cast<const uint2*>(x + static_cast<size_t>(m) * K + g * kGroup) + lane);
+  if (ln_w) {
+    // RMSNorm fused in (replaces the separate kernel in front of the linear layer): the token's
+    // inv = rsqrt(mean(x^2) + eps) over the whole row - every warp of the token recomputes it from L2 - then
+    // xn = bf16(x * inv * (1 + w)), rounded to bf16 as the unfused path stores it, and the digits are taken of xn.
+    const uint2* row = reinterpret_cast<const uint2*>(x + static_cast<size_t>(m) * K);
+    float ss = 0.f;
+    for (int j = lane; j < K / 4; j += 32) {
+      const uint2 q = __ldcg(row + j);
+      const float a0 = __uint_as_float(q.x << 16), a1 = __uint_as_float(q.x & 0xFFFF0000u);
+      const float a2 = __uint_as_float(q.y << 16), a3 = __uint_as_float(q.y & 0xFFFF0000u);
+      ss += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
+    }
+#pragma unroll
+    for (int off = 16; off; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    const float inv = rsqrtf(ss / static_cast<float>(K) + ln_eps);
+    const uint2 wq = __ldg(reinterpret_cast<const uint2*>(ln_w + g * kGroup) + lane);
+    auto nrm = [&](uint32_t xb, uint32_t wb) {  // both bf16 bit patterns in the high half
+      return static_cast<uint32_t>(float_to_bf16_bits(__uint_as_float(xb) * inv * (1.0f + __uint_as_float(wb))));
+    };
+    rv.x = nrm(rv.x << 16, wq.x << 16) | (nrm(rv.x & 0xFFFF0000u, wq.x & 0xFFFF0000u) << 16);
+    rv.y = nrm(rv.y << 16, wq.y << 16) | (nrm(rv.y & 0xFFFF0000u, wq.y & 0xFFFF0000u) << 16);
+    if (xn_out) reinterpret_cast<uint2*>(xn_out + static_cast<size_t>(m) * K + g * kGroup)[lane] = rv;
+  }
   float2* pairs = reinterpret_cast<float2*>(dig + static_cast<size_t>(G) * db_bytes);
   // token m belongs to set m / tm; its digit rows are rows cb (m / tm) + 3 (m % tm) .. + 2 of every 16-k chunk,
   // a chunk being db_bytes / 8 bytes (N rows of 16 bytes)
   const int f = m / tm;
   convert_group(rv, dig + static_cast<size_t>(g) * db_bytes, db_bytes >> 3, cb * f + 3 * (m - f * tm), pairs + g * M + m, lane);
+}
+
+// Stand-alone wait for consumers that are not kernels of this library: returns once every rank has
+// signalled the last gather (or sets W4A16_ETIMEOUT when the bounded wait runs out).
+__global__ void k_wait_gather(const unsigned* comm_local, int n, int* status) {
+  pdl_wait();
+  if (threadIdx.x == 0 &&
+      !wait_flags(comm_local, n, *reinterpret_cast<const volatile unsigned*>(comm_local + kCommSeq), kFlagSpinLimit))
+    atomicExch(status, W4A16_ETIMEOUT);
 }
 
 __global__ void k_pairs_reduce(int32_t* ids, const Pair* pairs, int nranks, int M) {
@@ -1145,10 +1276,10 @@ int cache_groups_for(int tiles, int G, int grid) {
   return per_cta < G ? per_cta : G;
 }
 
-template <int MT, int WB, bool ST>
+template <int MT, int WB, bool ST, bool COMM>
 int launch_kernel(const SkinnyParams& p, int grid, cudaStream_t st, int smem);
 
-template <int MT, int WB, bool ST = true>
+template <int MT, int WB, bool ST, bool COMM>
 int launch_cfg(SkinnyParams& p, int grid, cudaStream_t st, int smem_optin) {
   constexpr int kStageBytes = Fmt<WB>::kStage;
   constexpr bool kStream = ST;
@@ -1175,7 +1306,7 @@ int launch_cfg(SkinnyParams& p, int grid, cudaStream_t st, int smem_optin) {
     if (!found)
       return fail(W4A16_EINVAL, "decode kernel needs %d bytes of shared memory for M = %d; the device offers %d", smem,
                   p.M, smem_optin);
-    return launch_kernel<MT, WB, ST>(p, grid, st, smem);
+    return launch_kernel<MT, WB, ST, COMM>(p, grid, st, smem);
   }
   p.b_bytes = groups * 384 * p.M + 256;
   p.xs_bytes = groups * MT * 8;
@@ -1194,16 +1325,16 @@ int launch_cfg(SkinnyParams& p, int grid, cudaStream_t st, int smem_optin) {
   if (smem > smem_optin)
     return fail(W4A16_EINVAL, "decode kernel needs %d bytes of shared memory for in_f = %d, M = %d; the device offers %d",
                 smem, p.K, p.M, smem_optin);
-  return launch_kernel<MT, WB, ST>(p, grid, st, smem);
+  return launch_kernel<MT, WB, ST, COMM>(p, grid, st, smem);
 }
 
-template <int MT, int WB, bool ST>
+template <int MT, int WB, bool ST, bool COMM>
 int launch_kernel(const SkinnyParams& p, int grid, cudaStream_t st, int smem) {
   static int attr_set[64] = {};
   int dev = 0;
   W4_CUDA(cudaGetDevice(&dev));
   if (attr_set[dev & 63] < smem) {
-    W4_CUDA(cudaFuncSetAttribute(k_skinny<MT, WB, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    W4_CUDA(cudaFuncSetAttribute(k_skinny<MT, WB, ST, COMM>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set[dev & 63] = smem;
   }
   cudaLaunchConfig_t cfg = {};
@@ -1216,7 +1347,7 @@ int launch_kernel(const SkinnyParams& p, int grid, cudaStream_t st, int smem) {
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
   cfg.numAttrs = config().pdl ? 1 : 0;
-  W4_CUDA(cudaLaunchKernelEx(&cfg, k_skinny<MT, WB, ST>, p));
+  W4_CUDA(cudaLaunchKernelEx(&cfg, k_skinny<MT, WB, ST, COMM>, p));
   return W4A16_OK;
 }
 
@@ -1272,19 +1403,25 @@ int layer_of(LayerRef& L, const w4a16_w8_weights_t* w) {
   return W4A16_OK;
 }
 
+template <int WB, bool COMM>
+int launch_batch_c(SkinnyParams& q, int grid, cudaStream_t st, int smem_optin) {
+  switch (instance_for(q.M)) {
+    case 1: return q.dig ? launch_cfg<1, WB, true, COMM>(q, grid, st, smem_optin)
+                         : launch_cfg<1, WB, false, COMM>(q, grid, st, smem_optin);
+    case 2: return launch_cfg<2, WB, true, COMM>(q, grid, st, smem_optin);    // token sets (1, 1)
+    case 4: return launch_cfg<4, WB, true, COMM>(q, grid, st, smem_optin);    // (2, M - 2)
+    case 6: return launch_cfg<6, WB, true, COMM>(q, grid, st, smem_optin);    // (3, M - 3)
+    case 8: return launch_cfg<8, WB, true, COMM>(q, grid, st, smem_optin);    // (4, M - 4)
+    case 9: return launch_cfg<9, WB, true, COMM>(q, grid, st, smem_optin);    // (3, 3, 3)
+    case 12: return launch_cfg<12, WB, true, COMM>(q, grid, st, smem_optin);  // (4, 4, M - 8)
+    case 15: return launch_cfg<15, WB, true, COMM>(q, grid, st, smem_optin);  // (5, 5, M - 10)
+    default: return launch_cfg<16, WB, true, COMM>(q, grid, st, smem_optin);  // (8, 8)
+  }
+}
 template <int WB>
 int launch_batch(SkinnyParams& q, int grid, cudaStream_t st, int smem_optin) {
-  switch (instance_for(q.M)) {
-    case 1: return q.dig ? launch_cfg<1, WB, true>(q, grid, st, smem_optin) : launch_cfg<1, WB, false>(q, grid, st, smem_optin);
-    case 2: return launch_cfg<2, WB>(q, grid, st, smem_optin);    // token sets (1, 1)
-    case 4: return launch_cfg<4, WB>(q, grid, st, smem_optin);    // (2, M - 2)
-    case 6: return launch_cfg<6, WB>(q, grid, st, smem_optin);    // (3, M - 3)
-    case 8: return launch_cfg<8, WB>(q, grid, st, smem_optin);    // (4, M - 4)
-    case 9: return launch_cfg<9, WB>(q, grid, st, smem_optin);    // (3, 3, 3)
-    case 12: return launch_cfg<12, WB>(q, grid, st, smem_optin);  // (4, 4, M - 8)
-    case 15: return launch_cfg<15, WB>(q, grid, st, smem_optin);  // (5, 5, M - 10)
-    default: return launch_cfg<16, WB>(q, grid, st, smem_optin);  // (8, 8)
-  }
+  return (q.comm_wait || q.comm_signal) ? launch_batch_c<WB, true>(q, grid, st, smem_optin)
+                                         : launch_batch_c<WB, false>(q, grid, st, smem_optin);
 }
 
 int launch_skinny(SkinnyParams& p, const LayerRef* w, const uint16_t* x, int M, w4a16_scratch_t* s,
@@ -1314,14 +1451,14 @@ int launch_skinny(SkinnyParams& p, const LayerRef* w, const uint16_t* x, int M, 
   if (int rc = w4a16_scratch_check(s, w->out_f, M)) return rc;
   p.M = M;
   p.x = x;
-  const bool prepass = M >= 2 || (config().gemv_prepass && s->max_m >= 2 && p.G <= s->max_groups);
+  const bool prepass = M >= 2 || p.ln_w != nullptr || (config().gemv_prepass && s->max_m >= 2 && p.G <= s->max_groups);
   if (!prepass) {
     if (!gemv_cache_fits(cache_groups_for(p.tiles, p.G, grid), w->wbits == 4 ? Fmt<4>::kStage : Fmt<8>::kStage,
                          di->smem_optin))
       return fail(W4A16_EINVAL, "in_f = %d is too wide for the decode kernel's activation cache", w->in_f);
   } else {
     // the pre-pass: digit rows of all M tokens, once per call, into the scratch (behind the argmax pairs)
-    if (M > s->max_m || p.G > s->max_groups)
+    if (M > (s->max_m >= 2 ? s->max_m : 0) || p.G > s->max_groups)
       return fail(W4A16_ESCRATCH, "scratch: sized for max_m = %d and in_f <= %d, got M = %d, in_f = %d", s->max_m,
                   s->max_groups * kGroup, M, w->in_f);
     uint8_t* dig = reinterpret_cast<uint8_t*>(s->xf) + pair_bytes(s->max_splits);
@@ -1338,7 +1475,9 @@ int launch_skinny(SkinnyParams& p, const LayerRef* w, const uint16_t* x, int M, 
     int tm = 1, cb = 8, nrows = 16;
     set_geometry(M, tm, cb, nrows);
     p.db_bytes = 128 * nrows;
-    W4_CUDA(cudaLaunchKernelEx(&cfg, k_digits, x, dig, M, p.K, p.G, p.db_bytes, tm, cb));
+    const unsigned* wait_block = p.comm_wait ? p.comm_local : nullptr;
+    W4_CUDA(cudaLaunchKernelEx(&cfg, k_digits, x, dig, M, p.K, p.G, p.db_bytes, tm, cb, wait_block, p.comm_n, p.status,
+                               p.ln_w, p.ln_eps, p.xn_out));
   }
   if (int rc = w->wbits == 4 ? launch_batch<4>(p, grid, st, di->smem_optin) : launch_batch<8>(p, grid, st, di->smem_optin))
     return rc;
@@ -1361,6 +1500,95 @@ int run_gemm(void* y, int y_is_f32, const W* w, const uint16_t* x, int M, w4a16_
   p.ldy = L.out_f;
   return launch_skinny(p, &L, x, M, s, static_cast<cudaStream_t>(stream));
 }
+// Validates a communicator and copies it into the launch parameters.
+int set_comm(SkinnyParams& p, const w4a16_comm_t* comm, int wait_prev, int signal) {
+  W4_REQUIRE(comm != nullptr, "null communicator");
+  if (comm->nranks < 1 || comm->nranks > 8 || comm->rank < 0 || comm->rank >= comm->nranks)
+    return fail(W4A16_ECOMM, "communicator: rank %d of %d (1..8 ranks)", comm->rank, comm->nranks);
+  for (int r = 0; r < comm->nranks; ++r) {
+    if (comm->blocks[r] == nullptr || (reinterpret_cast<uintptr_t>(comm->blocks[r]) & 15) != 0)
+      return fail(W4A16_ECOMM, "communicator: flag block of rank %d is null or misaligned", r);
+    p.comm_peers[r] = comm->blocks[r];
+  }
+  p.comm_local = comm->blocks[comm->rank];
+  p.comm_n = comm->nranks;
+  p.comm_rank = comm->rank;
+  p.comm_wait = wait_prev ? 1 : 0;
+  p.comm_signal = signal ? 1 : 0;
+  return W4A16_OK;
+}
+
+template <class W>
+int run_gather(uint16_t* const* y_peers, const w4a16_comm_t* comm, int wait_prev, int out_f_total, int row_begin,
+               const W* w_shard, const uint16_t* x, int M, w4a16_scratch_t* s, void* stream) {
+  W4_REQUIRE(y_peers != nullptr, "gemm_skinny_gather: null peer table");
+  SkinnyParams p = {};
+  if (int rc = set_comm(p, comm, wait_prev, 1)) return rc;
+  LayerRef L;
+  if (int rc = layer_of(L, w_shard)) return rc;
+  if (row_begin < 0 || row_begin % kRowGranule != 0 || row_begin + L.out_f > out_f_total)
+    return fail(W4A16_ECOMM, "gemm_skinny_gather: rows [%d,%d) outside [0,%d)", row_begin, row_begin + L.out_f,
+                out_f_total);
+  for (int r = 0; r < comm->nranks; ++r) W4_REQUIRE(y_peers[r] != nullptr, "gemm_skinny_gather: null peer %d", r);
+  p.y = y_peers[comm->rank];
+  p.ldy = out_f_total;
+  p.y_col0 = row_begin;
+  int q = 0;
+  for (int r = 0; r < comm->nranks; ++r)
+    if (r != comm->rank) p.y_peers[q++] = y_peers[r];
+  p.npeers = q;
+  return launch_skinny(p, &L, x, M, s, static_cast<cudaStream_t>(stream));
+}
+
+template <class W>
+int run_argmax_sharded(int32_t* ids, void* const* pairs_peers, const w4a16_comm_t* comm, int wait_prev, int row_offset,
+                       const W* w_shard, const uint16_t* x, int M, w4a16_scratch_t* s, void* stream) {
+  W4_REQUIRE(ids != nullptr && pairs_peers != nullptr, "lm_head_argmax_sharded: null ids or pair tables");
+  SkinnyParams p = {};
+  if (int rc = set_comm(p, comm, wait_prev, 1)) return rc;
+  LayerRef L;
+  if (int rc = layer_of(L, w_shard)) return rc;
+  for (int r = 0; r < comm->nranks; ++r) {
+    W4_REQUIRE(pairs_peers[r] != nullptr && (reinterpret_cast<uintptr_t>(pairs_peers[r]) & 7) == 0,
+               "lm_head_argmax_sharded: pair table of rank %d is null or misaligned", r);
+    p.pairs_peers[r] = pairs_peers[r];
+  }
+  p.ldy = L.out_f;
+  p.argmax = 1;
+  p.ids = ids;
+  p.row_offset = row_offset;
+  return launch_skinny(p, &L, x, M, s, static_cast<cudaStream_t>(stream));
+}
+
+// The fused forms of a linear layer's neighbours (all optional, combinable): RMSNorm in front, SwiGLU or the
+// residual add behind.
+struct Fusion {
+  const uint16_t* ln_w = nullptr;
+  float ln_eps = 0.f;
+  uint16_t* xn_out = nullptr;
+  int epilogue = kEpiNone;
+};
+template <class W>
+int run_fused(uint16_t* y, const W* w, const uint16_t* x, int M, const Fusion& f, w4a16_scratch_t* s, void* stream) {
+  W4_REQUIRE(y != nullptr, "fused linear: y is null");
+  LayerRef L;
+  if (int rc = layer_of(L, w)) return rc;
+  SkinnyParams p = {};
+  p.y = y;
+  p.ln_w = f.ln_w;
+  p.ln_eps = f.ln_eps;
+  p.xn_out = f.xn_out;
+  p.epilogue = f.epilogue;
+  if (f.ln_w) W4_REQUIRE((reinterpret_cast<uintptr_t>(f.ln_w) & 7) == 0, "fused linear: norm weights not 8-byte aligned");
+  if (f.epilogue == kEpiSwiglu) {
+    W4_REQUIRE(L.out_f % 32 == 0, "swiglu epilogue: out_f %d must be a multiple of 32 (gate, up interleaved)", L.out_f);
+    p.ldy = L.out_f / 2;
+  } else {
+    p.ldy = L.out_f;
+  }
+  return launch_skinny(p, &L, x, M, s, static_cast<cudaStream_t>(stream));
+}
+
 template <class W>
 int run_argmax(int32_t* ids, uint16_t* logits, void* pairs, int row_offset, const W* w, const uint16_t* x, int M,
                w4a16_scratch_t* s, void* stream) {
@@ -1563,6 +1791,54 @@ int w4a16_gemv_static_reset(void* stream) {
   if (int rc = static_scratch_base(&b, di->device, static_cast<cudaStream_t>(stream))) return rc;
   W4_CUDA(cudaMemsetAsync(b + kStaticPartialBytes, 0, kStaticCounterBytes, static_cast<cudaStream_t>(stream)));
   return W4A16_OK;
+}
+
+int w4a16_gemm_skinny_gather(uint16_t* const* y_peers, const w4a16_comm_t* comm, int wait_prev, int out_f_total,
+                             int row_begin, const w4a16_weights_t* w_shard, const uint16_t* x, int M, w4a16_scratch_t* s,
+                             void* stream) {
+  return run_gather(y_peers, comm, wait_prev, out_f_total, row_begin, w_shard, x, M, s, stream);
+}
+
+int w4a16_lm_head_argmax_sharded(int32_t* ids, void* const* pairs_peers, const w4a16_comm_t* comm, int wait_prev,
+                                 int row_offset, const w4a16_weights_t* w_shard, const uint16_t* x, int M,
+                                 w4a16_scratch_t* s, void* stream) {
+  return run_argmax_sharded(ids, pairs_peers, comm, wait_prev, row_offset, w_shard, x, M, s, stream);
+}
+
+int w4a16_w8_lm_head_argmax_sharded(int32_t* ids, void* const* pairs_peers, const w4a16_comm_t* comm, int wait_prev,
+                                    int row_offset, const w4a16_w8_weights_t* w_shard, const uint16_t* x, int M,
+                                    w4a16_scratch_t* s, void* stream) {
+  return run_argmax_sharded(ids, pairs_peers, comm, wait_prev, row_offset, w_shard, x, M, s, stream);
+}
+
+int w4a16_wait_gather(const w4a16_comm_t* comm, void* stream) {
+  SkinnyParams p = {};
+  if (int rc = set_comm(p, comm, 1, 0)) return rc;
+  const DeviceInfo* di = device_info();
+  if (!di) return W4A16_ECUDA;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1);
+  cfg.blockDim = dim3(32);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = config().pdl ? 1 : 0;
+  W4_CUDA(cudaLaunchKernelEx(&cfg, k_wait_gather, static_cast<const unsigned*>(p.comm_local), p.comm_n, di->status));
+  return W4A16_OK;
+}
+
+int w4a16_linear_fused(uint16_t* y, const w4a16_weights_t* w, const uint16_t* x, int M, const uint16_t* ln_weight,
+                       float ln_eps, uint16_t* xn_out, int epilogue, w4a16_scratch_t* s, void* stream) {
+  W4_REQUIRE(epilogue == W4A16_EPILOGUE_NONE || epilogue == W4A16_EPILOGUE_SWIGLU || epilogue == W4A16_EPILOGUE_RESIDUAL,
+             "linear_fused: unknown epilogue %d", epilogue);
+  Fusion f;
+  f.ln_w = ln_weight;
+  f.ln_eps = ln_eps;
+  f.xn_out = xn_out;
+  f.epilogue = epilogue;
+  return run_fused(y, w, x, M, f, s, stream);
 }
 
 int w4a16_shard_rows(int out_f, int nranks, int rank, int* row_begin, int* row_end) {

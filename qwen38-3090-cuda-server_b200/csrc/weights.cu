@@ -68,9 +68,15 @@ const DeviceInfo* device_info() {
 // ------------------------------------------------------------------ kernels
 namespace {
 
+// Physical row of logical row o: the identity, or - for a gate|up layer repacked for the fused SwiGLU epilogue
+// (inter > 0) - gate row o at 2 o and up row o - inter at 2 (o - inter) + 1.
+__device__ __forceinline__ int physical_row(int o, int inter) {
+  return inter <= 0 ? o : (o < inter ? 2 * o : 2 * (o - inter) + 1);
+}
+
 // One thread per destination uint4: (row, 32-k chunk).
 __global__ void k_repack_q(uint8_t* __restrict__ dst, const uint32_t* __restrict__ sq, int out_f,
-                           int words_per_row, int G, int row_offset) {
+                           int words_per_row, int G, int row_offset, int inter) {
   const int C = G * 4;  // 32-k chunks per row
   const long long n = static_cast<long long>(out_f) * C;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
@@ -87,20 +93,20 @@ __global__ void k_repack_q(uint8_t* __restrict__ dst, const uint32_t* __restrict
       for (int k = 0; k < 8; ++k) o |= ((in[w] >> (4 * k)) & 0xFu) << (4 * nib_pos(k));
       out[w] = o;
     }
-    const int o = so + row_offset;
+    const int o = physical_row(so + row_offset, inter);
     *reinterpret_cast<uint4*>(dst + tile_group_offset(o, c >> 2, G) + (c & 3) * kChunkBytes +
                               weight_slot(o % kTileRows, c & 3) * 16) = make_uint4(out[0], out[1], out[2], out[3]);
   }
 }
 
 __global__ void k_repack_sz(uint8_t* __restrict__ dst, const uint16_t* __restrict__ ss,
-                            const uint32_t* __restrict__ sz, int out_f, int G, int row_offset) {
+                            const uint32_t* __restrict__ sz, int out_f, int G, int row_offset, int inter) {
   const long long n = static_cast<long long>(out_f) * G;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const int g = static_cast<int>(i % G);
     const int so = static_cast<int>(i / G);
-    const int o = so + row_offset;
+    const int o = physical_row(so + row_offset, inter);
     uint8_t* blk = dst + tile_group_offset(o, g, G);
     const int r = o % kTileRows;
     reinterpret_cast<uint16_t*>(blk + kTgScaleOff)[r] = ss[static_cast<size_t>(so) * G + g];
@@ -252,8 +258,8 @@ int w4a16_weights_alloc(w4a16_weights_t* w, int out_f, int in_f, int group_size,
   return W4A16_OK;
 }
 
-int w4a16_repack_into(const w4a16_weights_t* w, int dst_row_offset, const uint32_t* packed,
-                      const uint16_t* scale, const uint32_t* zp, int out_f, void* stream) {
+static int repack_rows(const w4a16_weights_t* w, int dst_row_offset, const uint32_t* packed, const uint16_t* scale,
+                       const uint32_t* zp, int out_f, int inter, void* stream) {
   if (int rc = check_weights(w)) return rc;
   W4_REQUIRE(packed && scale && zp, "repack_into: null source tensor");
   W4_REQUIRE(out_f > 0 && out_f % kRowGranule == 0, "repack_into: out_f %d not a positive multiple of 16",
@@ -266,11 +272,23 @@ int w4a16_repack_into(const w4a16_weights_t* w, int dst_row_offset, const uint32
   uint8_t* stream_base = reinterpret_cast<uint8_t*>(w->qweight);
   const long long nq = static_cast<long long>(out_f) * (w->in_f / 32);
   k_repack_q<<<grid_for(nq, 256), 256, 0, st>>>(stream_base, packed, out_f, w->in_f / 8, w->num_groups,
-                                                dst_row_offset);
+                                                dst_row_offset, inter);
   const long long ns = static_cast<long long>(out_f) * w->num_groups;
-  k_repack_sz<<<grid_for(ns, 256), 256, 0, st>>>(stream_base, scale, zp, out_f, w->num_groups, dst_row_offset);
+  k_repack_sz<<<grid_for(ns, 256), 256, 0, st>>>(stream_base, scale, zp, out_f, w->num_groups, dst_row_offset, inter);
   W4_CUDA(cudaGetLastError());
   return W4A16_OK;
+}
+
+int w4a16_repack_into(const w4a16_weights_t* w, int dst_row_offset, const uint32_t* packed,
+                      const uint16_t* scale, const uint32_t* zp, int out_f, void* stream) {
+  return repack_rows(w, dst_row_offset, packed, scale, zp, out_f, 0, stream);
+}
+
+int w4a16_repack_into_swiglu(const w4a16_weights_t* w, int dst_row_offset, const uint32_t* packed,
+                             const uint16_t* scale, const uint32_t* zp, int out_f, int inter, void* stream) {
+  W4_REQUIRE(w != nullptr && inter > 0 && 2 * inter == w->out_f,
+             "repack_into_swiglu: inter = %d must be half of the container's rows", inter);
+  return repack_rows(w, dst_row_offset, packed, scale, zp, out_f, inter, stream);
 }
 
 int w4a16_weights_free(w4a16_weights_t* w) {

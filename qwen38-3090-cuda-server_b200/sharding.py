@@ -56,3 +56,32 @@ def reduce_pairs(values: np.ndarray, indices: np.ndarray) -> np.ndarray:
                 bv, bi = v, i
         out[m] = 0 if bi == np.iinfo(np.int32).max else bi
     return out
+
+
+class FlagBlock:
+    """Host model of one rank's completion-flag block (w4a16_comm_t): `flags[r]` is a counter written by rank r,
+    `seq` counts this rank's own signalling launches. The device kernels implement exactly this:
+      signal  (every CTA of a sharded launch, after its last store): its share of UNIT = 65536 is added to
+              flags[this rank] on every rank; the launch as a whole adds UNIT and bumps `seq` once
+      wait    (prologue of the consumer): passes once flags[r] - seq * UNIT >= 0 (as signed 32-bit) for every r
+    All ranks issue the same sequence of signalling launches, so a rank's own `seq` names the launch whose
+    slices it is waiting for; counters only grow, a peer that is already one launch ahead does not matter, and
+    a launch of which only some CTAs have arrived does not reach the target."""
+    UNIT = 1 << 16
+
+    def __init__(self, nranks: int):
+        self.flags = np.zeros(nranks, np.uint32)
+        self.seq = np.uint32(0)
+
+    def launch(self) -> int:
+        """This rank signals one launch: returns what the launch adds to its counter on every rank."""
+        self.seq = np.uint32((int(self.seq) + 1) & 0xFFFFFFFF)
+        return self.UNIT
+
+    def add(self, rank: int, amount: int):
+        self.flags[rank] = np.uint32((int(self.flags[rank]) + amount) & 0xFFFFFFFF)
+
+    def arrived(self) -> bool:
+        target = (int(self.seq) * self.UNIT) & 0xFFFFFFFF
+        d = (self.flags.astype(np.int64) - target) & 0xFFFFFFFF
+        return bool(np.all(d < 0x80000000))

@@ -3,7 +3,9 @@
 Checks, on real GPUs: (1) the skinny GEMM whose epilogue stores its column slice into every
 rank's output over NVLink peer mappings (the fused all-gather) against the unsharded kernel and the
 CPU oracle; (2) the vocab-sharded lm_head: per-rank (max, global index) pairs, 8*M-byte all-gather,
-pair reduction, against the unsharded fused argmax."""
+pair reduction, against the unsharded fused argmax; (3) the completion flags: two chained sharded
+layers with no host barrier between them; (4) the one-launch sharded lm_head with the pair exchange
+and reduction inside the kernel; (5) the column-sharded prefill GEMM."""
 import importlib
 import os
 import sys
@@ -79,6 +81,78 @@ def main():
     a, b = ids.cpu().numpy(), ids1.cpu().numpy()
     assert all(p == q or g == 0 for p, q, g in zip(a, want, gaps)), (a, want)
     assert all(p == q or g == 0 for p, q, g in zip(a, b, gaps)), (a, b)
+    assert pkg.device_status() == 0
+
+    # ---- completion flags: two chained sharded layers with no host barrier in between ----
+    blocks = symm_mem.empty(64, dtype=torch.int32, device=torch.device("cuda", local))
+    blocks.zero_()
+    bh = symm_mem.rendezvous(blocks, dist.group.WORLD)
+    comm = pkg.make_comm([int(p) for p in bh.buffer_ptrs], rank)
+    N2 = 2048
+    p2, s2, z2 = synth.make_weights(N2, N, seed=12)            # layer 2 consumes the gathered [M, N] of layer 1
+    sp2, ss2, sz2, row2 = sharding.shard_on_disk(p2, s2, z2, world, rank)
+    w2_shard = pkg.weights_from_numpy(sp2, ss2, sz2)
+    w2_full = pkg.weights_from_numpy(p2, s2, z2)
+    s_big = pkg.gemv_scratch_alloc(N, N, 128, 16)
+    ya = symm_mem.empty(M * N, dtype=torch.bfloat16, device=torch.device("cuda", local))
+    yb = symm_mem.empty(M * N2, dtype=torch.bfloat16, device=torch.device("cuda", local))
+    ya.zero_()
+    yb.zero_()
+    ha, hb = symm_mem.rendezvous(ya, dist.group.WORLD), symm_mem.rendezvous(yb, dist.group.WORLD)
+    xs = dev_bf16(synth.make_activations(M, K, seed=13, sigma=0.05))
+    torch.cuda.synchronize()
+    dist.barrier()
+    for rep in range(3):
+        pkg.gemm_skinny_gather([int(p) for p in ha.buffer_ptrs], comm, N, row0, w_shard, xs, M, s_big)
+        pkg.gemm_skinny_gather([int(p) for p in hb.buffer_ptrs], comm, N2, row2, w2_shard, ya.view(M, N), M, s_big,
+                               wait_prev=True)
+        pkg.wait_gather(comm)
+        torch.cuda.synchronize()
+        r1 = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+        r2 = torch.empty((M, N2), dtype=torch.bfloat16, device="cuda")
+        pkg.gemm_small_w4a16(r1, w_full, xs, M, s_big)
+        pkg.gemm_small_w4a16(r2, w2_full, r1, M, s_big)
+        torch.cuda.synchronize()
+        # sharded and unsharded runs split the K range differently across CTAs: equal up to fp32 summation order,
+        # i.e. at most one bf16 ulp per element
+        d1 = (ya.view(M, N).float() - r1.float()).abs().max().item()
+        d2 = (yb.view(M, N2).float() - r2.float()).abs().max().item()
+        assert d1 <= r1.float().abs().max().item() * 2.0 ** -7, (rep, d1)
+        assert d2 <= r2.float().abs().max().item() * 2.0 ** -6, (rep, d2)
+        dist.barrier()
+    assert pkg.device_status() == 0
+
+    # ---- vocab-sharded lm_head in one launch: pairs exchanged by peer stores + flag, reduced in the kernel ----
+    table = symm_mem.empty(world * 16 * 2, dtype=torch.int32, device=torch.device("cuda", local))
+    table.zero_()
+    ht = symm_mem.rendezvous(table, dist.group.WORLD)
+    torch.cuda.synchronize()
+    dist.barrier()
+    for Mh in (1, M):
+        ids_s = torch.full((Mh,), -1, dtype=torch.int32, device="cuda")
+        pkg.lm_head_argmax_sharded(ids_s, [int(p) for p in ht.buffer_ptrs], comm, row0, w_shard, dx[:Mh], Mh, s_big)
+        torch.cuda.synchronize()
+        got = ids_s.cpu().numpy()
+        assert all(p == q or g == 0 for p, q, g in zip(got, want[:Mh], gaps[:Mh])), (Mh, got, want[:Mh])
+        dist.barrier()
+    assert pkg.device_status() == 0
+
+    # ---- column-sharded prefill: tiles stored into every rank's C, then the flag ----
+    Mp = 300
+    ws = pkg.gemm_workspace_alloc(4096)
+    xp = dev_bf16(synth.make_activations(Mp, K, seed=14))
+    cp = symm_mem.empty(Mp * N, dtype=torch.bfloat16, device=torch.device("cuda", local))
+    cp.zero_()
+    hc = symm_mem.rendezvous(cp, dist.group.WORLD)
+    torch.cuda.synchronize()
+    dist.barrier()
+    pkg.gemm_w4a16_sharded([int(p) for p in hc.buffer_ptrs], comm, N, row0, w_shard, xp, Mp, ws)
+    pkg.wait_gather(comm)
+    torch.cuda.synchronize()
+    cfull = torch.empty((Mp, N), dtype=torch.bfloat16, device="cuda")
+    pkg.gemm_w4a16(cfull, w_full, xp, Mp, ws)
+    torch.cuda.synchronize()
+    assert torch.equal(cp.view(Mp, N).view(torch.int16), cfull.view(torch.int16)), "sharded prefill != unsharded"
     assert pkg.device_status() == 0
     dist.barrier()
     if rank == 0:

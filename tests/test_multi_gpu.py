@@ -1,4 +1,5 @@
-"""2-GPU parity of the sharded entry points (skipped on boxes with a single GPU)."""
+"""Parity of the sharded entry points on every world size the box offers (2, 4, 8 ranks; skipped on boxes
+with a single GPU)."""
 import os
 import socket
 import subprocess
@@ -10,15 +11,16 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def test_sharded_entry_points_on_two_gpus():
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_sharded_entry_points(world):
     import torch
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs at least 2 GPUs")
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs at least {world} GPUs")
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
     port = s.getsockname()[1]
     s.close()
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world),
            "--master-addr", "127.0.0.1", "--master-port", str(port),
            os.path.join(ROOT, "tests", "multi_gpu_worker.py")]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600)

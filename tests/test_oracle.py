@@ -169,6 +169,33 @@ def test_w8_gemm_f64_equals_numpy(oracle, synth):
     assert np.array_equal(ids, oracle.argmax_bf16(logits)) and np.all(gaps >= 0)
 
 
+def test_elementwise_neighbours_match_torch(oracle, synth):
+    """rmsnorm / residual_add / swiglu (src/kernels/elementwise.cu:8-49 of the reference) against torch fp32."""
+    torch = pytest.importorskip("torch")
+
+    def bits(t):
+        return t.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+
+    x = synth.make_activations(4, 5120, seed=21)
+    w = synth.make_activations(1, 5120, seed=22, sigma=0.1)[0]
+    xf, wf = torch.from_numpy(synth.bf16_bits_to_f32(x)), torch.from_numpy(synth.bf16_bits_to_f32(w))
+    want = bits(xf * torch.rsqrt((xf * xf).mean(1, keepdim=True) + 1e-6) * (1 + wf))
+    got = oracle.rmsnorm(x, w, 1e-6)
+    # the summation order differs from torch's: at most a unit in the last place of a few outputs
+    d = np.abs(got.astype(np.int32) - want.astype(np.int32))
+    assert d.max() <= 1 and (d != 0).mean() < 0.01
+    h = synth.make_activations(2, 256, seed=23)
+    y = synth.make_activations(2, 256, seed=24)
+    want = bits(torch.from_numpy(synth.bf16_bits_to_f32(h)) + torch.from_numpy(synth.bf16_bits_to_f32(y)))
+    assert np.array_equal(oracle.residual_add(h, y), want)
+    f = synth.make_activations(3, 2048, seed=25, sigma=2.0)
+    ff = torch.from_numpy(synth.bf16_bits_to_f32(f))
+    g, u = ff[:, :1024], ff[:, 1024:]
+    want = bits((g / (1 + torch.exp(-g))) * u)
+    d = np.abs(oracle.swiglu(f).astype(np.int32) - want.astype(np.int32))
+    assert d.max() <= 1 and (d != 0).mean() < 0.01
+
+
 def test_synthetic_config_totals(synth):
     shapes = synth.decode_pass_shapes()
     assert len(shapes) == 256

@@ -80,6 +80,67 @@ def test_two_rank_gather_and_pair_reduce():
     assert all(r[2] for r in res), "pair-reduced argmax ids differ from the unsharded result"
 
 
+def _flag_worker(rank, world, port, q):
+    """Each rank keeps a FlagBlock; 'peer stores' of the flag value travel as gloo all-gathers. Rank 1 leaves
+    after the second launch: rank 0's third wait must not pass (on the device it would run out and report)."""
+    import importlib
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+    sharding = importlib.import_module(PKG + ".sharding")
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        blk = sharding.FlagBlock(world)
+        blk.seq = sharding.np.uint32(0xFFFF)              # next launch wraps the 32-bit counters
+        blk.flags[:] = (0xFFFF << 16) & 0xFFFFFFFF
+        seen = []
+        for launch in range(2):
+            amount = blk.launch()                           # this rank's launch is done: its CTAs add their shares
+            vals = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
+            dist.all_gather(vals, torch.tensor([amount], dtype=torch.int64))
+            before = blk.arrived()                          # own seq moved on, the adds have not landed yet
+            blk.add(rank, amount - 1)                       # all but one CTA of the own launch: still not enough
+            partial = blk.arrived()
+            blk.add(rank, 1)
+            for r, t in enumerate(vals):
+                if r != rank:
+                    blk.add(r, int(t.item()))
+            seen.append((before or partial, blk.arrived()))
+        # third launch: only rank 0 takes part
+        stuck = None
+        if rank == 0:
+            blk.add(0, blk.launch())
+            stuck = not blk.arrived()
+        q.put((rank, seen, stuck))
+    except Exception as e:
+        q.put((rank, repr(e), None))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+def test_flag_protocol_two_ranks():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_flag_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted([q.get(timeout=180) for _ in procs], key=lambda r: r[0])
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, seen, stuck in res:
+        assert isinstance(seen, list), seen
+        # before the peers' values land the wait does not pass; after, it does - across the 32-bit wrap too
+        assert seen == [(False, True), (False, True)], (rank, seen)
+    assert res[0][2] is True      # a rank that never signals keeps the others' wait from passing
+    assert res[1][2] is None
+
+
 def test_shard_planner_matches_c_abi(pkg):
     import importlib
     sharding = importlib.import_module(PKG + ".sharding")
