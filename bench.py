@@ -319,6 +319,32 @@ def sharded_configs(pkg, synth, torch, dist, symm_mem, comm, rank, world, local,
         del y_gu, y_dn
     out["config2_sharded_mlp_gate_up_down"] = verify
 
+    # ---- the same MLP without the gather: row-sharded gate|up with the SwiGLU epilogue (local), K-sharded down,
+    #      fp32 partials of [M, 5120] into every rank's buffer, reduced in rank order (one exchange per MLP) ----
+    dk = [make_layer_weights(pkg, torch, gen, H, I // world, 6500 + 10 * c + rank) for c in range(copies)]
+    free_mlp = {}
+    for M in (1, 9, 16):
+        x0 = torch.randn((M, H), device="cuda").to(torch.bfloat16)
+        act = torch.empty((M, I // world), dtype=torch.bfloat16, device="cuda")
+        hres = torch.zeros((M, H), dtype=torch.bfloat16, device="cuda")
+        pbuf, p_pbuf = sym(world * M * H, torch.float32)
+        torch.cuda.synchronize()
+        dist.barrier()
+
+        def mlp2(i):
+            w, _ = gu[i % copies]
+            pkg.linear_fused(act, w, x0, M, scratch, epilogue=pkg.EPILOGUE_SWIGLU, stream=stream)
+            pkg.gemm_skinny_partial(p_pbuf, comm, dk[i % copies], act, M, scratch, stream=stream)
+            pkg.reduce_partials(hres, pbuf, comm, M, H, residual=True, stream=stream)
+
+        us = timed(mlp2, 4 * copies)
+        alg = synth.algorithmic_bytes(2 * I, H, M, out_bytes=2 * M * I) + synth.algorithmic_bytes(H, I, M)
+        free_mlp[f"M{M}"] = {"us_per_mlp": round(us, 2), "aggregate_tbps": round(alg / us / 1e6, 3)}
+        del pbuf
+    out["config2_sharded_mlp_gather_free"] = free_mlp
+    for w in dk:
+        pkg.awq_free(w)
+
     # ---- config 3: vocab-sharded lm_head, one launch per call (ring of weight copies larger than L2) ----
     V = 248320
     b, e = pkg.shard_rows(V, world, rank)

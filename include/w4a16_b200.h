@@ -247,6 +247,22 @@ typedef struct w4a16_comm {
 int w4a16_gemm_skinny_gather(uint16_t* const* y_peers, const w4a16_comm_t* comm, int wait_prev,
                              int out_f_total, int row_begin, const w4a16_weights_t* w_shard,
                              const uint16_t* x, int M, w4a16_scratch_t* s, void* stream);
+/* The gather-free sharded MLP (no reference counterpart; the single-GPU chain it replaces is
+ * src/model/model.cu:779-785): gate|up stays ROW-sharded and runs with the SwiGLU epilogue on the shard
+ * (w4a16_linear_fused, no exchange at all), its [M][inter / nranks] output is exactly the input slice of the
+ * K-sharded down projection, and only the [M][hidden] partial sums cross the link:
+ *   w4a16_gemm_skinny_partial  this rank's fp32 partial of Y = X W^T over its K range (w_kshard: all out_f rows,
+ *                              in_f = the shard's share of K) is stored into slot `rank` of EVERY rank's buffer
+ *                              (partial_peers[r]: rank r's buffer of nranks x M x out_f floats, peer-mapped), then
+ *                              the completion flag is raised;
+ *   w4a16_reduce_partials      waits (bounded) for every rank's flag, adds the nranks slots of the local buffer in
+ *                              rank order (the same bits on every rank), rounds to bf16 once and writes y [M][out_f],
+ *                              or, with residual != 0, adds it to y in place as residual_add does. */
+int w4a16_gemm_skinny_partial(float* const* partial_peers, const w4a16_comm_t* comm,
+                              const w4a16_weights_t* w_kshard, const uint16_t* x_slice, int M,
+                              w4a16_scratch_t* s, void* stream);
+int w4a16_reduce_partials(uint16_t* y, const float* partials_local, const w4a16_comm_t* comm, int M,
+                          int out_f, int residual, void* stream);
 /* For consumers that are not kernels of this library: one tiny kernel on `stream` that returns once every
  * rank has signalled the last launch of this communicator (bounded; W4A16_ETIMEOUT in the status word
  * when the wait runs out). */

@@ -108,6 +108,9 @@ _SIGNATURES = {
                                      C.POINTER(Workspace), C.c_void_p]),
     "w4a16_gemm_skinny_gather": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(Comm), C.c_int, C.c_int, C.c_int,
                                            C.POINTER(Weights), C.c_void_p, C.c_int, C.POINTER(Scratch), C.c_void_p]),
+    "w4a16_gemm_skinny_partial": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(Comm), C.POINTER(Weights), C.c_void_p,
+                                            C.c_int, C.POINTER(Scratch), C.c_void_p]),
+    "w4a16_reduce_partials": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(Comm), C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "w4a16_wait_gather": (C.c_int, [C.POINTER(Comm), C.c_void_p]),
     "w4a16_lm_head_argmax_sharded": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(Comm), C.c_int, C.c_int,
                                                C.POINTER(Weights), C.c_void_p, C.c_int, C.POINTER(Scratch), C.c_void_p]),
@@ -298,6 +301,18 @@ def gemm_skinny_gather(y_peer_ptrs, comm: Comm, out_f_total: int, row_begin: int
     output of the previous launch on this communicator."""
     check(lib().w4a16_gemm_skinny_gather(_ptr_table(y_peer_ptrs), C.byref(comm), 1 if wait_prev else 0, out_f_total,
                                          row_begin, C.byref(w), _ptr(x), M, C.byref(s), _stream(stream)))
+
+
+def gemm_skinny_partial(partial_peer_ptrs, comm: Comm, w_kshard: Weights, x_slice, M: int, s: Scratch, stream=None):
+    """K-sharded layer: this rank's fp32 partial goes into slot `rank` of every rank's buffer, then the flag."""
+    check(lib().w4a16_gemm_skinny_partial(_ptr_table(partial_peer_ptrs), C.byref(comm), C.byref(w_kshard), _ptr(x_slice),
+                                          M, C.byref(s), _stream(stream)))
+
+
+def reduce_partials(y, partials_local, comm: Comm, M: int, out_f: int, residual: bool = False, stream=None):
+    """Waits for every rank's partial, adds them in rank order, writes (or adds to) the bf16 y [M, out_f]."""
+    check(lib().w4a16_reduce_partials(_ptr(y), _ptr(partials_local), C.byref(comm), M, out_f, 1 if residual else 0,
+                                      _stream(stream)))
 
 
 def wait_gather(comm: Comm, stream=None):

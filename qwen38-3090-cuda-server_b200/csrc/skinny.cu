@@ -104,6 +104,11 @@ struct Geo {
   static constexpr int kDColsS = kStepGroups * N;        // D columns per step
   static constexpr int kDCol0 = AD2 * kAColsS;           // first D column
   static constexpr int GB = 4;                           // M = 1: groups whose tensor-memory loads are in flight together
+  // Who waits for "the D slot this step fills has been read out". With a deep D ring (8 steps) the unpack warps
+  // do, long before it matters, and the issuers - the busiest threads at M = 1 - are spared the wait; with a
+  // shallow one (4 steps) the wait is on the critical loop and belongs to the issuer, so that the operand is
+  // already unpacked when the slot comes free.
+  static constexpr bool kIssuerWaitsD = DD2 < 8;
   static_assert(3 * TM <= CB && FW * CB <= N, "token sets must fit their column blocks");
   static_assert(kDCol0 + DD2 * kDColsS <= kTmemCols, "tensor memory budget");
   static_assert(AD2 <= DD2 && 2 <= DD2 / 2, "ring depths");
@@ -590,7 +595,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
         // A written (its writers also saw the step's weights and table entry landed), and the D slot this
         // step fills has been read out by every fix-up warp
         if (!wait_h(afull_a + a * 8, static_cast<uint32_t>(t / AD2) & 1u, p.hint, kSpinLimit) ||
-            (t >= DD2 && !wait_h(dempty_a + d * 8, static_cast<uint32_t>(t / DD2 - 1) & 1u, p.hint, kSpinLimit))) {
+            (GE::kIssuerWaitsD && t >= DD2 &&
+             !wait_h(dempty_a + d * 8, static_cast<uint32_t>(t / DD2 - 1) & 1u, p.hint, kSpinLimit))) {
           atomicExch(p.status, W4A16_ETIMEOUT);
           break;
         }
@@ -673,8 +679,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
       load_row(base);
       // the A slot's previous step has been multiplied (whether the D slot is free is the issuer's concern: the
       // operand can be unpacked while the fix-up warps are still reading the sums of DD2 steps ago)
-      if (t >= AD2 && !wait_h(done_a + ((t - AD2) & (DD2 - 1)) * 8, static_cast<uint32_t>((t - AD2) / DD2) & 1u, p.hint,
-                              kSpinLimit)) {
+      if ((t >= AD2 && !wait_h(done_a + ((t - AD2) & (DD2 - 1)) * 8, static_cast<uint32_t>((t - AD2) / DD2) & 1u, p.hint,
+                               kSpinLimit)) ||
+          (!GE::kIssuerWaitsD && t >= DD2 &&
+           !wait_h(dempty_a + (t & (DD2 - 1)) * 8, static_cast<uint32_t>(t / DD2 - 1) & 1u, p.hint, kSpinLimit))) {
         atomicExch(p.status, W4A16_ETIMEOUT);
         break;
       }
@@ -1207,6 +1215,25 @@ __global__ void __launch_bounds__(128, 16) k_digits(const uint16_t* __restrict__
   convert_group(rv, dig + static_cast<size_t>(g) * db_bytes, db_bytes >> 3, cb * f + 3 * (m - f * tm), pairs + g * M + m, lane);
 }
 
+// Cross-rank reduction of a K-sharded layer: every rank's fp32 partial [M][N] sits in slot r of this rank's buffer
+// (stored there by the producers' epilogues over NVLink); once every rank's flag is up, the slots are added in
+// rank order - the same order on every rank, so all ranks get the same bits - and rounded to bf16 once; with
+// `residual` the result is added to the running hidden state in place, as residual_add does.
+__global__ void k_reduce_partials(uint16_t* __restrict__ y, const float* __restrict__ partials, int nranks, long long n,
+                                  int residual, const unsigned* comm_local, int* status) {
+  pdl_wait();
+  if (threadIdx.x == 0 &&
+      !wait_flags(comm_local, nranks, *reinterpret_cast<const volatile unsigned*>(comm_local + kCommSeq), kFlagSpinLimit))
+    atomicExch(status, W4A16_ETIMEOUT);
+  __syncthreads();
+  const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (i >= n) return;
+  float acc = 0.f;
+  for (int r = 0; r < nranks; ++r) acc += __ldcg(partials + r * n + i);
+  const uint16_t hb = float_to_bf16_bits(acc);
+  y[i] = residual ? float_to_bf16_bits(bf16_bits_to_float(y[i]) + bf16_bits_to_float(hb)) : hb;
+}
+
 // Stand-alone wait for consumers that are not kernels of this library: returns once every rank has
 // signalled the last gather (or sets W4A16_ETIMEOUT when the bounded wait runs out).
 __global__ void k_wait_gather(const unsigned* comm_local, int n, int* status) {
@@ -1237,7 +1264,7 @@ struct Config {
 
 const Config& config() {
   static Config c = [] {
-    Config k{8, 1, 2000, 0};
+    Config k{6, 1, 2000, 0};
     if (const char* e = getenv("W4A16_GEMV_PREPASS")) k.gemv_prepass = atoi(e) != 0;
     if (const char* e = getenv("W4A16_DEPTH")) k.depth = atoi(e);
     if (const char* e = getenv("W4A16_PDL")) k.pdl = atoi(e) != 0;
@@ -1809,6 +1836,50 @@ int w4a16_w8_lm_head_argmax_sharded(int32_t* ids, void* const* pairs_peers, cons
                                     int row_offset, const w4a16_w8_weights_t* w_shard, const uint16_t* x, int M,
                                     w4a16_scratch_t* s, void* stream) {
   return run_argmax_sharded(ids, pairs_peers, comm, wait_prev, row_offset, w_shard, x, M, s, stream);
+}
+
+int w4a16_gemm_skinny_partial(float* const* partial_peers, const w4a16_comm_t* comm, const w4a16_weights_t* w_kshard,
+                              const uint16_t* x_slice, int M, w4a16_scratch_t* s, void* stream) {
+  W4_REQUIRE(partial_peers != nullptr, "gemm_skinny_partial: null buffer table");
+  SkinnyParams p = {};
+  if (int rc = set_comm(p, comm, 0, 1)) return rc;
+  LayerRef L;
+  if (int rc = layer_of(L, w_kshard)) return rc;
+  W4_REQUIRE(M >= 1 && M <= 16, "gemm_skinny_partial: M = %d outside [1,16]", M);
+  const size_t slot = static_cast<size_t>(comm->rank) * M * L.out_f;  // this rank's slot in every rank's buffer
+  int q = 0;
+  for (int r = 0; r < comm->nranks; ++r) {
+    W4_REQUIRE(partial_peers[r] != nullptr, "gemm_skinny_partial: null buffer of rank %d", r);
+    if (r == comm->rank) p.y = partial_peers[r] + slot;
+    else p.y_peers[q++] = partial_peers[r] + slot;
+  }
+  p.npeers = q;
+  p.y_f32 = 1;
+  p.ldy = L.out_f;
+  return launch_skinny(p, &L, x_slice, M, s, static_cast<cudaStream_t>(stream));
+}
+
+int w4a16_reduce_partials(uint16_t* y, const float* partials_local, const w4a16_comm_t* comm, int M, int out_f,
+                          int residual, void* stream) {
+  W4_REQUIRE(y != nullptr && partials_local != nullptr, "reduce_partials: null pointer");
+  W4_REQUIRE(M >= 1 && out_f >= 1, "reduce_partials: M = %d, out_f = %d", M, out_f);
+  SkinnyParams p = {};
+  if (int rc = set_comm(p, comm, 1, 0)) return rc;
+  const DeviceInfo* di = device_info();
+  if (!di) return W4A16_ECUDA;
+  const long long n = static_cast<long long>(M) * out_f;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>((n + 255) / 256));
+  cfg.blockDim = dim3(256);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = config().pdl ? 1 : 0;
+  W4_CUDA(cudaLaunchKernelEx(&cfg, k_reduce_partials, y, partials_local, comm->nranks, n, residual ? 1 : 0,
+                             static_cast<const unsigned*>(p.comm_local), di->status));
+  return W4A16_OK;
 }
 
 int w4a16_wait_gather(const w4a16_comm_t* comm, void* stream) {

@@ -37,6 +37,18 @@ def shard_fused_gate_up(gate, up, nranks: int, rank: int):
     return g, u
 
 
+def shard_k_on_disk(packed, scale, zp, nranks: int, rank: int):
+    """Slice the on-disk tensors along K (whole groups of 128) for a K-sharded layer: every output row, this
+    rank's share of the input features. Returns (packed, scale, zp, k_begin)."""
+    K = packed.shape[1] * 8
+    if K % (128 * nranks) != 0:
+        raise ValueError(f"in_f {K} does not split into {nranks} shards of whole 128-k groups")
+    per = K // nranks
+    k0, k1 = rank * per, (rank + 1) * per
+    return (np.ascontiguousarray(packed[:, k0 // 8:k1 // 8]), np.ascontiguousarray(scale[:, k0 // 128:k1 // 128]),
+            np.ascontiguousarray(zp[:, k0 // 128:k1 // 128]), k0)
+
+
 def place_slice(y_full: np.ndarray, y_slice: np.ndarray, row_begin: int):
     """What the fused epilogue / the all-gather does: slice -> columns [row_begin, row_begin + n)."""
     y_full[:, row_begin:row_begin + y_slice.shape[1]] = y_slice

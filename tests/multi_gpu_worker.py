@@ -137,6 +137,50 @@ def main():
         dist.barrier()
     assert pkg.device_status() == 0
 
+    # ---- gather-free MLP: row-sharded gate|up + SwiGLU (local), K-sharded down, partials reduced in rank order ----
+    Hm, Im, Mm = 1024, 2048, 8
+    gate, up = synth.make_weights(Im, Hm, seed=21), synth.make_weights(Im, Hm, seed=22)
+    down = synth.make_weights(Hm, Im, seed=23)
+
+    def dev(a, dt=np.int32):
+        return torch.from_numpy(np.ascontiguousarray(a).view(dt)).cuda()
+
+    def swiglu_container(g, u, inter):
+        wq = pkg.awq_alloc_fused(2 * inter, Hm)
+        for off, (pk, sc, zz) in ((0, g), (inter, u)):
+            pkg.awq_repack_into_swiglu(wq, off, dev(pk), dev(sc, np.int16), dev(zz), inter)
+        return wq
+
+    xm = dev_bf16(synth.make_activations(Mm, Hm, seed=24, sigma=0.5))
+    h0 = synth.make_activations(Mm, Hm, seed=25)
+    sm = pkg.gemv_scratch_alloc(Im, 2 * Im, 128, 16)
+    full_gu, full_dn = swiglu_container(gate, up, Im), pkg.weights_from_numpy(*down)
+    act = torch.empty((Mm, Im), dtype=torch.bfloat16, device="cuda")
+    pkg.linear_fused(act, full_gu, xm, Mm, sm, epilogue=pkg.EPILOGUE_SWIGLU)
+    h_ref = dev_bf16(h0).clone()
+    pkg.linear_fused(h_ref, full_dn, act, Mm, sm, epilogue=pkg.EPILOGUE_RESIDUAL)
+    w_gu = swiglu_container(sharding.shard_on_disk(*gate, world, rank)[:3], sharding.shard_on_disk(*up, world, rank)[:3],
+                            Im // world)
+    w_dn = pkg.weights_from_numpy(*sharding.shard_k_on_disk(*down, world, rank)[:3])
+    pbuf = symm_mem.empty(world * Mm * Hm, dtype=torch.float32, device=torch.device("cuda", local))
+    pbuf.zero_()
+    hp = symm_mem.rendezvous(pbuf, dist.group.WORLD)
+    torch.cuda.synchronize()
+    dist.barrier()
+    for rep in range(2):
+        h_r = dev_bf16(h0).clone()
+        act_r = torch.empty((Mm, Im // world), dtype=torch.bfloat16, device="cuda")
+        pkg.linear_fused(act_r, w_gu, xm, Mm, sm, epilogue=pkg.EPILOGUE_SWIGLU)
+        pkg.gemm_skinny_partial([int(p) for p in hp.buffer_ptrs], comm, w_dn, act_r, Mm, sm)
+        pkg.reduce_partials(h_r, pbuf, comm, Mm, Hm, residual=True)
+        torch.cuda.synchronize()
+        assert rel_err(h_r.float().cpu().numpy().astype(np.float64), h_ref.float().cpu().numpy().astype(np.float64)) <= 1e-2
+        allh = [torch.empty_like(h_r) for _ in range(world)]
+        dist.all_gather(allh, h_r)
+        assert all(torch.equal(a.view(torch.int16), allh[0].view(torch.int16)) for a in allh), "ranks disagree"
+        dist.barrier()
+    assert pkg.device_status() == 0
+
     # ---- column-sharded prefill: tiles stored into every rank's C, then the flag ----
     Mp = 300
     ws = pkg.gemm_workspace_alloc(4096)

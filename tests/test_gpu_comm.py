@@ -194,3 +194,62 @@ def test_sharded_prefill_two_emulated_ranks(pkg, synth, sharding):
     pkg.awq_free(full)
     for w, _ in parts:
         pkg.awq_free(w)
+
+
+@pytest.mark.parametrize("M", [1, 8])
+def test_gather_free_mlp_two_emulated_ranks(pkg, oracle, synth, sharding, M):
+    """gate|up row-sharded with the SwiGLU epilogue (no exchange) -> K-sharded down -> fp32 partials into every
+    rank's buffer -> reduce in rank order + residual add; against the unsharded fused chain."""
+    from gpu_util import rel_err
+    H, I, R = 1024, 2048, 2
+    gate, up = synth.make_weights(I, H, seed=101), synth.make_weights(I, H, seed=102)
+    down = synth.make_weights(H, I, seed=103)
+    h0 = synth.make_activations(M, H, seed=104)
+    x = dev_bf16(synth.make_activations(M, H, seed=105, sigma=0.5))
+    s = pkg.gemv_scratch_alloc(I, 2 * I, 128, 16)
+
+    def dev(a, dt=np.int32):
+        return torch.from_numpy(np.ascontiguousarray(a).view(dt)).cuda()
+
+    def swiglu_container(g, u, inter):
+        w = pkg.awq_alloc_fused(2 * inter, H)
+        for off, (pk, sc, zp) in ((0, g), (inter, u)):
+            pkg.awq_repack_into_swiglu(w, off, dev(pk), dev(sc, np.int16), dev(zp), inter)
+        return w
+
+    # one GPU, fused: two launches
+    full = swiglu_container(gate, up, I)
+    wd = pkg.weights_from_numpy(*down)
+    act = torch.empty((M, I), dtype=torch.bfloat16, device="cuda")
+    pkg.linear_fused(act, full, x, M, s, epilogue=pkg.EPILOGUE_SWIGLU)
+    want = dev_bf16(h0).clone()
+    pkg.linear_fused(want, wd, act, M, s, epilogue=pkg.EPILOGUE_RESIDUAL)
+    # two emulated ranks
+    flags, ptrs = _blocks(R)
+    bufs = [torch.zeros((R, M, H), dtype=torch.float32, device="cuda") for _ in range(R)]
+    hs = [dev_bf16(h0).clone() for _ in range(R)]
+    torch.cuda.synchronize()
+    comms = [pkg.make_comm(ptrs, r) for r in range(R)]
+    keep = []
+    for r in range(R):
+        gs = sharding.shard_on_disk(*gate, R, r)[:3]
+        us = sharding.shard_on_disk(*up, R, r)[:3]
+        w_r = swiglu_container(gs, us, I // R)
+        wd_r = pkg.weights_from_numpy(*sharding.shard_k_on_disk(*down, R, r)[:3])
+        act_r = torch.empty((M, I // R), dtype=torch.bfloat16, device="cuda")
+        pkg.linear_fused(act_r, w_r, x, M, s, epilogue=pkg.EPILOGUE_SWIGLU)
+        pkg.gemm_skinny_partial([b.data_ptr() for b in bufs], comms[r], wd_r, act_r, M, s)
+        keep += [w_r, wd_r, act_r]
+    for r in range(R):
+        pkg.reduce_partials(hs[r], bufs[r], comms[r], M, H, residual=True)
+    torch.cuda.synchronize()
+    assert pkg.device_status() == 0
+    assert torch.equal(hs[0].view(torch.int16), hs[1].view(torch.int16)), "the ranks disagree"
+    got = hs[0].float().cpu().numpy().astype(np.float64)
+    ref = want.float().cpu().numpy().astype(np.float64)
+    assert rel_err(got, ref) <= 1e-2
+    d = np.abs(host_bits(hs[0]).astype(np.int32) - host_bits(want).astype(np.int32))
+    assert (d > 2).mean() < 0.01    # the same arithmetic up to the order of fp32 sums
+    pkg.gemv_scratch_free(s)
+    for w in (full, wd) + tuple(k for k in keep if hasattr(k, "qweight")):
+        pkg.awq_free(w)
