@@ -229,12 +229,16 @@ __device__ __forceinline__ uint32_t sub_bf16x2(uint32_t a, uint32_t b) {
   return d;
 }
 
-// ---- cross-rank flags: system-scope release adds into the peers' flag words, bounded polling with acquire ----
+// ---- cross-rank flags: one system-scope fence per CTA, relaxed adds into the peers' flag words, bounded polling ----
 // A rank's block: words [0, 8) are counters written by the ranks (word r by rank r), word 16 is this rank's own
 // count of signalling launches. Every signalling launch adds exactly kCommUnit to this rank's counter on every
-// rank - each CTA its share, right after its own last store, with release semantics - so "every rank's slice of
-// launch number s has landed" reads: counter[r] >= s * kCommUnit for every r. No CTA waits for another one, and
-// no second fence is needed: a CTA's release covers the stores its threads made before the CTA barrier.
+// rank - each CTA its share, right after its own last store - so "every rank's slice of launch number s has
+// landed" reads: counter[r] >= s * kCommUnit for every r. No CTA waits for another one.
+// Release side: the CTA's stores, the CTA barrier, then ONE thread issues one fence.acq_rel.sys (cumulative over
+// the stores it observed through the barrier) and the adds without waiting for any of them; a release per add
+// would put one NVLink round trip per peer in series. Acquire side: the lanes of one warp poll one counter each
+// with acquire loads (a fence after relaxed polls measured slower); the warp's vote and the barrier the caller
+// releases the CTA with carry the order on to the other threads.
 constexpr int kCommSeq = 16;                   // word of a rank's block
 constexpr unsigned kCommUnit = 1u << 16;       // what one launch adds in total (more than any grid has CTAs)
 constexpr uint32_t kFlagSpinLimit = 1u << 20;  // polls (each a system-scope load and a short sleep): about a second
@@ -243,32 +247,48 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void red_add_release_sys(unsigned* p, unsigned v) {
-  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void red_add_relaxed_sys(unsigned* p, unsigned v) {
+  asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-// Waits until every rank's counter in this rank's block has reached launch number `seq`; false if the limit ran out.
-__device__ __forceinline__ bool wait_flags(const unsigned* local, int n, unsigned seq, uint32_t limit) {
+__device__ __forceinline__ void fence_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+// Waits until every rank's counter in this rank's block has reached launch number `seq`; false if the limit ran
+// out. Called by the lanes of `mask` (converged, all of one warp) with the same arguments: lane number i of the
+// mask polls counters i, i + |mask|, ...; the answer is the same on every lane.
+__device__ __forceinline__ bool wait_flags(const unsigned* local, int n, unsigned seq, uint32_t limit,
+                                           unsigned mask = 0xffffffffu) {
   const unsigned target = seq * kCommUnit;
-  for (int r = 0; r < n; ++r) {
+  const int lanes = __popc(mask), me = __popc(mask & ((1u << (threadIdx.x & 31)) - 1u));
+  bool ok = true;
+  for (int r = me; r < n && ok; r += lanes) {
     uint32_t spins = 0;
     while (static_cast<int>(ld_acquire_sys(local + r) - target) < 0) {
-      if (++spins > limit) return false;
-      __nanosleep(64);
+      if (++spins > limit) {
+        ok = false;
+        break;
+      }
+      __nanosleep(32);
     }
   }
-  return true;
+  return __all_sync(mask, ok);
+}
+// This rank's own count of signalling launches so far (the launch number the counters are compared with).
+__device__ __forceinline__ unsigned comm_seq(const unsigned* local) {
+  return *reinterpret_cast<const volatile unsigned*>(local + kCommSeq);
 }
 // Called by ONE thread of every CTA after the CTA-wide barrier that follows its last store: this CTA's share of
 // the launch's signal goes to every rank (the local block included); CTA 0 also counts the launch.
 __device__ __forceinline__ void signal_cta_done(unsigned* local, unsigned* const* peers, int n, int rank) {
   const unsigned share = blockIdx.x == 0 ? kCommUnit - (gridDim.x - 1) : 1u;
-  for (int r = 0; r < n; ++r) red_add_release_sys(peers[r] + rank, share);
+  fence_sys();
+  for (int r = 0; r < n; ++r) red_add_relaxed_sys(peers[r] + rank, share);
   if (blockIdx.x == 0) atomicAdd(local + kCommSeq, 1u);
 }
-// The same for a launch whose exchange is done by a single thread of the grid (the vocab-sharded lm_head).
+// The same for a launch whose exchange is done by a single thread of the grid (the vocab-sharded lm_head); the
+// caller has fenced after the stores the signal covers.
 __device__ __forceinline__ unsigned signal_whole_launch(unsigned* local, unsigned* const* peers, int n, int rank) {
   const unsigned seq = atomicAdd(local + kCommSeq, 1u) + 1u;
-  for (int r = 0; r < n; ++r) red_add_release_sys(peers[r] + rank, kCommUnit);
+  fence_sys();
+  for (int r = 0; r < n; ++r) red_add_relaxed_sys(peers[r] + rank, kCommUnit);
   return seq;
 }
 

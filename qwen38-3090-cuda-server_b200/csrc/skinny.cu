@@ -474,10 +474,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
       // the flags (thousands of pollers on one line would stand in the way of the very store they wait
       // for); the other converting warps park on a barrier of the CTA.
       if (warp == kWConv0) {
+        const bool seen = wait_flags(p.comm_local, p.comm_n, comm_seq(p.comm_local), kFlagSpinLimit);
         if (lane == 0) {
-          if (!wait_flags(p.comm_local, p.comm_n, *reinterpret_cast<volatile unsigned*>(p.comm_local + kCommSeq),
-                          kFlagSpinLimit))
-            atomicExch(p.status, W4A16_ETIMEOUT);
+          if (!seen) atomicExch(p.status, W4A16_ETIMEOUT);
           mbar_arrive(commrdy_a);
         }
         __syncwarp();
@@ -1130,7 +1129,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
           unsigned seq = 0;
           if (tid == 0) seq = signal_whole_launch(p.comm_local, p.comm_peers, p.comm_n, p.comm_rank);
           seq = __shfl_sync(mask, seq, 0);
-          if (!wait_flags(p.comm_local, p.comm_n, seq, kFlagSpinLimit)) atomicExch(p.status, W4A16_ETIMEOUT);
+          if (!wait_flags(p.comm_local, p.comm_n, seq, kFlagSpinLimit, mask)) atomicExch(p.status, W4A16_ETIMEOUT);
           const Pair* tab = static_cast<const Pair*>(p.pairs_peers[p.comm_rank]);
           Pair w{-FLT_MAX, INT_MAX};
           for (int r = 0; r < p.comm_n; ++r) {
@@ -1176,8 +1175,7 @@ __global__ void __launch_bounds__(128, 16) k_digits(const uint16_t* __restrict__
   pdl_wait();  // the previous kernel produced x (and the main kernel before it may still be reading `dig`)
   if (comm_local) {
     // x is a gathered output: every rank's slice of it must have landed here
-    if (threadIdx.x == 0 &&
-        !wait_flags(comm_local, comm_n, *reinterpret_cast<const volatile unsigned*>(comm_local + kCommSeq), kFlagSpinLimit))
+    if (threadIdx.x < 32 && !wait_flags(comm_local, comm_n, comm_seq(comm_local), kFlagSpinLimit))
       atomicExch(status, W4A16_ETIMEOUT);
     __syncthreads();
   }
@@ -1222,8 +1220,7 @@ __global__ void __launch_bounds__(128, 16) k_digits(const uint16_t* __restrict__
 __global__ void k_reduce_partials(uint16_t* __restrict__ y, const float* __restrict__ partials, int nranks, long long n,
                                   int residual, const unsigned* comm_local, int* status) {
   pdl_wait();
-  if (threadIdx.x == 0 &&
-      !wait_flags(comm_local, nranks, *reinterpret_cast<const volatile unsigned*>(comm_local + kCommSeq), kFlagSpinLimit))
+  if (threadIdx.x < 32 && !wait_flags(comm_local, nranks, comm_seq(comm_local), kFlagSpinLimit))
     atomicExch(status, W4A16_ETIMEOUT);
   __syncthreads();
   const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
@@ -1238,8 +1235,7 @@ __global__ void k_reduce_partials(uint16_t* __restrict__ y, const float* __restr
 // signalled the last gather (or sets W4A16_ETIMEOUT when the bounded wait runs out).
 __global__ void k_wait_gather(const unsigned* comm_local, int n, int* status) {
   pdl_wait();
-  if (threadIdx.x == 0 &&
-      !wait_flags(comm_local, n, *reinterpret_cast<const volatile unsigned*>(comm_local + kCommSeq), kFlagSpinLimit))
+  if (threadIdx.x < 32 && !wait_flags(comm_local, n, comm_seq(comm_local), kFlagSpinLimit))
     atomicExch(status, W4A16_ETIMEOUT);
 }
 

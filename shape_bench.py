@@ -30,8 +30,8 @@ def run_case(pkg, synth, torch, kind, N, K, M, iters, ring_mb, warmup=5, graph=T
     w8 = kind.endswith("8")
     wbytes = (N * K + N * G * 2) if w8 else (N * K // 2 + N * G * 3)
     copies = max(1, min(64, -(-ring_mb * (1 << 20) // wbytes))) if ring_mb > 0 else 1
-    if kind == "prefill":
-        copies = 1  # compute bound: one weight copy
+    if kind == "prefill" and M >= 1024:
+        copies = 1  # compute bound: one weight copy (below that the weight stream matters: keep the ring)
     gen = torch.Generator(device="cuda").manual_seed(N * 31 + K)
     ws = []
     for _ in range(copies if not w8 else 0):

@@ -144,6 +144,70 @@ def test_skinny_model_shapes(pkg, oracle, synth, scratch, N, K, M):
     pkg.awq_free(w)
 
 
+def _edge_activations(synth, K):
+    """Rows of activations at the corners of the block fixed-point conversion (one exponent per token and
+    128-k group): all zero; an outlier channel 2^13 above its group; magnitudes of 1e-20 and 1e20; a group whose largest value is an exact power of two; one non-zero per group."""
+    rng = np.random.Generator(np.random.PCG64(99))
+    base = rng.standard_normal((6, K)).astype(np.float32)
+    base[0] = 0.0
+    base[1, 5::128] *= 8192.0
+    base[2] *= 1e-20
+    base[3] *= 1e20
+    base[4] = np.exp2(-rng.integers(0, 12, K)).astype(np.float32) * rng.choice([-1.0, 1.0], K)
+    base[4, 17::128] = -4.0
+    base[5] = 0.0
+    base[5, 100::128] = -0.3
+    return synth.f32_to_bf16_bits(base)
+
+
+def test_activation_corner_cases(pkg, oracle, synth, scratch):
+    """Every token is checked on its own scale (the rows differ by 40 orders of magnitude), through the
+    M = 1 kernel (conversion inside the kernel) and the M = 6 kernel (conversion in the pre-pass)."""
+    N, K = 384, 1024
+    (packed, scale, zp), w = _weights(pkg, synth, N, K, seed=77)
+    x = _edge_activations(synth, K)
+    M = x.shape[0]
+    ref = oracle.gemm_f64(packed, scale, zp, x)
+    Y = Guarded((M, N), torch.bfloat16)
+    pkg.gemm_small_w4a16(Y.t, w, dev_bf16(x), M, scratch)
+    torch.cuda.synchronize()
+    assert pkg.device_status() == 0 and Y.intact()
+    got = host_bits(Y.t)
+    for m in range(M):
+        y = Guarded((N,), torch.bfloat16)
+        pkg.gemv_w4a16(y.t, w, dev_bf16(x[m]), scratch)
+        torch.cuda.synchronize()
+        assert y.intact()
+        for bits in (got[m], host_bits(y.t)):
+            if m == 0:
+                assert not synth.bf16_bits_to_f32(bits).any()  # zero activations give exact zeros
+            else:
+                _check_bf16(bits, ref[m], synth)
+    assert pkg.device_status() == 0
+    pkg.awq_free(w)
+
+
+def test_non_finite_activations_stay_in_their_token(pkg, oracle, synth, scratch):
+    """An inf in one token makes that token's outputs non-finite (the reference gives inf or NaN there,
+    0 * inf where a weight equals its zero point) and leaves the other tokens' outputs as they were."""
+    N, K, M = 256, 512, 4
+    (packed, scale, zp), w = _weights(pkg, synth, N, K, seed=78)
+    x = synth.make_activations(M, K, seed=78)
+    clean = Guarded((M, N), torch.bfloat16)
+    pkg.gemm_small_w4a16(clean.t, w, dev_bf16(x), M, scratch)
+    x2 = x.copy()
+    x2[2, 200] = 0x7F80  # +inf
+    dirty = Guarded((M, N), torch.bfloat16)
+    pkg.gemm_small_w4a16(dirty.t, w, dev_bf16(x2), M, scratch)
+    torch.cuda.synchronize()
+    assert pkg.device_status() == 0 and dirty.intact()
+    a, b = host_bits(clean.t), host_bits(dirty.t)
+    for m in (0, 1, 3):
+        assert np.array_equal(a[m], b[m])
+    assert not np.isfinite(synth.bf16_bits_to_f32(b[2])).any()
+    pkg.awq_free(w)
+
+
 def test_skinny_rows_agree_with_gemv(pkg, synth, scratch):
     """Row m of the M-row product equals the GEMV of x[m] to within the reference's 2e-2 gate
     (bench/bench_verify.cu:55-75); here the two use the same kernel and k order, so bitwise."""
