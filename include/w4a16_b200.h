@@ -230,8 +230,9 @@ int w4a16_shard_rows(int out_f, int nranks, int rank, int* row_begin, int* row_e
 /* Completion flags of the fused exchanges. Every rank owns one 256-byte block of zero-initialised,
  * peer-mapped device memory (a symmetric-memory allocation, an IPC mapping ...): words [0, nranks) are
  * counters written by the ranks (word r by rank r: every signalling launch adds 65536 in total, each CTA
- * its share with a system-scope release add over NVLink right after its own last store), word 16 is the
- * rank's own count of signalling launches. blocks[r] is rank r's block as mapped here; blocks[rank] is the local one. All ranks must issue
+ * its share right after its own last store: one system-scope fence, then one add per rank over NVLink),
+ * word 16 is the rank's own count of signalling launches. blocks[r] is rank r's block as mapped here;
+ * blocks[rank] is the local one. All ranks must issue
  * the same sequence of signalling launches on a communicator (every w4a16_*_gather / *_sharded call below
  * signals once). Zero the blocks and make that visible on every rank (a host barrier) before the first
  * call. Every wait is bounded (about a second): on expiry the waiting kernel records W4A16_ETIMEOUT in
