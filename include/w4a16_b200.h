@@ -110,7 +110,10 @@ int w4a16_selftest_wait_timeout(int polls, void* stream);
 int w4a16_weights_alloc(w4a16_weights_t* w, int out_f, int in_f, int group_size, void* stream);
 /* awq_repack_into (gemv_w4a16.cuh:87-89, gemv_w4a16.cu:317-323): on-disk tensors
  * packed [out_f][in_f/8] u32, scale [out_f][G] bf16, zp [out_f/8][G] u32 -> private
- * layout, rows written at dst_row_offset (a multiple of 16). */
+ * layout, rows written at dst_row_offset (a multiple of 16). Asynchronous on `stream`; the next matmul call
+ * on the same stream is ordered behind it by the library. A matmul on ANOTHER stream, or weight buffers
+ * written by other means, need the caller's own event or synchronisation before the first launch that
+ * reads them (the kernels fetch weights before they wait for the kernel in front of them). */
 int w4a16_repack_into(const w4a16_weights_t* w, int dst_row_offset, const uint32_t* packed,
                       const uint16_t* scale, const uint32_t* zp, int out_f, void* stream);
 /* awq_free (gemv_w4a16.cuh:90). */

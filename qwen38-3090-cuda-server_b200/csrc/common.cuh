@@ -38,6 +38,14 @@ struct DeviceInfo {
 // Cached per device; returns nullptr (and sets the error) on failure.
 const DeviceInfo* device_info();
 
+// The matmul kernels start fetching weights before griddepcontrol.wait, and only that wait guarantees that the
+// stores of the kernel in front of them are visible. So every entry that writes weight buffers notes its
+// stream, and the next matmul call on that stream is enqueued without the programmatic-serialisation
+// attribute: fully ordered behind the write. take_weight_write is true once per noted stream; with no write
+// pending it costs one relaxed atomic load.
+void note_weight_write(cudaStream_t st);
+bool take_weight_write(cudaStream_t st);
+
 // Validates a weight container (non-null 16-byte aligned buffers, supported shape).
 int check_weights(const w4a16_weights_t* w);
 

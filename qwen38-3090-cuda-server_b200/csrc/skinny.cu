@@ -152,6 +152,7 @@ struct SkinnyParams {
   unsigned* comm_local;
   unsigned* comm_peers[8];   // every rank's block, index = rank (the local one included)
   int comm_n, comm_rank;
+  int ordered;               // launch without the programmatic-serialisation attribute (a weight write is in front)
   int comm_wait;             // before x is read: wait until every rank has signalled its previous launch
   int comm_signal;           // after the last store of the grid: raise this rank's flag on every rank
   void* pairs_peers[8];      // vocab-sharded lm_head: every rank's [ranks][16] table of (max, index) pairs
@@ -1369,7 +1370,7 @@ int launch_kernel(const SkinnyParams& p, int grid, cudaStream_t st, int smem) {
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
-  cfg.numAttrs = config().pdl ? 1 : 0;
+  cfg.numAttrs = (config().pdl && !p.ordered) ? 1 : 0;
   W4_CUDA(cudaLaunchKernelEx(&cfg, k_skinny<MT, WB, ST, COMM>, p));
   return W4A16_OK;
 }
@@ -1455,6 +1456,7 @@ int launch_skinny(SkinnyParams& p, const LayerRef* w, const uint16_t* x, int M, 
   W4_REQUIRE(w->num_groups <= 256, "in_f = %d is wider than the decode kernel supports (32768)", w->in_f);
   const DeviceInfo* di = device_info();
   if (!di) return W4A16_ECUDA;
+  p.ordered = take_weight_write(st) ? 1 : 0;
   const int TR = tile_rows();
   p.stream = w->stream;
   p.N = w->out_f;
@@ -1494,7 +1496,10 @@ int launch_skinny(SkinnyParams& p, const LayerRef* w, const uint16_t* x, int M, 
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
-    cfg.numAttrs = config().pdl ? 1 : 0;
+    // the first launch of the call carries the ordering behind a weight write; the main kernel may then overlap
+    // with this one as usual
+    cfg.numAttrs = (config().pdl && !p.ordered) ? 1 : 0;
+    p.ordered = 0;
     int tm = 1, cb = 8, nrows = 16;
     set_geometry(M, tm, cb, nrows);
     p.db_bytes = 128 * nrows;

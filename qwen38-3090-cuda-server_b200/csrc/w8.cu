@@ -107,6 +107,7 @@ int w4a16_w8_quantize(w4a16_w8_weights_t* dst, const uint16_t* src, int out_f, i
     cudaFree(s);
     return fail(W4A16_ECUDA, "w8_quantize: %s", cudaGetErrorString(e));
   }
+  note_weight_write(st);
   dst->qweight = static_cast<int8_t*>(q);
   dst->scale = static_cast<uint16_t*>(s);
   dst->out_f = out_f;

@@ -6,7 +6,9 @@
 // (src/kernels/gemv_w4a16.cu:308-334 of the reference project) and
 // w4a16_dequant_rows (src/kernels/gemm_w4a16.cu:15-38,56-61).
 #include <cstring>
+#include <atomic>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -34,6 +36,9 @@ int fail(int code, const char* fmt, ...) {
 constexpr int kMaxDevices = 64;
 static DeviceInfo g_dev[kMaxDevices];
 static std::mutex g_dev_mu;
+static std::mutex g_ww_mu;
+static std::vector<cudaStream_t> g_ww_streams;  // streams with a weight write no matmul call has followed yet
+static std::atomic<int> g_ww_count{0};
 
 __device__ int g_status_word = 0;
 
@@ -163,6 +168,25 @@ int grid_for(long long n, int block) {
 
 }  // namespace
 
+void note_weight_write(cudaStream_t st) {
+  std::lock_guard<std::mutex> lk(g_ww_mu);
+  for (cudaStream_t q : g_ww_streams)
+    if (q == st) return;
+  g_ww_streams.push_back(st);
+  g_ww_count.store(static_cast<int>(g_ww_streams.size()), std::memory_order_release);
+}
+bool take_weight_write(cudaStream_t st) {
+  if (g_ww_count.load(std::memory_order_relaxed) == 0) return false;
+  std::lock_guard<std::mutex> lk(g_ww_mu);
+  for (size_t i = 0; i < g_ww_streams.size(); ++i)
+    if (g_ww_streams[i] == st) {
+      g_ww_streams.erase(g_ww_streams.begin() + static_cast<long>(i));
+      g_ww_count.store(static_cast<int>(g_ww_streams.size()), std::memory_order_release);
+      return true;
+    }
+  return false;
+}
+
 int check_weights(const w4a16_weights_t* w) {
   W4_REQUIRE(w != nullptr, "weights: null struct");
   W4_REQUIRE(w->qweight && w->scale && w->zp, "weights: null buffer");
@@ -241,6 +265,7 @@ int w4a16_weights_alloc(w4a16_weights_t* w, int out_f, int in_f, int group_size,
     // rows of the last tile past out_f: zero scales, so they contribute nothing and are never stored.
     // On the caller's stream, so that it is ordered before the repack that follows on that stream.
     e = cudaMemsetAsync(q, 0, qb, static_cast<cudaStream_t>(stream));
+    note_weight_write(static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) {
       cudaFree(q);
       cudaFree(s);
@@ -276,6 +301,7 @@ static int repack_rows(const w4a16_weights_t* w, int dst_row_offset, const uint3
   const long long ns = static_cast<long long>(out_f) * w->num_groups;
   k_repack_sz<<<grid_for(ns, 256), 256, 0, st>>>(stream_base, scale, zp, out_f, w->num_groups, dst_row_offset, inter);
   W4_CUDA(cudaGetLastError());
+  note_weight_write(st);
   return W4A16_OK;
 }
 
