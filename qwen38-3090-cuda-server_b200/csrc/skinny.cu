@@ -924,7 +924,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
               const uint32_t slot = (k & 1) ? (ew >> 8) & 0xFFu : ew & 0xFFu;
               const float s = __uint_as_float(sz[j] & 0xFFFF0000u);
               const float z = __uint_as_float(0x4B000000u | (sz[j] & 0xFFu)) - 8388608.0f;
-#pragma unroll
               {
                 // (sum of X, 2^-p): by cache slot, or (pre-pass) by k group
                 const float2 xv = xs_tab[kStream ? ((ew >> 19) & 0xFFu) + (k & 1) : slot];

@@ -49,3 +49,32 @@ def test_static_scratch_rejects_layers_beyond_its_limit(pkg, synth):
         pkg.gemv_w4a16_static(y, w, x)
     assert e.value.code == -1 and "65536" in str(e.value)
     pkg.awq_free(w)
+
+
+def test_static_scratch_entry_allocates_nothing_and_captures(pkg, synth):
+    """After the first call on the device, further calls leave the free device memory where it was, and
+    the entry can be captured into a CUDA graph whose replay gives the eager call's bits."""
+    N, K = 4096, 2048
+    packed, scale, zp = synth.make_weights(N, K, seed=5)
+    w = pkg.weights_from_numpy(packed, scale, zp)
+    x = dev_bf16(synth.make_activations(1, K, seed=6)[0])
+    eager = torch.empty(N, dtype=torch.bfloat16, device="cuda")
+    pkg.gemv_w4a16_static(eager, w, x)  # first call on this device: one-time kernel attribute, outside capture
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        pkg.gemv_w4a16_static(eager, w, x)
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, f"free device memory moved by {free0 - free1} bytes across three calls"
+    replayed = torch.zeros(N, dtype=torch.bfloat16, device="cuda")
+    side = torch.cuda.Stream()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            pkg.gemv_w4a16_static(replayed, w, x, stream=side)
+        g.replay()
+    torch.cuda.synchronize()
+    assert pkg.device_status() == 0
+    assert torch.equal(replayed.view(torch.int16), eager.view(torch.int16))
+    pkg.awq_free(w)
