@@ -325,14 +325,23 @@ __device__ __forceinline__ float small_int_to_float(uint32_t v) {
 // use as consecutive 16-byte rows (an 8-row core matrix every 128 bytes). The rows the tensor core reads
 // beyond them are the next chunk's bytes: they only produce accumulator columns nobody reads, and the
 // whole K range of a token fits: 384 bytes per group for M = 1.
+// M = 1 with the conversion inside the kernel: warps 16..19 have nothing to do once the activations are
+// converted. They take over the ends of the split-tile segments from the fix-up warps (the partial rows'
+// stores, the ticket and the sum of the pieces are a global-memory round trip of 1 to 2 us under load, which a
+// fix-up warp in the middle of the stream cannot make up for). Each lane quarter has a mailbox of two entries -
+// a CTA's unit range has at most two split pieces - of 32 partial sums and the tile number.
+template <int MT, bool ST>
+__host__ __device__ constexpr bool tile_end_helper() { return MT == 1 && !ST; }
+constexpr int kMailStride = 40;                    // words per mailbox entry (32 sums, the tile, padding)
+constexpr int kMailWords = 2 * CW * kMailStride;
 template <int MT, bool ST>
 __host__ __device__ constexpr int bar_count(int depth, int bdepth) {
-  return 2 * depth + Geo<MT, ST>::AD2 + 2 * Geo<MT, ST>::DD2 + 2 + (ST ? 2 * bdepth : 0) + 1;
+  return 2 * depth + Geo<MT, ST>::AD2 + 2 * Geo<MT, ST>::DD2 + 2 + (ST ? 2 * bdepth : 0) + 1 + (tile_end_helper<MT, ST>() ? 2 * CW : 0);
 }
 template <int MT, bool ST>
 __host__ __device__ inline int total_smem(int depth, int stage_bytes, int b_bytes, int xs_bytes, int bdepth) {
   return depth * stage_bytes + b_bytes + kSide * kTileRows * 4 + xs_bytes + kTable * 8 + 256 * 4 +
-         bar_count<MT, ST>(depth, bdepth) * 8 + 16;
+         (tile_end_helper<MT, ST>() ? kMailWords * 4 : 0) + bar_count<MT, ST>(depth, bdepth) * 8 + 16;
 }
 
 // One token's 128 values of one k group (this lane: k = 4 lane .. 4 lane + 3, `rv`) -> three int8 digit
@@ -395,7 +404,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   uint8_t* xsinv = side + kSide * kTileRows * 4;
   uint2* table = reinterpret_cast<uint2*>(xsinv + p.xs_bytes);
   uint32_t* ready = reinterpret_cast<uint32_t*>(table + kTable);  // [slot]: tokens whose digit rows are written
-  uint64_t* bars = reinterpret_cast<uint64_t*>(ready + 256);
+  float* mail = reinterpret_cast<float*>(ready + 256);  // [2 entries][lane quarter][kMailStride] (helper instances only)
+  constexpr bool kHelper = tile_end_helper<MT, ST>();
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ready + 256 + (kHelper ? kMailWords : 0));
   const int BD = p.bdepth, BS = p.bshift;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + bar_count<MT, ST>(DS, BD));
   int* sflag = reinterpret_cast<int*>(tmem_slot + 1);
@@ -413,11 +424,16 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   // bytes between the digit rows of consecutive groups (cache slots for M = 1, ring slots otherwise), and
   // between the 16-k chunks of one group
   const int b_slot = kStream ? p.db_bytes : 384 * M, b_lbo = kStream ? 16 * N : 48 * M;
-  int T;  // steps of this CTA
+  int T;       // steps of this CTA
+  int nsplit;  // its segments that are pieces of split tiles AND have more of the walk behind them (0, 1 or 2):
+               // the pieces come first in the walk, so only the last piece of a range without whole tiles is left out
   {
     SegIter si;
     si.init(u0, u1, G, p.mg_G);
     T = si.steps();
+    nsplit = (si.head_partial ? 1 : 0) + (si.tail_partial ? 1 : 0);
+    const int whole = si.t_last - si.t_first + 1 - nsplit;
+    if (whole == 0 && nsplit > 0) --nsplit;
   }
 
   const uint32_t ring_a = smem_u32(ring);
@@ -435,6 +451,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   const uint32_t bfull_a = tmemrdy_a + 8;           // [BD]  M >= 2: digit rows of a step landed (tx bytes)
   const uint32_t bempty_a = bfull_a + BD * 8;       // [BD]  M >= 2: the step's MMAs have completed (seen by the first fix-up warp)
   const uint32_t commrdy_a = bfull_a + (kStream ? 2 * BD : 0) * 8;  // every rank's flag of the previous launch has been seen
+  const uint32_t mailfull_a = commrdy_a + 8;        // [2][CW] helper instances: a split segment's sums are in the mailbox
 
   if (tid < 256) ready[tid] = 0u;
   {
@@ -779,7 +796,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
     // One warp per TMEM lane quarter and token set: warps 0..3 take the first TM tokens, warps 16..19 and
     // 20..23 (idle after converting) the next ones when M is larger. Each keeps its own running sums, so
     // the sets never have to be combined; a D slot is released when every active warp has loaded from it.
-    auto fixup = [&](const int F) {           // F: this warp's token set
+    auto fixup = [&](const int F, const bool helper) {  // F: this warp's token set; helper: only the split segments' ends
     constexpr int TM = GE::TM, CB = GE::CB;
     const int m0 = F * TM;                    // its tokens: m0 .. m0 + TM - 1 (those below M)
     const int q = warp & 3, r = q * 32 + lane;
@@ -864,7 +881,21 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
         ok = false;
       }
     }
-    for (int t = 0; ok && t < T;) {
+    const bool hands_over = kHelper && !helper && !p.argmax;  // split segments end in the helper warp
+    int nmail = 0;                                            // mailbox entries sent (fix-up) or taken (helper)
+    for (int t = 0; ok && (helper ? nmail < nsplit : t < T);) {
+      bool seg_end = true, seg_whole = false;
+      int seg_tile = 0;
+      if (helper) {
+        const float* mslot = mail + (nmail * CW + q) * kMailStride;
+        if (!wait_h(mailfull_a + (nmail * CW + q) * 8, 0, p.hint, 4 * kSpinLimit)) {
+          atomicExch(p.status, W4A16_ETIMEOUT);
+          break;
+        }
+        fin[0] = mslot[lane];
+        seg_tile = reinterpret_cast<const int*>(mslot)[32];
+        ++nmail;
+      } else {
       // A round is one or two steps (two unless the first ends its segment): one wait per issuer (a commit
       // covers everything its thread issued before), GB groups' tensor-memory loads in flight together.
       if (!wait_h(done_a + (t & (DD2 - 1)) * 8, static_cast<uint32_t>(t / DD2) & 1u, p.hint, kSpinLimit)) {
@@ -1004,10 +1035,26 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
       }
       const uint2 el = two ? e1 : e0;  // the round's last step
       t += two ? 2 : 1;
-      if ((el.x >> 17) & 1u) {
-        // ---- end of this CTA's segment of row tile el.y ----
-        const int tile = static_cast<int>(el.y);
-        bool last = ((el.x >> 18) & 1u) != 0;  // a whole tile is final at once
+      seg_end = ((el.x >> 17) & 1u) != 0;
+      seg_whole = ((el.x >> 18) & 1u) != 0;
+      seg_tile = static_cast<int>(el.y);
+      }
+      if (seg_end) {
+        // ---- end of this CTA's segment of row tile seg_tile ----
+        const int tile = seg_tile;
+        bool last = seg_whole;  // a whole tile is final at once
+        if constexpr (kHelper) {
+          if (hands_over && !last && t < T) {  // (the CTA's last segment ends right here: a hand-over would only add a hop)
+            float* mslot = mail + (nmail * CW + q) * kMailStride;
+            mslot[lane] = fin[0];
+            if (lane == 0) reinterpret_cast<int*>(mslot)[32] = tile;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(mailfull_a + (nmail * CW + q) * 8);
+            ++nmail;
+            fin[0] = 0.f;
+            continue;
+          }
+        }
         float v[TM];
 #pragma unroll
         for (int i = 0; i < TM; ++i) v[i] = fin[i];
@@ -1146,7 +1193,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
     }
     };
     const int fset = warp < CW ? 0 : (warp - kWConv0) / CW + 1;
-    if (fset < GE::FW && fset * GE::TM < M) fixup(fset);
+    const bool helper = kHelper && warp >= kWConv0 && warp < kWConv0 + CW && !p.argmax;
+    if (helper || (fset < GE::FW && fset * GE::TM < M)) fixup(helper ? 0 : fset, helper);
   }
 
   // every role ends here: tensor memory goes back only after all its readers and writers are done
@@ -1377,7 +1425,7 @@ int launch_kernel(const SkinnyParams& p, int grid, cudaStream_t st, int smem) {
 // M = 1: the digit rows of `groups` k groups (384 B + one pair per group) must fit beside a two-stage
 // weight ring.
 bool gemv_cache_fits(int groups, int stage_bytes, int smem_optin) {
-  const int fixed = 2 * stage_bytes + kSide * kTileRows * 4 + kTable * 8 + 64 * 8 + 16 + 256;
+  const int fixed = 2 * stage_bytes + kSide * kTileRows * 4 + kTable * 8 + 256 * 4 + kMailWords * 4 + 64 * 8 + 16 + 256;
   return groups * (384 + 8) <= smem_optin - fixed;
 }
 
