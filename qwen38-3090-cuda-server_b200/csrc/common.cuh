@@ -237,6 +237,17 @@ __device__ __forceinline__ uint32_t sub_bf16x2(uint32_t a, uint32_t b) {
   return d;
 }
 
+// 64-bit words that carry a value and its "valid" tag together: one store makes both visible at once, so the
+// reader needs no fence and the writer no flag.
+__device__ __forceinline__ void st_relaxed_gpu_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_gpu_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
 // ---- cross-rank flags: one system-scope fence per CTA, relaxed adds into the peers' flag words, bounded polling ----
 // A rank's block: words [0, 8) are counters written by the ranks (word r by rank r), word 16 is this rank's own
 // count of signalling launches. Every signalling launch adds exactly kCommUnit to this rank's counter on every

@@ -77,6 +77,7 @@ constexpr int kSideSteps = 12;             // (scale, zp) side ring, in steps: a
 constexpr int kSide = kSideSteps * 2;      // in groups
 constexpr int kTable = 64;                 // step table entries (ring)
 constexpr uint32_t kSpinLimit = 1u << 20;  // polls before a wait gives up
+constexpr uint32_t kPieceTag = 0x7A6B5C4Du;  // upper half of a published (sum, tag) word of a split tile's piece
 constexpr int kFixBar = 1;                 // named barrier of the fix-up warps
 constexpr int kTmemCols = 512;             // all of tensor memory; the next launch's CTA, resident beside this one,
                                            // gets it when this CTA exits (it cannot multiply before that anyway)
@@ -300,13 +301,8 @@ __device__ __forceinline__ void tmem_ld_span(uint32_t base, uint32_t* d) {
     tmem_ld_span<C0 + W, CNT - W>(base, d + W);
   }
 }
-// Ticket counter with release + acquire in one operation: the partial rows written before it (by the whole
-// warp, ordered by __syncwarp) are visible to whoever draws a later ticket, and whoever draws the last one
-// sees every earlier contributor's rows. Saves the two full memory fences of the fence-atomic-fence form.
-__device__ __forceinline__ unsigned ticket_acq_rel(unsigned* addr) {
-  unsigned old;
-  asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(addr) : "memory");
-  return old;
+__device__ __forceinline__ unsigned long long tagged(float v) {
+  return (static_cast<unsigned long long>(kPieceTag) << 32) | __float_as_uint(v);
 }
 // u / d for u * d < 2^40, with m = ceil(2^40 / d) from the host: a multiply and a shift instead of the
 // division loop (three of them sat in the start-up path of every launch).
@@ -425,15 +421,14 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   // between the 16-k chunks of one group
   const int b_slot = kStream ? p.db_bytes : 384 * M, b_lbo = kStream ? 16 * N : 48 * M;
   int T;       // steps of this CTA
-  int nsplit;  // its segments that are pieces of split tiles AND have more of the walk behind them (0, 1 or 2):
-               // the pieces come first in the walk, so only the last piece of a range without whole tiles is left out
+  int nsplit;  // 1 if the helper warps get a segment of this CTA: the piece at the end of its range (the first
+               // piece of that tile, so this CTA adds the tile up) with whole tiles still to come after it
   {
     SegIter si;
     si.init(u0, u1, G, p.mg_G);
     T = si.steps();
-    nsplit = (si.head_partial ? 1 : 0) + (si.tail_partial ? 1 : 0);
-    const int whole = si.t_last - si.t_first + 1 - nsplit;
-    if (whole == 0 && nsplit > 0) --nsplit;
+    const int whole = si.t_last - si.t_first + 1 - (si.head_partial ? 1 : 0) - (si.tail_partial ? 1 : 0);
+    nsplit = (si.tail_partial && whole > 0) ? 1 : 0;
   }
 
   const uint32_t ring_a = smem_u32(ring);
@@ -802,7 +797,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
     const int q = warp & 3, r = q * 32 + lane;
     const int fslot = F * CW + q;             // this warp's index among the fix-up warps
     const uint32_t lane_t = tmem + (static_cast<uint32_t>(q * 32) << 16) + GE::kDCol0 + (kStream ? F * CB : 0);
-    unsigned* tickets = p.counters + static_cast<size_t>(F) * p.tiles * CW;  // [tile][quarter] of this token set
 
     float fin[TM];
     float best_v[TM];
@@ -1043,65 +1037,82 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
         // ---- end of this CTA's segment of row tile seg_tile ----
         const int tile = seg_tile;
         bool last = seg_whole;  // a whole tile is final at once
-        if constexpr (kHelper) {
-          if (hands_over && !last && t < T) {  // (the CTA's last segment ends right here: a hand-over would only add a hop)
-            float* mslot = mail + (nmail * CW + q) * kMailStride;
-            mslot[lane] = fin[0];
-            if (lane == 0) reinterpret_cast<int*>(mslot)[32] = tile;
-            __syncwarp();
-            if (lane == 0) mbar_arrive(mailfull_a + (nmail * CW + q) * 8);
-            ++nmail;
-            fin[0] = 0.f;
-            continue;
-          }
-        }
         float v[TM];
 #pragma unroll
         for (int i = 0; i < TM; ++i) v[i] = fin[i];
         if (!last) {
-          // split tile: this warp publishes its 32 rows and moves on; no CTA-wide barrier
+          // Split tile. Every piece but the tile's first is PUBLISHED: its 32 rows go to this CTA's slot as
+          // 8-byte (sum, tag) words and the warp moves on - no fence, no ticket, nothing to wait for. The CTA
+          // that owns the tile's first units is the one that adds up: it polls the other pieces' words until
+          // their tags are there, adds them in CTA order to its own sums (a fixed order: bitwise reproducible),
+          // zeroes the words for the next launch and writes the rows out. That piece is always the last one
+          // of its owner's walk apart from whole tiles (the piece at the END of a range comes second, after
+          // the piece at its start), and the pieces it waits for are the first or only segments of theirs.
           // first and last CTA whose unit range touches this tile (32-bit: U * gridDim.x < 2^32, host-checked)
           const uint32_t X0 = static_cast<uint32_t>(tile) * G, Uu = static_cast<uint32_t>(U);
           const int c_first = static_cast<int>(((X0 + 1) * gridDim.x - 1) / Uu);
           const int c_last = static_cast<int>(((X0 + G) * gridDim.x - 1) / Uu);
-          const int which = (static_cast<int>(fdiv(static_cast<uint32_t>(u0), p.mg_G)) == tile) ? 0 : 1;
-          float* slotp = p.partial + (static_cast<size_t>(blockIdx.x) * 2 + which) * SLOT;
+          unsigned long long* slots = reinterpret_cast<unsigned long long*>(p.partial);
+          if (static_cast<int>(blockIdx.x) != c_first) {
+            const int which = (static_cast<int>(fdiv(static_cast<uint32_t>(u0), p.mg_G)) == tile) ? 0 : 1;
+            unsigned long long* slotp = slots + (static_cast<size_t>(blockIdx.x) * 2 + which) * SLOT;
 #pragma unroll
-          for (int i = 0; i < TM; ++i)
-            if (m0 + i < M) slotp[(m0 + i) * kTileRows + r] = fin[i];
-          __syncwarp();
-          unsigned old = 0;
-          if (lane == 0) old = ticket_acq_rel(tickets + tile * CW + q);
-          old = __shfl_sync(0xffffffffu, old, 0);
-          if (old == static_cast<unsigned>(c_last - c_first)) {
-            // The last ticket for these rows: every other piece is already in memory, so this warp adds
-            // them up right away (the D ring is deep enough to absorb the pause), in a fixed order.
-            if (lane == 0) tickets[tile * CW + q] = 0;  // leave it clean for the next launch
+            for (int i = 0; i < TM; ++i)
+              if (m0 + i < M) st_relaxed_gpu_u64(slotp + (m0 + i) * kTileRows + r, tagged(fin[i]));
+          } else {
+            if constexpr (kHelper) {
+              if (hands_over && t < T) {  // more of the walk follows: the helper warp does the waiting
+                float* mslot = mail + (nmail * CW + q) * kMailStride;
+                mslot[lane] = fin[0];
+                if (lane == 0) reinterpret_cast<int*>(mslot)[32] = tile;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(mailfull_a + (nmail * CW + q) * 8);
+                ++nmail;
+                fin[0] = 0.f;
+                continue;
+              }
+            }
             last = true;
-            __syncwarp();
+            constexpr int PB = TM <= 2 ? 4 : (TM <= 4 ? 2 : 1);  // pieces whose loads are in flight together
+            for (int cb = c_first + 1; cb <= c_last && ok; cb += PB) {
+              unsigned long long piece[PB][TM];
+              const unsigned long long* sl[PB];
 #pragma unroll
-            for (int i = 0; i < TM; ++i) v[i] = 0.f;
-            // four pieces' loads in flight at a time, added in CTA order: bitwise reproducible
-            for (int cb = c_first; cb <= c_last; cb += 4) {
-              float piece[4][TM];
+              for (int k = 0; k < PB; ++k) {
+                const int cc = cb + k <= c_last ? cb + k : c_last;
+                const uint32_t cu0 = fdiv(Uu * static_cast<uint32_t>(cc), p.mg_grid);
+                const int wc = (static_cast<int>(fdiv(cu0, p.mg_G)) == tile) ? 0 : 1;
+                sl[k] = slots + (static_cast<size_t>(cc) * 2 + wc) * SLOT + r;
+              }
+              uint32_t spins = 0;
+              for (;;) {
+                bool all = true;
 #pragma unroll
-              for (int k = 0; k < 4; ++k) {
-                const int cc = cb + k;
-                if (cc <= c_last) {
-                  const uint32_t cu0 = fdiv(Uu * static_cast<uint32_t>(cc), p.mg_grid);
-                  const int wc = (static_cast<int>(fdiv(cu0, p.mg_G)) == tile) ? 0 : 1;
-                  const float* sl = p.partial + (static_cast<size_t>(cc) * 2 + wc) * SLOT;
+                for (int k = 0; k < PB; ++k)
+                  if (cb + k <= c_last) {
 #pragma unroll
-                  for (int i = 0; i < TM; ++i)
-                    if (m0 + i < M) piece[k][i] = __ldcg(sl + (m0 + i) * kTileRows + r);
+                    for (int i = 0; i < TM; ++i)
+                      if (m0 + i < M) {
+                        piece[k][i] = ld_relaxed_gpu_u64(sl[k] + (m0 + i) * kTileRows);
+                        all = all && static_cast<uint32_t>(piece[k][i] >> 32) == kPieceTag;
+                      }
+                  }
+                if (__all_sync(0xffffffffu, all)) break;
+                if (++spins > kSpinLimit) {
+                  atomicExch(p.status, W4A16_ETIMEOUT);
+                  ok = false;
+                  break;
                 }
               }
 #pragma unroll
-              for (int k = 0; k < 4; ++k)
+              for (int k = 0; k < PB; ++k)
                 if (cb + k <= c_last) {
 #pragma unroll
                   for (int i = 0; i < TM; ++i)
-                    if (m0 + i < M) v[i] += piece[k][i];
+                    if (m0 + i < M) {
+                      v[i] += __uint_as_float(static_cast<uint32_t>(piece[k][i]));
+                      st_relaxed_gpu_u64(const_cast<unsigned long long*>(sl[k]) + (m0 + i) * kTileRows, 0ull);
+                    }
                 }
             }
           }
@@ -1729,8 +1740,8 @@ int w4a16_scratch_alloc(w4a16_scratch_t* s, int max_in, int max_out, int min_gro
   s->max_m = max_m;
   s->max_groups = max_in / min_group;
   s->max_splits = di->sms * kMaxCtasPerSm;  // CTAs of the persistent grid
-  // two partial tiles per CTA (head and tail of its unit range), widest tile, 16 tokens
-  s->partial_elems = static_cast<size_t>(s->max_splits) * 2 * kTileRows * 16;
+  // two partial tiles per CTA (head and tail of its unit range), widest tile, 16 tokens, 8-byte (sum, tag) words
+  s->partial_elems = static_cast<size_t>(s->max_splits) * 2 * kTileRows * 16 * 2;
   const size_t counters = counter_bytes(max_out);
   // per-CTA argmax pairs, then (max_m >= 2) the pre-pass output: digit rows of max_m tokens for every k group
   const size_t pairs = pair_bytes(s->max_splits) +
@@ -1740,6 +1751,7 @@ int w4a16_scratch_alloc(w4a16_scratch_t* s, int max_in, int max_out, int min_gro
   if (e == cudaSuccess) e = cudaMalloc(&cn, counters);
   if (e == cudaSuccess) e = cudaMalloc(&pa, s->partial_elems * sizeof(float));
   if (e == cudaSuccess) e = cudaMemset(cn, 0, counters);
+  if (e == cudaSuccess) e = cudaMemset(pa, 0, s->partial_elems * sizeof(float));  // no piece published yet
   if (e != cudaSuccess) {
     cudaFree(xf);
     cudaFree(cn);
@@ -1764,11 +1776,10 @@ int w4a16_scratch_free(w4a16_scratch_t* s) {
 
 int w4a16_scratch_check(const w4a16_scratch_t* s, int out_f, int M) {
   W4_REQUIRE(s != nullptr, "scratch_check: null struct");
-  (void)M;
   const DeviceInfo* di = device_info();
   if (!di) return W4A16_ECUDA;
   const int ctas = di->sms * kMaxCtasPerSm;
-  const size_t need = static_cast<size_t>(ctas) * 2 * kTileRows * 16;
+  const size_t need = static_cast<size_t>(ctas) * 2 * kTileRows * (M > 0 && M <= 16 ? M : 16) * 2;
   if (need > s->partial_elems)
     return fail(W4A16_ESCRATCH, "scratch: partial buffer holds %zu floats, %zu needed", s->partial_elems, need);
   if (out_f > s->max_out)
@@ -1791,6 +1802,7 @@ int w4a16_choose_splits(int out_f, int num_groups) {
 int w4a16_scratch_reset(w4a16_scratch_t* s, void* stream) {
   W4_REQUIRE(s != nullptr && s->xgsum != nullptr, "scratch_reset: scratch not allocated");
   W4_CUDA(cudaMemsetAsync(s->xgsum, 0, counter_bytes(s->max_out), static_cast<cudaStream_t>(stream)));
+  if (s->partial) W4_CUDA(cudaMemsetAsync(s->partial, 0, s->partial_elems * sizeof(float), static_cast<cudaStream_t>(stream)));
   return W4A16_OK;
 }
 
@@ -1864,7 +1876,7 @@ int w4a16_gemv_static_reset(void* stream) {
   if (!di) return W4A16_ECUDA;
   unsigned char* b = nullptr;
   if (int rc = static_scratch_base(&b, di->device, static_cast<cudaStream_t>(stream))) return rc;
-  W4_CUDA(cudaMemsetAsync(b + kStaticPartialBytes, 0, kStaticCounterBytes, static_cast<cudaStream_t>(stream)));
+  W4_CUDA(cudaMemsetAsync(b, 0, kStaticPartialBytes + kStaticCounterBytes, static_cast<cudaStream_t>(stream)));
   return W4A16_OK;
 }
 
