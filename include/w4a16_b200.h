@@ -122,9 +122,9 @@ int w4a16_weights_free(w4a16_weights_t* w);
 /* gemv_scratch_alloc / gemv_scratch_free (gemv_w4a16.cuh:106-107, gemv_w4a16.cu:344-371). */
 int w4a16_scratch_alloc(w4a16_scratch_t* s, int max_in, int max_out, int min_group, int max_m);
 int w4a16_scratch_free(w4a16_scratch_t* s);
-/* Zeroes the arrival tickets of a scratch on `stream`. Only needed after a bounded wait
- * expired (a launch that gave up may leave tickets behind); launches that complete leave
- * them at zero themselves. */
+/* Zeroes the counters and the published split-tile pieces of a scratch on `stream`. Only needed
+ * after a bounded wait expired (a launch that gave up may leave some behind); launches that
+ * complete leave them at zero themselves. */
 int w4a16_scratch_reset(w4a16_scratch_t* s, void* stream);
 /* gemv_partial_check (gemv_w4a16.cuh:109): W4A16_ESCRATCH instead of abort. */
 int w4a16_scratch_check(const w4a16_scratch_t* s, int out_f, int M);
@@ -145,7 +145,7 @@ int w4a16_gemv(void* y, int y_is_f32, const w4a16_weights_t* w, const uint16_t* 
  * and clears its counters, so make that call before capturing a stream. All calls share the
  * array: calls that overlap on the GPU race; calls in stream order are fine. */
 int w4a16_gemv_static(void* y, int y_is_f32, const w4a16_weights_t* w, const uint16_t* x, void* stream);
-/* Zeroes the arrival tickets inside the built-in array of w4a16_gemv_static on `stream`
+/* Zeroes the counters and published pieces inside the built-in array of w4a16_gemv_static on `stream`
  * (recovery after W4A16_ETIMEOUT; allocates nothing). */
 int w4a16_gemv_static_reset(void* stream);
 /* gemm_small_w4a16 and gemm_mma_w4a16 (gemv_w4a16.cuh:124-125,187-188):

@@ -10,9 +10,10 @@
 //   * persistent grid, one CTA per SM (24 warps, all 512 tensor-memory columns, about 160 KB of shared
 //     memory). The (128-row tile, k group) units of the matrix are dealt out as equal contiguous
 //     ranges, so every CTA streams the same number of bytes whatever N and K are. A row tile whose K
-//     range is shared by several CTAs is finished by the last warp to arrive for its rows, which
-//     adds the partial tiles in a fixed order (bitwise reproducible, no float atomics). Shared
-//     tiles are processed FIRST, so that reduction overlaps everybody's main loop.
+//     range is shared by several CTAs is finished by the CTA that owns its first units: the others
+//     publish their partial rows as (sum, tag) words, the owner adds them in CTA order (bitwise
+//     reproducible, no float atomics, no fences). Shared tiles are processed FIRST, so that this
+//     overlaps everybody's main loop.
 //   * the arithmetic is exact integer work on the 5th-generation tensor cores
 //     (tcgen05.mma kind::i8, 128 x N x 32, int32 accumulators in tensor memory):
 //       - weights: a nibble becomes an int8 with ONE logic instruction per four weights
@@ -322,10 +323,10 @@ __device__ __forceinline__ float small_int_to_float(uint32_t v) {
 // beyond them are the next chunk's bytes: they only produce accumulator columns nobody reads, and the
 // whole K range of a token fits: 384 bytes per group for M = 1.
 // M = 1 with the conversion inside the kernel: warps 16..19 have nothing to do once the activations are
-// converted. They take over the ends of the split-tile segments from the fix-up warps (the partial rows'
-// stores, the ticket and the sum of the pieces are a global-memory round trip of 1 to 2 us under load, which a
-// fix-up warp in the middle of the stream cannot make up for). Each lane quarter has a mailbox of two entries -
-// a CTA's unit range has at most two split pieces - of 32 partial sums and the tile number.
+// converted. When a fix-up warp reaches the end of a split tile's piece that this CTA has to add up, and more of
+// the CTA's walk follows, the waiting for the other CTAs' pieces (a global-memory round trip of 1 to 2 us under
+// load, which a fix-up warp in the middle of the stream cannot make up for) goes to the helper warp of its lane
+// quarter: a mailbox entry of 32 sums and the tile number (two entries per quarter; one is used).
 template <int MT, bool ST>
 __host__ __device__ constexpr bool tile_end_helper() { return MT == 1 && !ST; }
 constexpr int kMailStride = 40;                    // words per mailbox entry (32 sums, the tile, padding)
@@ -1333,7 +1334,8 @@ const Config& config() {
   return c;
 }
 
-// arrival tickets per (token set, tile, lane quarter) + the argmax ticket, for layers of up to max_out rows
+// counters of the scratch (sized for one per (token set, tile, lane quarter); in use: the fused argmax's arrival
+// ticket behind them), for layers of up to max_out rows
 size_t counter_bytes(int max_out) {
   return (3 * (static_cast<size_t>(max_out) / kTileRows + 2) * CW + 8) * sizeof(unsigned);
 }
