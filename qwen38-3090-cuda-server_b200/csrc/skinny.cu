@@ -172,10 +172,13 @@ __device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
 }
 
 // ---- the order in which a CTA walks its unit range [u0,u1) -------------------------------
-// A segment is a run of consecutive k groups of one row tile. Row tiles that this CTA shares with a
-// neighbour come first (the piece at the start of the range, then the piece at its end), whole tiles
-// after, so the cross-CTA reduction of the shared tiles overlaps everybody's main loop instead of
-// sitting at the end of the kernel. A segment of L groups is ceil(L/2) steps.
+// A segment is a run of consecutive k groups of one row tile. The piece at the START of the range (the end of
+// a row tile that the previous CTA began) always comes first: it is only published, and the CTA that adds that
+// tile up finds it early. The piece at the END of the range (the beginning of a row tile, which this CTA adds
+// up once the other CTAs' pieces are there) comes second where an idle warp can do the waiting while the whole
+// tiles stream (tail_last = false: M = 1 without the fused argmax), and last otherwise, when every piece it
+// waits for - first or only segments of their CTAs - has long been published. A segment of L groups is
+// ceil(L/2) steps.
 struct Seg {
   int tile, g0, L;
   bool whole;  // the segment is the tile's full K range
@@ -183,11 +186,12 @@ struct Seg {
 
 struct SegIter {
   int G, t_first, t_last, head_g0, tail_g1;
-  bool single, head_partial, tail_partial;
+  bool single, head_partial, tail_partial, tail_last;
   int phase, t;
 
-  __device__ void init(int u0, int u1, int G_, unsigned long long mg_G) {
+  __device__ void init(int u0, int u1, int G_, unsigned long long mg_G, bool tail_last_) {
     G = G_;
+    tail_last = tail_last_;
     t_first = static_cast<int>(static_cast<uint32_t>((static_cast<unsigned long long>(u0) * mg_G) >> 40));
     t_last = static_cast<int>(static_cast<uint32_t>((static_cast<unsigned long long>(u1 - 1) * mg_G) >> 40));
     head_g0 = u0 - t_first * G;
@@ -208,7 +212,7 @@ struct SegIter {
     }
     if (phase == 1) {
       phase = 2;
-      if (tail_partial) {
+      if (tail_partial && !tail_last) {
         s.tile = t_last; s.g0 = 0; s.L = tail_g1; s.whole = false;
         return true;
       }
@@ -219,6 +223,13 @@ struct SegIter {
       if (tt == t_last && tail_partial) continue;
       s.tile = tt; s.g0 = 0; s.L = G; s.whole = true;
       return true;
+    }
+    if (phase == 2) {
+      phase = 3;
+      if (tail_partial && tail_last) {
+        s.tile = t_last; s.g0 = 0; s.L = tail_g1; s.whole = false;
+        return true;
+      }
     }
     return false;
   }
@@ -421,15 +432,16 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
   // bytes between the digit rows of consecutive groups (cache slots for M = 1, ring slots otherwise), and
   // between the 16-k chunks of one group
   const int b_slot = kStream ? p.db_bytes : 384 * M, b_lbo = kStream ? 16 * N : 48 * M;
+  const bool tail_last = !(tile_end_helper<MT, ST>() && !p.argmax);  // see SegIter
   int T;       // steps of this CTA
   int nsplit;  // 1 if the helper warps get a segment of this CTA: the piece at the end of its range (the first
                // piece of that tile, so this CTA adds the tile up) with whole tiles still to come after it
   {
     SegIter si;
-    si.init(u0, u1, G, p.mg_G);
+    si.init(u0, u1, G, p.mg_G, tail_last);
     T = si.steps();
     const int whole = si.t_last - si.t_first + 1 - (si.head_partial ? 1 : 0) - (si.tail_partial ? 1 : 0);
-    nsplit = (si.tail_partial && whole > 0) ? 1 : 0;
+    nsplit = (si.tail_partial && whole > 0 && !tail_last) ? 1 : 0;
   }
 
   const uint32_t ring_a = smem_u32(ring);
@@ -556,7 +568,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
     // kernel: weights never depend on it.
     if (lane == 0) {
       SegIter it;
-      it.init(u0, u1, G, p.mg_G);
+      it.init(u0, u1, G, p.mg_G, tail_last);
       Seg sg;
       int st = 0, t = 0;
       uint32_t ph = 1;  // a fresh "empty" barrier reads as already released
@@ -756,7 +768,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
       if (lane == 0 && team_ok) {
         pdl_wait();
         SegIter it;
-        it.init(u0, u1, G, p.mg_G);
+        it.init(u0, u1, G, p.mg_G, tail_last);
         Seg sg;
         int t = 0;
         bool ok = true;
