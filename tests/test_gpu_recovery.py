@@ -69,3 +69,37 @@ def test_alloc_and_repack_on_a_side_stream(pkg, oracle, synth):
             st.synchronize()
             assert np.array_equal(host_bits(dst), want)
             pkg.awq_free(w)
+
+
+def test_matmul_right_behind_a_repack_on_the_same_stream(pkg, oracle, synth):
+    """The decode kernels fetch weights before they wait for the kernel in front of them, so the library
+    enqueues the first matmul behind a weight write on its stream as a fully serialised launch. A repack
+    followed at once by a GEMV, with no synchronisation in between, must give the bits of a GEMV on settled
+    weights - for every one of a few rounds that overwrite the same container with new weights."""
+    N, K = 4096, 2048
+    st = torch.cuda.Stream()
+    s = pkg.gemv_scratch_alloc(K, N, 128, 1)
+    x = dev_bf16(synth.make_activations(1, K, seed=9)[0])
+    torch.cuda.synchronize()
+    with torch.cuda.stream(st):
+        w = pkg.awq_alloc_fused(N, K)
+        for rnd in range(4):
+            packed, scale, zp = synth.make_weights(N, K, seed=50 + rnd)
+            dp = torch.from_numpy(packed.view(np.int32)).cuda()
+            ds = torch.from_numpy(scale.view(np.int16)).cuda()
+            dz = torch.from_numpy(zp.view(np.int32)).cuda()
+            torch.cuda.synchronize()  # the uploads above ran on this stream too; what is tested comes next
+            early = torch.empty(N, dtype=torch.bfloat16, device="cuda")
+            pkg.awq_repack_into(w, 0, dp, ds, dz, stream=st)
+            pkg.gemv_w4a16(early, w, x, s, stream=st)   # no synchronisation since the repack
+            st.synchronize()
+            settled = torch.empty(N, dtype=torch.bfloat16, device="cuda")
+            pkg.gemv_w4a16(settled, w, x, s, stream=st)
+            st.synchronize()
+            assert torch.equal(early.view(torch.int16), settled.view(torch.int16)), f"round {rnd}"
+            ref = oracle.gemm_f64(packed, scale, zp, synth.make_activations(1, K, seed=9))[0]
+            got = synth.bf16_bits_to_f32(host_bits(settled)).astype(np.float64)
+            assert np.max(np.abs(got - ref)) / np.max(np.abs(ref)) <= 1e-2
+        pkg.awq_free(w)
+    assert pkg.device_status() == 0
+    pkg.gemv_scratch_free(s)
