@@ -1178,14 +1178,31 @@ __global__ void __launch_bounds__(kThreads, 1) k_skinny(const SkinnyParams p) {
         *sflag = last;
       }
       named_bar_sync(kFixBar, nfix);
-      if (*sflag && tid < M) {
-        Pair b{-FLT_MAX, INT_MAX};
-        for (unsigned cc = 0; cc < gridDim.x; ++cc) {
-          Pair qv;
-          qv.v = __ldcg(&cta_pairs[cc * 16 + tid].v);
-          qv.i = __ldcg(&cta_pairs[cc * 16 + tid].i);
-          if (better(qv.v, qv.i, b.v, b.i)) b = qv;
+      if (*sflag) {
+        // The last CTA to arrive: every CTA's pairs are in memory. One warp per token (in turn): its lanes load
+        // the CTAs' pairs side by side - one L2 round trip instead of a thread walking all the CTAs - and a
+        // shuffle tree picks the winner (larger value, else lower index: the order of comparisons does not matter).
+        const int nw = nfix >> 5;
+        for (int m = fslot; m < M; m += nw) {
+          Pair b{-FLT_MAX, INT_MAX};
+          for (unsigned cc = lane; cc < gridDim.x; cc += 32) {
+            Pair qv;
+            qv.v = __ldcg(&cta_pairs[cc * 16 + m].v);
+            qv.i = __ldcg(&cta_pairs[cc * 16 + m].i);
+            if (better(qv.v, qv.i, b.v, b.i)) b = qv;
+          }
+#pragma unroll
+          for (int off = 16; off; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, b.v, off);
+            const int oi = __shfl_xor_sync(0xffffffffu, b.i, off);
+            if (better(ov, oi, b.v, b.i)) b = Pair{ov, oi};
+          }
+          if (lane == 0) cand[m] = b;
         }
+        named_bar_sync(kFixBar, nfix);
+      }
+      if (*sflag && tid < M) {
+        const Pair b = cand[tid];
         const int idx = (b.i == INT_MAX) ? 0 : b.i;  // nothing finite: index 0, as a plain scan gives
         const Pair mine{b.v, (b.i == INT_MAX) ? INT_MAX : b.i + p.row_offset};
         if (p.pairs_out) static_cast<Pair*>(p.pairs_out)[tid] = mine;
