@@ -102,9 +102,8 @@ def test_odd_group_counts_and_ragged_tiles(pkg, oracle, synth, scratch, N, K, M)
 
 
 def test_token_batches_on_a_wide_layer(pkg, oracle, synth, scratch):
-    """in_f = 17408 with enough rows that every CTA multiplies all 136 groups: the activation cache holds
-    three tokens, so M = 7 runs as three launches. Sampled rows against fp64, and equal to M single-token
-    calls bit for bit."""
+    """in_f = 17408 with enough rows that every CTA multiplies all 136 groups, M = 7 in one launch. Sampled rows
+    against fp64, and equal to M single-token calls bit for bit (the same integer sums, added in the same order)."""
     N, K, M = 20480, 17408, 7
     (packed, scale, zp), w = _weights(pkg, synth, N, K, seed=9)
     x = synth.make_activations(M, K, seed=21)
